@@ -1,0 +1,78 @@
+"""Pins the CPU oracle (C restatement and PyTorch port) to golden outputs that
+were produced by importing the reference's own pure-PyTorch definitions."""
+import pytest
+import torch
+
+import oracle
+from oracle import torch_port
+from helpers import golden_names, load_golden, assert_close
+
+PIN = 2e-5   # fp32 round-off between a double-precision loop and the reference's fp32 tensors
+
+
+def _opt(d, k):
+    return d.get(k)
+
+
+@pytest.mark.parametrize("impl", ["c", "torch"])
+@pytest.mark.parametrize("name", golden_names("m1_"))
+def test_selective_scan_pinned(name, impl):
+    d = load_golden(name)
+    fn = oracle.selective_scan if impl == "c" else torch_port.selective_scan
+    out, last = fn(d["u"], d["delta"], d["A"], d["B"], d["C"], _opt(d, "D"), _opt(d, "z"),
+                   _opt(d, "delta_bias"), delta_softplus=True, return_last_state=True)
+    # bf16 fixtures hold the reference output after its cast back to bf16
+    tol = 4e-3 if d["bf16"] else PIN
+    assert_close(out, d["out"], tol, name + " out")
+    assert_close(last, d["last_state"], PIN, name + " last_state")
+
+
+@pytest.mark.parametrize("impl", ["c", "torch"])
+@pytest.mark.parametrize("name", golden_names("ssu_"))
+def test_state_update_pinned(name, impl):
+    d = load_golden(name)
+    fn = oracle.selective_state_update if impl == "c" else torch_port.selective_state_update
+    state = d["state0"].clone()
+    # a carried state narrowed to bf16 each step can flip one bf16 ulp between implementations
+    tol = 4e-3 if d["bf16"] else PIN
+    for s in range(d["x"].shape[0]):
+        z = None if "z" not in d else d["z"][s]
+        out = fn(state, d["x"][s], d["dt"][s], d["A"], d["B"][s], d["C"][s], d["D"], z, d["dt_bias"],
+                 dt_softplus=True)
+        if d["bf16"]:   # the fixture narrows the carried state to bf16 after each step
+            state = state.bfloat16().float()
+        assert_close(out, d["out"][s], tol, f"{name} out[{s}]")
+    assert_close(state, d["state_final"], tol, name + " state")
+
+
+@pytest.mark.parametrize("impl", ["c", "torch"])
+@pytest.mark.parametrize("name", golden_names("ssd_"))
+def test_ssd_pinned(name, impl):
+    d = load_golden(name)
+    Q = int(d["chunk_size"])
+    if impl == "torch" and d["x"].shape[1] % Q != 0:
+        pytest.skip("the PyTorch port, like the reference's chunked definition, needs whole chunks")
+    fn = oracle.ssd_chunk_scan if impl == "c" else torch_port.ssd_chunk_scan
+    out, fin = fn(d["x"], d["dt"], d["A"], d["B"], d["C"], Q, _opt(d, "D"), _opt(d, "z"), d["dt_bias"],
+                  _opt(d, "initial_states"), dt_softplus=True)
+    assert_close(out, d["out"], PIN, name + " out")
+    assert_close(fin, d["final_states"], PIN, name + " final_states")
+
+
+def test_oracle_ssd_equals_recurrence():
+    """Cross-check inside the oracle: SSD with scalar A per head is the Mamba-1 recurrence."""
+    g = torch.Generator().manual_seed(5)
+    b, L, H, P, G, N, Q = 1, 96, 2, 4, 1, 8, 32
+    x = torch.randn(b, L, H, P, generator=g)
+    dt = torch.rand(b, L, H, generator=g)
+    A = -torch.rand(H, generator=g) - 0.5
+    B = torch.randn(b, L, G, N, generator=g)
+    C = torch.randn(b, L, G, N, generator=g)
+    out, fin = oracle.ssd_chunk_scan(x, dt, A, B, C, Q)
+    u = x.permute(0, 2, 3, 1).reshape(b, H * P, L)
+    dl = dt.permute(0, 2, 1).repeat_interleave(P, dim=1)
+    A1 = A.repeat_interleave(P)[:, None].expand(H * P, N).contiguous()
+    o1, l1 = oracle.selective_scan(u, dl, A1, B.permute(0, 2, 3, 1), C.permute(0, 2, 3, 1),
+                                   return_last_state=True)
+    assert_close(out.permute(0, 2, 3, 1).reshape(b, H * P, L), o1, 1e-6, "ssd vs scan")
+    assert_close(fin.reshape(b, H * P, N), l1, 1e-6, "final vs last")
