@@ -1,0 +1,180 @@
+/*
+ * mamba_b200 -- C ABI of the B200 (sm_100a) scan library, libmamba_b200.so.
+ *
+ * Three forward operators of state-spaces/mamba are served:
+ *   Mamba-1 selective scan, the Mamba-2 SSD chunked scan, and the single-token
+ *   decode state update.  The library never allocates or frees device memory,
+ *   keeps no pointer after a call returns, never synchronises the device and
+ *   never throws: every entry returns 0 or a negative MB200_ERR_* code and
+ *   mb200_last_error() gives the text for the calling thread.  All kernels are
+ *   enqueued on the cudaStream_t passed as `stream` (as a void*), on the device
+ *   named by args->device (made current for the call).
+ *
+ * All strides are in ELEMENTS of the tensor they describe.  A stride of 0 is a
+ * broadcast.  Optional tensors are NULL when absent.
+ */
+#ifndef MAMBA_B200_H
+#define MAMBA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MB200_OK               0
+#define MB200_ERR_BAD_ARG     -1   /* a shape, stride, alignment or pointer the call cannot accept   */
+#define MB200_ERR_UNSUPPORTED -2   /* a documented feature of the operator that this build lacks      */
+#define MB200_ERR_LAUNCH      -3   /* the CUDA runtime refused a launch or an attribute change        */
+#define MB200_ERR_NO_DEVICE   -4   /* no sm_100 device / wrong device index                           */
+
+typedef enum mb200_dtype { MB200_F32 = 0, MB200_F16 = 1, MB200_BF16 = 2 } mb200_dtype;
+
+/* Library version (major*10000 + minor*100 + patch) and last error text of this thread. */
+int mb200_version(void);
+const char *mb200_last_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Mamba-1 selective scan forward.
+ * Replaces selective_scan_cuda.fwd (csrc/selective_scan/selective_scan.cpp:226-336, bound at
+ * :494-497; kernel csrc/selective_scan/selective_scan_fwd_kernel.cuh:72-308), which
+ * SelectiveScanFn.forward calls (mamba_ssm/ops/selective_scan_interface.py:58).
+ *
+ *   h_t = exp(dt_t A) h_{t-1} + dt_t B_t u_t ;  y_t = C_t . h_t + D u_t ;  out_t = y_t * silu(z_t)
+ *   dt_t = delta_t + delta_bias, passed through softplus (identity above 20) when delta_softplus.
+ *
+ * u, delta, z, out, out_pregate : (batch, dim, seqlen), io_dtype, seqlen stride 1.
+ * A : (dim, dstate) fp32.   D, delta_bias : (dim) fp32, contiguous.
+ * B, C : when *_variable, (batch, ngroups, dstate, seqlen) io_dtype with seqlen stride 1 and
+ *        strides {batch, group, dstate}; otherwise (dim, dstate) fp32 with strides {dim, dstate, 0}.
+ * out        : gated output when z is given, else y.  out_pregate (optional, only with z): y.
+ * last_state : optional (batch, dim, dstate) fp32 contiguous, h after the last step.
+ * dstate <= 256.  Complex A is not supported (MB200_ERR_UNSUPPORTED is the caller's to raise).
+ */
+typedef struct mb200_scan_args {
+    const void *u, *delta;
+    const float *A;
+    const void *B, *C;
+    const float *D;
+    const void *z;
+    const float *delta_bias;
+    void *out, *out_pregate;
+    float *last_state;
+    int32_t batch, dim, seqlen, dstate, ngroups;
+    int32_t io_dtype;                 /* mb200_dtype of u, delta, z, out and of variable B, C */
+    int32_t B_variable, C_variable, delta_softplus;
+    int32_t device;
+    int64_t u_stride[2], delta_stride[2], z_stride[2], out_stride[2], pregate_stride[2]; /* {batch, dim} */
+    int64_t A_stride[2];              /* {dim, dstate} */
+    int64_t B_stride[3], C_stride[3];
+} mb200_scan_args;
+
+int mb200_selective_scan_fwd(const mb200_scan_args *args, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Single-token decode state update, state modified in place.
+ * Replaces the launch in selective_state_update (mamba_ssm/ops/triton/selective_state_update.py:
+ * 135-221, kernel :23-132).
+ *
+ *   dt = dt + dt_bias (softplus, identity above 20);  state <- state * exp(A dt) + (B dt) x
+ *   out = sum_n state C + D x, then * silu(z)
+ *
+ * state : (nstates, nheads, dim, dstate) state_dtype.   x, z, out : (batch, nheads, dim) x_dtype.
+ * dt : (batch, nheads, dim) dt_dtype.   A : (nheads, dim, dstate) fp32.
+ * B, C : (batch, ngroups, dstate) bc_dtype.   D, dt_bias : (nheads, dim) fp32.
+ * state_batch_indices : optional int32 (batch); row b uses state[idx[b]]; idx < 0 marks padding
+ *   (out row written as 0, no state touched).
+ * The call is a pure enqueue (no allocation, no host state), so it can sit inside a CUDA graph,
+ * as the reference's generation loop requires (mamba_ssm/utils/generation.py:342-389).
+ */
+typedef struct mb200_ssu_args {
+    void *state;
+    const void *x, *dt;
+    const float *A;
+    const void *B, *C;
+    const float *D;
+    const void *z;
+    const float *dt_bias;
+    void *out;
+    const int32_t *state_batch_indices;
+    int32_t batch, nheads, dim, dstate, ngroups;
+    int32_t state_dtype, x_dtype, dt_dtype, bc_dtype;
+    int32_t dt_softplus;
+    int32_t device;
+    int64_t state_stride[4];          /* {batch, head, dim, dstate} */
+    int64_t x_stride[3], dt_stride[3], z_stride[3], out_stride[3];   /* {batch, head, dim} */
+    int64_t A_stride[3];              /* {head, dim, dstate} */
+    int64_t B_stride[3], C_stride[3]; /* {batch, group, dstate} */
+    int64_t D_stride[2], dt_bias_stride[2];                          /* {head, dim} */
+} mb200_ssu_args;
+
+int mb200_selective_state_update(const mb200_ssu_args *args, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Mamba-2 SSD chunked scan forward.
+ * Replaces the five launches of _mamba_chunk_scan_combined_fwd
+ * (mamba_ssm/ops/triton/ssd_combined.py:343-394): _chunk_cumsum_fwd (ssd_chunk_state.py:718-741),
+ * _chunk_state_fwd (:812-842), _state_passing_fwd (ssd_state_passing.py:196-224),
+ * _bmm_chunk_fwd (ssd_bmm.py:165-210) and _chunk_scan_fwd (ssd_chunk_scan.py:1259-1308).
+ *
+ * x, z, out : (batch, seqlen, nheads, headdim) io_dtype, headdim stride 1, strides {batch, seq, head}.
+ * dt : (batch, seqlen, nheads) dt_dtype, strides {batch, seq, head}.   A, dt_bias : (nheads) fp32.
+ * B, C : (batch, seqlen, ngroups, dstate) io_dtype, dstate stride 1, strides {batch, seq, group}.
+ * D : (nheads) fp32, or (nheads, headdim) fp32 contiguous when D_has_hdim.
+ * seq_idx : optional int32 (batch, seqlen) contiguous; positions with different ids do not interact.
+ * initial_states : optional (batch, nheads, headdim, dstate) fp32 contiguous.
+ * final_states   : optional (batch, nheads, headdim, dstate) fp32 contiguous.
+ * scratch : caller-owned device buffer of at least mb200_ssd_scratch_bytes() bytes, 256-byte
+ *   aligned; holds dt, the dt*A cumulative sums, the per-chunk states and C.B^T between stages.
+ * phases : MB200_SSD_PHASE_ALL for the operator.  A sequence that is split across devices runs
+ *   MB200_SSD_PHASE_LOCAL first (cumulative sums, per-chunk states, and -- with zero incoming state --
+ *   the state at the end of the local range into final_states plus the product of the chunk decays
+ *   into range_decay), exchanges states, then MB200_SSD_PHASE_OUTPUT with initial_states set to the
+ *   incoming state (inter-chunk recurrence and chunk outputs; scratch must be untouched in between).
+ * range_decay : optional (batch, nheads) fp32, written in the LOCAL phase.
+ */
+#define MB200_SSD_PHASE_LOCAL  1
+#define MB200_SSD_PHASE_OUTPUT 2
+#define MB200_SSD_PHASE_ALL    3
+
+typedef struct mb200_ssd_args {
+    const void *x, *dt;
+    const float *A;
+    const void *B, *C;
+    const float *D;
+    const void *z;
+    const float *dt_bias;
+    const int32_t *seq_idx;
+    const float *initial_states;
+    void *out;
+    float *final_states;
+    float *range_decay;
+    void *scratch;
+    size_t scratch_bytes;
+    int32_t batch, seqlen, nheads, headdim, ngroups, dstate, chunk_size;
+    int32_t io_dtype, dt_dtype;
+    int32_t dt_softplus, D_has_hdim;
+    float dt_min, dt_max;             /* clamp applied after softplus; {0, +inf} disables it */
+    int32_t phases;
+    int32_t device;
+    int64_t x_stride[3], z_stride[3], out_stride[3], dt_stride[3], B_stride[3], C_stride[3];
+} mb200_ssd_args;
+
+int mb200_ssd_scratch_bytes(const mb200_ssd_args *args, size_t *bytes);
+int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream);
+
+/*
+ * Folds an incoming state through a device's local range when a sequence is split across devices:
+ *   s_out = range_decay[b,h] * s_in + s_local      over (batch*nheads) rows of `row` fp32 elements.
+ * No counterpart in the reference (its SSD scan always sees the whole sequence on one device,
+ * mamba_ssm/ops/triton/ssd_state_passing.py:72-80 being the recurrence this applies range-wise).
+ * s_in may be NULL (treated as zero); s_out may alias s_local.
+ */
+int mb200_ssd_fold_state(const float *s_in, const float *range_decay, const float *s_local, float *s_out,
+                         int64_t rows, int64_t row, int32_t device, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAMBA_B200_H */

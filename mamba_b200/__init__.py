@@ -1,0 +1,18 @@
+"""mamba_b200 -- B200 (sm_100a) kernels behind the scan operators of state-spaces/mamba.
+
+    from mamba_b200 import selective_scan_fn, mamba_chunk_scan_combined, selective_state_update
+
+are drop-in replacements (forward / inference) for the reference's functions of the same name.
+All work is done by hand-written CUDA in ``libmamba_b200.so`` (C ABI: include/mamba_b200.h);
+there is no CPU path and no fallback -- a missing library raises on first use.
+"""
+from .ops import (  # noqa: F401
+    mamba_chunk_scan_combined,
+    selective_scan_fn,
+    selective_state_update,
+    ssd_finish,
+    ssd_fold_state,
+    ssd_local_states,
+)
+
+__version__ = "0.1.0"

@@ -1,0 +1,96 @@
+// Shared device/host helpers of libmamba_b200: error reporting, dtype loads, scalar math.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mamba_b200.h"
+
+namespace mb200 {
+
+// ---- error text (thread local), set by every failing entry point -------------------------------
+void set_error(const char *fmt, ...);
+int fail(int code, const char *fmt, ...);
+// Makes `device` current; checks that it is an sm_100 part.  Returns MB200_OK or an error code.
+int enter_device(int device);
+int sm_count(int device);
+
+#define MB200_CHECK_ARG(cond, ...)                                     \
+    do {                                                               \
+        if (!(cond)) return ::mb200::fail(MB200_ERR_BAD_ARG, __VA_ARGS__); \
+    } while (0)
+
+#define MB200_CHECK_LAUNCH(what)                                                          \
+    do {                                                                                  \
+        cudaError_t e__ = cudaGetLastError();                                             \
+        if (e__ != cudaSuccess)                                                           \
+            return ::mb200::fail(MB200_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e__)); \
+    } while (0)
+
+// ---- dtype helpers ------------------------------------------------------------------------------
+template <typename T> struct DType;
+template <> struct DType<float> { static constexpr int code = MB200_F32; };
+template <> struct DType<__half> { static constexpr int code = MB200_F16; };
+template <> struct DType<__nv_bfloat16> { static constexpr int code = MB200_BF16; };
+
+__host__ __device__ inline int dtype_size(int code) { return code == MB200_F32 ? 4 : 2; }
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Element `i` of a tensor whose dtype is only known at run time (uniform branch; small tensors only).
+__device__ __forceinline__ float load_any(const void *p, int dtype, int64_t i)
+{
+    if (dtype == MB200_F32) return static_cast<const float *>(p)[i];
+    if (dtype == MB200_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
+    return __half2float(static_cast<const __half *>(p)[i]);
+}
+__device__ __forceinline__ void store_any(void *p, int dtype, int64_t i, float v)
+{
+    if (dtype == MB200_F32) static_cast<float *>(p)[i] = v;
+    else if (dtype == MB200_BF16) static_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+    else static_cast<__half *>(p)[i] = __float2half_rn(v);
+}
+
+// A 16-byte packet of T widened to floats and back.
+template <typename T> struct Vec16 {
+    static constexpr int N = 16 / sizeof(T);
+    uint4 raw;
+    __device__ __forceinline__ void load(const T *p) { raw = *reinterpret_cast<const uint4 *>(p); }
+    __device__ __forceinline__ void store(T *p) const { *reinterpret_cast<uint4 *>(p) = raw; }
+    __device__ __forceinline__ void unpack(float (&f)[N]) const
+    {
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < N; ++i) f[i] = to_float(e[i]);
+    }
+    __device__ __forceinline__ void pack(const float (&f)[N])
+    {
+        T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < N; ++i) e[i] = from_float<T>(f[i]);
+    }
+};
+
+// ---- scalar math --------------------------------------------------------------------------------
+// softplus with the identity branch above 20 that every site of the path uses.
+__device__ __forceinline__ float softplus20(float x) { return x <= 20.f ? log1pf(expf(x)) : x; }
+__device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float fast_silu(float z) { return __fdividef(z, 1.f + __expf(-z)); }
+__device__ __forceinline__ float ex2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
+
+}  // namespace mb200

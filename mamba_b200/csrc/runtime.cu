@@ -1,0 +1,55 @@
+// Host-side runtime of libmamba_b200: thread-local error text, device entry, version.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace mb200 {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+// Immutable per-device attributes, filled on first use (idempotent, so a race only repeats the query).
+static int g_sm_count[64] = {0};
+static int g_checked[64] = {0};
+
+int enter_device(int device)
+{
+    if (device < 0 || device >= 64) return fail(MB200_ERR_NO_DEVICE, "device index %d out of range", device);
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return fail(MB200_ERR_NO_DEVICE, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
+    if (!g_checked[device]) {
+        int major = 0, sms = 0;
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (major != 10)
+            return fail(MB200_ERR_NO_DEVICE, "device %d has compute capability %d.x; this library holds sm_100a code only",
+                        device, major);
+        g_sm_count[device] = sms;
+        g_checked[device] = 1;
+    }
+    return MB200_OK;
+}
+
+int sm_count(int device) { return g_sm_count[device]; }
+
+}  // namespace mb200
+
+extern "C" int mb200_version(void) { return 100; }
+extern "C" const char *mb200_last_error(void) { return mb200::g_error; }

@@ -1,0 +1,377 @@
+// Mamba-2 SSD chunked forward for sm_100a: stage kernels that work for every shape and dtype.
+//
+// Stages (each one launch, all on the caller's stream, handing fp32 intermediates through the
+// caller's scratch buffer):
+//   1. chunk_cumsum   dt <- clamp(softplus(dt + bias)), dA_cum <- cumsum_Q(dt A)
+//   2. chunk_state    S_c[p,n] = sum_k x[k,p] B[k,n] exp(min(dA_last - dA_k, 0)) dt_k
+//   3. state_passing  H_{c+1} = exp(dA_last_c) H_c + S_c, slot c rewritten with H_c
+//   4. chunk_cb       CB[m,k] = C_m . B_k   (lower block triangle)
+//   5. chunk_scan     y_m = exp(dA_m) C_m.H_c + sum_{k<=m} CB[m,k] exp(min(dA_m - dA_k,0)) dt_k x_k + D x_m,
+//                     then y_m * silu(z_m)
+// The contractions here run on the fp32 FMA pipes through a 64x64 shared-memory tile loop, which
+// keeps fp32 inputs exact; the bf16/fp16 tensor-core tiles for the benchmark shapes live in
+// ssd_tc.cu and replace stages 2, 4 and 5 when the shape qualifies.
+#include "ssd_common.cuh"
+
+namespace mb200 {
+namespace {
+
+constexpr int kT = 256;       // threads per CTA in the tile kernels
+constexpr int kKT = 32;       // reduction step
+constexpr int kLd = 68;       // padded leading dimension of the staged tiles (keeps float4 alignment)
+
+// acc[4][4] += A[64 x K] * B[K x 64] for the thread's 4x4 patch (rows ty*4.., cols tx*4..).
+// fa(k, i) / fb(k, j) return the (bounds-checked) operand elements; *_KFAST says the source is
+// contiguous along k, which only changes which thread fetches which element.
+template <bool A_KFAST, bool B_KFAST, class FA, class FB>
+__device__ __forceinline__ void tile_gemm(float (&acc)[4][4], int K, FA fa, FB fb, float *As, float *Bs)
+{
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    for (int k0 = 0; k0 < K; k0 += kKT) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < kKT * 64; e += kT) {
+            int kk, i;
+            if (A_KFAST) { i = e / kKT; kk = e % kKT; } else { kk = e / 64; i = e % 64; }
+            As[kk * kLd + i] = (k0 + kk < K) ? fa(k0 + kk, i) : 0.f;
+        }
+        for (int e = threadIdx.x; e < kKT * 64; e += kT) {
+            int kk, j;
+            if (B_KFAST) { j = e / kKT; kk = e % kKT; } else { kk = e / 64; j = e % 64; }
+            Bs[kk * kLd + j] = (k0 + kk < K) ? fb(k0 + kk, j) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < kKT; ++kk) {
+            const float4 av = *reinterpret_cast<const float4 *>(As + kk * kLd + ty * 4);
+            const float4 bv = *reinterpret_cast<const float4 *>(Bs + kk * kLd + tx * 4);
+            const float ar[4] = {av.x, av.y, av.z, av.w}, br[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
+        }
+    }
+}
+
+// ---- stage 1 ------------------------------------------------------------------------------------
+// One CTA per (chunk, batch, 32 heads): coalesced read of dt over heads, transposed in shared
+// memory, then a warp scan along the chunk per head.
+__global__ void __launch_bounds__(256) ssd_cumsum_kernel(const mb200_ssd_args a, float *dt_out, float *dA_out, int nchunks)
+{
+    extern __shared__ float sm[];   // Q x 33
+    const int Q = a.chunk_size;
+    const int c = blockIdx.x, b = blockIdx.y, h0 = blockIdx.z * 32;
+    const int t0 = c * Q;
+    for (int e = threadIdx.x; e < Q * 32; e += 256) {
+        const int k = e / 32, hh = e % 32;
+        const int h = h0 + hh;
+        float v = 0.f;
+        if (h < a.nheads && t0 + k < a.seqlen) {
+            v = load_any(a.dt, a.dt_dtype, (int64_t)b * a.dt_stride[0] + (int64_t)(t0 + k) * a.dt_stride[1] + (int64_t)h * a.dt_stride[2]);
+            if (a.dt_bias) v += a.dt_bias[h];
+            if (a.dt_softplus) v = softplus20(v);
+            v = fminf(fmaxf(v, a.dt_min), a.dt_max);
+        }
+        sm[k * 33 + hh] = v;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int hh = warp; hh < 32; hh += 8) {
+        const int h = h0 + hh;
+        if (h >= a.nheads) break;
+        const float A = a.A[h];
+        float carry = 0.f;
+        const int64_t o = (((int64_t)b * a.nheads + h) * nchunks + c) * Q;
+        for (int k0 = 0; k0 < Q; k0 += 32) {
+            const int k = k0 + lane;
+            const float dtv = k < Q ? sm[k * 33 + hh] : 0.f;
+            float v = dtv * A;
+#pragma unroll
+            for (int o2 = 1; o2 < 32; o2 <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, v, o2);
+                if (lane >= o2) v += up;
+            }
+            v += carry;
+            if (k < Q) {
+                dt_out[o + k] = dtv;
+                dA_out[o + k] = v;
+            }
+            carry = __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+}
+
+// ---- stage 2 ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kT) ssd_chunk_state_kernel(const mb200_ssd_args a, const float *dtb, const float *dAb,
+                                                             float *states, int nchunks)
+{
+    __shared__ __align__(16) float As[kKT * kLd], Bs[kKT * kLd];
+    const int Q = a.chunk_size, P = a.headdim, N = a.dstate;
+    const int tilesN = (N + 63) / 64;
+    const int p0 = (blockIdx.x / tilesN) * 64, n0 = (blockIdx.x % tilesN) * 64;
+    const int b = blockIdx.y / nchunks, c = blockIdx.y % nchunks, h = blockIdx.z;
+    const int g = h / (a.nheads / a.ngroups);
+    const int t0 = c * Q;
+    const int len = min(Q, a.seqlen - t0);
+    const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * Q;
+    const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * Q;
+    const float dA_last = dAc[Q - 1];
+    const T *x = static_cast<const T *>(a.x) + (int64_t)b * a.x_stride[0] + (int64_t)t0 * a.x_stride[1] + (int64_t)h * a.x_stride[2];
+    const T *B = static_cast<const T *>(a.B) + (int64_t)b * a.B_stride[0] + (int64_t)t0 * a.B_stride[1] + (int64_t)g * a.B_stride[2];
+    float acc[4][4] = {};
+    tile_gemm<false, false>(
+        acc, len,
+        [&](int k, int i) { return p0 + i < P ? to_float(x[(int64_t)k * a.x_stride[1] + p0 + i]) * (__expf(fminf(dA_last - dAc[k], 0.f)) * dtc[k]) : 0.f; },
+        [&](int k, int j) { return n0 + j < N ? to_float(B[(int64_t)k * a.B_stride[1] + n0 + j]) : 0.f; }, As, Bs);
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float *S = states + (((int64_t)b * nchunks + c) * a.nheads + h) * (int64_t)P * N;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int p = p0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (p < P && n < N) S[(int64_t)p * N + n] = acc[i][j];
+        }
+}
+
+// ---- stage 3 ------------------------------------------------------------------------------------
+// Elementwise over P*N, serial over chunks.  Slot c of `states` receives the state entering chunk c.
+__global__ void __launch_bounds__(256) ssd_state_passing_kernel(const mb200_ssd_args a, const float *dAb, float *states,
+                                                                int nchunks, bool write_prev)
+{
+    const int64_t PN = (int64_t)a.headdim * a.dstate;
+    const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int Q = a.chunk_size;
+    const float *dA_last = dAb + ((int64_t)b * a.nheads + h) * nchunks * Q + (Q - 1);
+    if (e < PN) {
+        float run = a.initial_states ? a.initial_states[((int64_t)b * a.nheads + h) * PN + e] : 0.f;
+        for (int c = 0; c < nchunks; ++c) {
+            float *slot = states + (((int64_t)b * nchunks + c) * a.nheads + h) * PN + e;
+            const float s = *slot;
+            if (write_prev) *slot = run;
+            run = fmaf(__expf(dA_last[(int64_t)c * Q]), run, s);
+        }
+        if (a.final_states) a.final_states[((int64_t)b * a.nheads + h) * PN + e] = run;
+    }
+    if (a.range_decay && blockIdx.x == 0 && threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int c = 0; c < nchunks; ++c) tot += dA_last[(int64_t)c * Q];
+        a.range_decay[(int64_t)b * a.nheads + h] = __expf(tot);
+    }
+}
+
+// ---- stage 4 ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kT) ssd_cb_kernel(const mb200_ssd_args a, float *cb, int nchunks)
+{
+    __shared__ __align__(16) float As[kKT * kLd], Bs[kKT * kLd];
+    const int Q = a.chunk_size, N = a.dstate;
+    const int tiles = (Q + 63) / 64;
+    const int m0 = (blockIdx.x / tiles) * 64, k0 = (blockIdx.x % tiles) * 64;
+    if (k0 > m0) return;   // strictly upper blocks are never read
+    const int b = blockIdx.y / nchunks, c = blockIdx.y % nchunks, g = blockIdx.z;
+    const int t0 = c * Q;
+    const int len = min(Q, a.seqlen - t0);
+    const T *C = static_cast<const T *>(a.C) + (int64_t)b * a.C_stride[0] + (int64_t)t0 * a.C_stride[1] + (int64_t)g * a.C_stride[2];
+    const T *B = static_cast<const T *>(a.B) + (int64_t)b * a.B_stride[0] + (int64_t)t0 * a.B_stride[1] + (int64_t)g * a.B_stride[2];
+    float acc[4][4] = {};
+    tile_gemm<true, true>(
+        acc, N, [&](int n, int i) { return m0 + i < len ? to_float(C[(int64_t)(m0 + i) * a.C_stride[1] + n]) : 0.f; },
+        [&](int n, int j) { return k0 + j < len ? to_float(B[(int64_t)(k0 + j) * a.B_stride[1] + n]) : 0.f; }, As, Bs);
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float *out = cb + (((int64_t)b * nchunks + c) * a.ngroups + g) * (int64_t)Q * Q;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, k = k0 + tx * 4 + j;
+            if (m < Q && k < Q) out[(int64_t)m * Q + k] = acc[i][j];
+        }
+}
+
+// ---- stage 5 ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kT) ssd_chunk_scan_kernel(const mb200_ssd_args a, const float *dtb, const float *dAb,
+                                                            const float *states, const float *cb, int nchunks)
+{
+    __shared__ __align__(16) float As[kKT * kLd], Bs[kKT * kLd];
+    const int Q = a.chunk_size, P = a.headdim, N = a.dstate;
+    const int tilesP = (P + 63) / 64;
+    const int m0 = (blockIdx.x / tilesP) * 64, p0 = (blockIdx.x % tilesP) * 64;
+    const int b = blockIdx.y / nchunks, c = blockIdx.y % nchunks, h = blockIdx.z;
+    const int g = h / (a.nheads / a.ngroups);
+    const int t0 = c * Q;
+    const int len = min(Q, a.seqlen - t0);
+    if (m0 >= len) return;
+    const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * Q;
+    const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * Q;
+    const T *x = static_cast<const T *>(a.x) + (int64_t)b * a.x_stride[0] + (int64_t)t0 * a.x_stride[1] + (int64_t)h * a.x_stride[2];
+    const T *C = static_cast<const T *>(a.C) + (int64_t)b * a.C_stride[0] + (int64_t)t0 * a.C_stride[1] + (int64_t)g * a.C_stride[2];
+    const float *prev = states + (((int64_t)b * nchunks + c) * a.nheads + h) * (int64_t)P * N;
+    const float *cbc = cb + (((int64_t)b * nchunks + c) * a.ngroups + g) * (int64_t)Q * Q;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+
+    float acc[4][4] = {};
+    // contribution of the state entering the chunk: exp(dA_m) * C_m . H[p,:]
+    tile_gemm<true, true>(
+        acc, N, [&](int n, int i) { return m0 + i < len ? to_float(C[(int64_t)(m0 + i) * a.C_stride[1] + n]) : 0.f; },
+        [&](int n, int j) { return p0 + j < P ? prev[(int64_t)(p0 + j) * N + n] : 0.f; }, As, Bs);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        const float sc = m < len ? __expf(dAc[m]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] *= sc;
+    }
+    // causal intra-chunk part
+    const int kend = min(m0 + 64, len);
+    tile_gemm<true, false>(
+        acc, kend,
+        [&](int k, int i) {
+            const int m = m0 + i;
+            return (m < len && k <= m) ? cbc[(int64_t)m * Q + k] * __expf(fminf(dAc[m] - dAc[k], 0.f)) * dtc[k] : 0.f;
+        },
+        [&](int k, int j) { return p0 + j < P ? to_float(x[(int64_t)k * a.x_stride[1] + p0 + j]) : 0.f; }, As, Bs);
+
+    const T *z = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)t0 * a.z_stride[1] + (int64_t)h * a.z_stride[2] : nullptr;
+    T *out = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)t0 * a.out_stride[1] + (int64_t)h * a.out_stride[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= len) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int p = p0 + tx * 4 + j;
+            if (p >= P) continue;
+            float y = acc[i][j];
+            if (a.D) y = fmaf(to_float(x[(int64_t)m * a.x_stride[1] + p]), a.D_has_hdim ? a.D[(int64_t)h * P + p] : a.D[h], y);
+            if (z) y *= silu(to_float(z[(int64_t)m * a.z_stride[1] + p]));
+            out[(int64_t)m * a.out_stride[1] + p] = from_float<T>(y);
+        }
+    }
+}
+
+__global__ void ssd_fold_kernel(const float *s_in, const float *decay, const float *s_local, float *s_out, int64_t rows,
+                                int64_t row)
+{
+    const int64_t total = rows * row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const float in = s_in ? s_in[i] : 0.f;
+        s_out[i] = fmaf(decay[i / row], in, s_local[i]);
+    }
+}
+
+template <typename T>
+int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
+{
+    char *base = static_cast<char *>(a.scratch);
+    float *dtb = reinterpret_cast<float *>(base + lay.off_dt);
+    float *dAb = reinterpret_cast<float *>(base + lay.off_dA);
+    float *states = reinterpret_cast<float *>(base + lay.off_states);
+    float *cb = reinterpret_cast<float *>(base + lay.off_cb);
+    const int nc = lay.nchunks, Q = a.chunk_size;
+    const int64_t PN = (int64_t)a.headdim * a.dstate;
+    if (a.phases & MB200_SSD_PHASE_LOCAL) {
+        const size_t cs_smem = sizeof(float) * Q * 33;
+        if (cs_smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(ssd_cumsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
+            if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd chunk_cumsum: shared memory opt-in: %s", cudaGetErrorString(e));
+        }
+        ssd_cumsum_kernel<<<dim3(nc, a.batch, (a.nheads + 31) / 32), 256, cs_smem, stream>>>(a, dtb, dAb, nc);
+        MB200_CHECK_LAUNCH("ssd chunk_cumsum");
+        ssd_chunk_state_kernel<T><<<dim3(((a.headdim + 63) / 64) * ((a.dstate + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(
+            a, dtb, dAb, states, nc);
+        MB200_CHECK_LAUNCH("ssd chunk_state");
+        if (!(a.phases & MB200_SSD_PHASE_OUTPUT) && (a.final_states || a.range_decay)) {
+            // range summary only: fold the local chunk states from a zero state, leave the slots as they are
+            mb200_ssd_args z = a;
+            z.initial_states = nullptr;
+            ssd_state_passing_kernel<<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(z, dAb, states, nc, false);
+            MB200_CHECK_LAUNCH("ssd range summary");
+        }
+    }
+    if (a.phases & MB200_SSD_PHASE_OUTPUT) {
+        mb200_ssd_args p = a;
+        if (!(a.phases & MB200_SSD_PHASE_LOCAL)) p.range_decay = nullptr;
+        ssd_state_passing_kernel<<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true);
+        MB200_CHECK_LAUNCH("ssd state_passing");
+        const int tq = (Q + 63) / 64;
+        ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);
+        MB200_CHECK_LAUNCH("ssd chunk_cb");
+        ssd_chunk_scan_kernel<T><<<dim3(tq * ((a.headdim + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(a, dtb, dAb, states, cb, nc);
+        MB200_CHECK_LAUNCH("ssd chunk_scan");
+    }
+    return MB200_OK;
+}
+
+int check_ssd(const mb200_ssd_args &a)
+{
+    MB200_CHECK_ARG(a.x && a.dt && a.A && a.B && a.C, "ssd: a required tensor is NULL");
+    MB200_CHECK_ARG(a.batch >= 0 && a.seqlen >= 0 && a.nheads > 0 && a.headdim > 0 && a.ngroups > 0 && a.dstate > 0 && a.chunk_size > 0,
+                    "ssd: bad sizes (batch %d seqlen %d nheads %d headdim %d ngroups %d dstate %d chunk %d)", a.batch, a.seqlen,
+                    a.nheads, a.headdim, a.ngroups, a.dstate, a.chunk_size);
+    MB200_CHECK_ARG(a.nheads % a.ngroups == 0, "nheads must be divisible by ngroups");
+    MB200_CHECK_ARG(a.io_dtype == MB200_F32 || a.io_dtype == MB200_F16 || a.io_dtype == MB200_BF16, "ssd: unknown io_dtype %d", a.io_dtype);
+    MB200_CHECK_ARG(a.dt_dtype == MB200_F32 || a.dt_dtype == MB200_F16 || a.dt_dtype == MB200_BF16, "ssd: unknown dt_dtype %d", a.dt_dtype);
+    MB200_CHECK_ARG(a.chunk_size <= 1024, "ssd: chunk_size must be <= 1024");
+    MB200_CHECK_ARG((a.phases & ~MB200_SSD_PHASE_ALL) == 0 && a.phases != 0, "ssd: phases must be a combination of LOCAL and OUTPUT");
+    return MB200_OK;
+}
+
+}  // namespace
+}  // namespace mb200
+
+extern "C" int mb200_ssd_scratch_bytes(const mb200_ssd_args *args, size_t *bytes)
+{
+    using namespace mb200;
+    if (!args || !bytes) return fail(MB200_ERR_BAD_ARG, "ssd_scratch_bytes: NULL argument");
+    if (int rc = check_ssd(*args)) return rc;
+    *bytes = ssd_scratch_layout(*args).total;
+    return MB200_OK;
+}
+
+extern "C" int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream_)
+{
+    using namespace mb200;
+    if (!args) return fail(MB200_ERR_BAD_ARG, "ssd_chunk_scan_fwd: args is NULL");
+    const mb200_ssd_args &a = *args;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (int rc = check_ssd(a)) return rc;
+    MB200_CHECK_ARG(!(a.phases & MB200_SSD_PHASE_OUTPUT) || a.out, "ssd: out is NULL");
+    if (a.seq_idx) return fail(MB200_ERR_UNSUPPORTED, "ssd: seq_idx is not supported yet");
+    if (a.batch == 0) return MB200_OK;
+    if (int rc = enter_device(a.device)) return rc;
+    MB200_CHECK_ARG(a.batch * (int64_t)((a.seqlen + a.chunk_size - 1) / a.chunk_size) <= 65535 && a.nheads <= 65535 && a.batch <= 65535,
+                    "ssd: batch*nchunks and nheads must be <= 65535");
+    const SsdScratch lay = ssd_scratch_layout(a);
+    if (a.seqlen == 0) {
+        if (a.final_states && (a.phases & MB200_SSD_PHASE_OUTPUT)) {
+            const size_t n = sizeof(float) * (size_t)a.batch * a.nheads * a.headdim * a.dstate;
+            cudaError_t e = a.initial_states ? cudaMemcpyAsync(a.final_states, a.initial_states, n, cudaMemcpyDeviceToDevice, stream)
+                                             : cudaMemsetAsync(a.final_states, 0, n, stream);
+            if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: final state copy: %s", cudaGetErrorString(e));
+        }
+        return MB200_OK;
+    }
+    MB200_CHECK_ARG(a.scratch && a.scratch_bytes >= lay.total, "ssd: scratch too small (%zu < %zu bytes)", a.scratch_bytes, lay.total);
+    MB200_CHECK_ARG((reinterpret_cast<uintptr_t>(a.scratch) & 255) == 0, "ssd: scratch must be 256-byte aligned");
+    if (a.io_dtype == MB200_F32) return run_ssd<float>(a, lay, stream);
+    if (a.io_dtype == MB200_BF16) return run_ssd<__nv_bfloat16>(a, lay, stream);
+    return run_ssd<__half>(a, lay, stream);
+}
+
+extern "C" int mb200_ssd_fold_state(const float *s_in, const float *range_decay, const float *s_local, float *s_out,
+                                    int64_t rows, int64_t row, int32_t device, void *stream)
+{
+    using namespace mb200;
+    MB200_CHECK_ARG(range_decay && s_local && s_out && rows >= 0 && row > 0, "ssd_fold_state: bad argument");
+    if (rows == 0) return MB200_OK;
+    if (int rc = enter_device(device)) return rc;
+    const int64_t total = rows * row;
+    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    ssd_fold_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(s_in, range_decay, s_local, s_out, rows, row);
+    MB200_CHECK_LAUNCH("ssd_fold_state");
+    return MB200_OK;
+}

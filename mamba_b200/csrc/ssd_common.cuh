@@ -1,0 +1,34 @@
+// Shared definitions of the SSD (Mamba-2) chunked forward: scratch layout and stage entry points.
+#pragma once
+
+#include "common.cuh"
+
+namespace mb200 {
+
+// Scratch the SSD stages hand to each other (all fp32, each region 256-byte aligned):
+//   dt      (batch, nheads, nchunks, Q)        dt after bias/softplus/clamp, 0 past seqlen
+//   dA_cum  (batch, nheads, nchunks, Q)        inclusive cumsum of dt*A inside each chunk
+//   states  (batch, nchunks, nheads, P, N)     chunk states; the inter-chunk recurrence then
+//                                              overwrites slot c with the state ENTERING chunk c
+//   cb      (batch, nchunks, ngroups, Q, Q)    C.B^T per chunk (lower block triangle only)
+struct SsdScratch {
+    size_t off_dt, off_dA, off_states, off_cb, total;
+    int nchunks;
+};
+
+inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+inline SsdScratch ssd_scratch_layout(const mb200_ssd_args &a)
+{
+    SsdScratch s;
+    s.nchunks = (a.seqlen + a.chunk_size - 1) / a.chunk_size;
+    const size_t per = (size_t)a.batch * a.nheads * s.nchunks * a.chunk_size * sizeof(float);
+    s.off_dt = 0;
+    s.off_dA = align256(s.off_dt + per);
+    s.off_states = align256(s.off_dA + per);
+    s.off_cb = align256(s.off_states + (size_t)a.batch * s.nchunks * a.nheads * a.headdim * a.dstate * sizeof(float));
+    s.total = align256(s.off_cb + (size_t)a.batch * s.nchunks * a.ngroups * a.chunk_size * a.chunk_size * sizeof(float));
+    return s;
+}
+
+}  // namespace mb200

@@ -1,0 +1,304 @@
+"""The three scan operators of state-spaces/mamba, served by libmamba_b200.so.
+
+Signatures, argument meaning, return values and error behaviour mirror the reference:
+
+* ``selective_scan_fn``          mamba_ssm/ops/selective_scan_interface.py:118-124 (forward of :36-68)
+* ``mamba_chunk_scan_combined``  mamba_ssm/ops/triton/ssd_combined.py:628-648 (forward :343-394)
+* ``selective_state_update``     mamba_ssm/ops/triton/selective_state_update.py:135-221
+
+Forward only (inference): the outputs carry no autograd graph.  PyTorch supplies device memory
+and the current stream; all arithmetic happens in the library's CUDA kernels.
+"""
+import ctypes
+import math
+
+import torch
+
+from . import _lib as L
+
+
+def _last_dim_contiguous(t):
+    return t if t is None or t.stride(-1) == 1 else t.contiguous()
+
+
+def _fp32(t):
+    return t if t is None or t.dtype == torch.float32 else t.float()
+
+
+# --------------------------------------------------------------------------------------- Mamba-1
+def selective_scan_fn(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus=False,
+                      return_last_state=False):
+    """Mamba-1 selective scan forward.
+
+    u, delta, z: (batch, dim, seqlen).  A: (dim, dstate) fp32.  B, C: (batch, dstate, seqlen),
+    (batch, ngroups, dstate, seqlen) or constant (dim, dstate).  D, delta_bias: (dim) fp32.
+    Returns ``out`` (gated by silu(z) when z is given) or ``(out, last_state)`` with
+    ``last_state`` (batch, dim, dstate) fp32.
+    """
+    L.require_cuda(u, delta, A, B, C, D, z, delta_bias)
+    if A.is_complex():
+        raise NotImplementedError("mamba_b200: complex A is not supported")
+    u, delta, z = _last_dim_contiguous(u), _last_dim_contiguous(delta), _last_dim_contiguous(z)
+    B, C = _last_dim_contiguous(B), _last_dim_contiguous(C)
+    D = None if D is None else _fp32(D).contiguous()
+    delta_bias = None if delta_bias is None else _fp32(delta_bias).contiguous()
+    A = _fp32(A)
+    assert u.dim() == 3 and delta.shape == u.shape, "u and delta must both be (batch, dim, seqlen)"
+    assert delta.dtype == u.dtype, "u and delta must have the same dtype"
+    batch, dim, seqlen = u.shape
+    assert A.dim() == 2 and A.shape[0] == dim, "A must be (dim, dstate)"
+    dstate = A.shape[1]
+    B_var, C_var = B.dim() >= 3, C.dim() >= 3
+    if B_var and B.dim() == 3:
+        B = B.unsqueeze(1)
+    if C_var and C.dim() == 3:
+        C = C.unsqueeze(1)
+    ngroups = B.shape[1] if B_var else (C.shape[1] if C_var else 1)
+    for name, t, var in (("B", B, B_var), ("C", C, C_var)):
+        if var:
+            assert t.shape == (batch, ngroups, dstate, seqlen), f"{name} must be (batch, ngroups, dstate, seqlen)"
+            assert t.dtype == u.dtype, f"variable {name} must have the dtype of u"
+        else:
+            assert t.shape == (dim, dstate), f"constant {name} must be (dim, dstate)"
+    if not B_var:
+        B = _fp32(B)
+    if not C_var:
+        C = _fp32(C)
+    if z is not None:
+        assert z.shape == u.shape and z.dtype == u.dtype, "z must match u"
+    if D is not None:
+        assert D.shape == (dim,)
+    if delta_bias is not None:
+        assert delta_bias.shape == (dim,)
+
+    out = torch.empty_like(delta)
+    last_state = torch.empty(batch, dim, dstate, device=u.device, dtype=torch.float32) if return_last_state else None
+
+    a = L.ScanArgs()
+    a.u, a.delta, a.A, a.B, a.C = L.ptr(u), L.ptr(delta), L.ptr(A), L.ptr(B), L.ptr(C)
+    a.D, a.z, a.delta_bias = L.ptr(D), L.ptr(z), L.ptr(delta_bias)
+    a.out, a.out_pregate, a.last_state = L.ptr(out), None, L.ptr(last_state)
+    a.batch, a.dim, a.seqlen, a.dstate, a.ngroups = batch, dim, seqlen, dstate, ngroups
+    a.io_dtype = L.dtype_code(u.dtype)
+    a.B_variable, a.C_variable, a.delta_softplus = int(B_var), int(C_var), int(bool(delta_softplus))
+    a.device = u.device.index
+    L.set_strides(a.u_stride, u, 2)
+    L.set_strides(a.delta_stride, delta, 2)
+    L.set_strides(a.out_stride, out, 2)
+    if z is not None:
+        L.set_strides(a.z_stride, z, 2)
+    L.set_strides(a.A_stride, A, 2)
+    L.set_strides(a.B_stride, B, 3 if B_var else 2)
+    L.set_strides(a.C_stride, C, 3 if C_var else 2)
+    L.check(L.lib().mb200_selective_scan_fwd(ctypes.byref(a), L.stream_ptr(u.device)))
+    return out if not return_last_state else (out, last_state)
+
+
+# --------------------------------------------------------------------------------------- decode
+def selective_state_update(state, x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus=False,
+                           state_batch_indices=None):
+    """Single-token decode update; ``state`` is modified in place.
+
+    state: (batch, dim, dstate) or (batch, nheads, dim, dstate); x, dt, z: (batch, dim) or
+    (batch, nheads, dim); A: (dim, dstate) or (nheads, dim, dstate); B, C: (batch, dstate) or
+    (batch, ngroups, dstate); D, dt_bias: (dim,) or (nheads, dim).  Stride-0 (broadcast) views of
+    A, dt, dt_bias and D are used as they are.  Returns out with the shape and dtype of x.
+    """
+    L.require_cuda(state, x, dt, A, B, C, D, z, dt_bias, state_batch_indices)
+    has_heads = state.dim() > 3
+    if state.dim() == 3:
+        state = state.unsqueeze(1)
+    if x.dim() == 2:
+        x = x.unsqueeze(1)
+    if dt.dim() == 2:
+        dt = dt.unsqueeze(1)
+    if A.dim() == 2:
+        A = A.unsqueeze(0)
+    if B.dim() == 2:
+        B = B.unsqueeze(1)
+    if C.dim() == 2:
+        C = C.unsqueeze(1)
+    if D is not None and D.dim() == 1:
+        D = D.unsqueeze(0)
+    if z is not None and z.dim() == 2:
+        z = z.unsqueeze(1)
+    if dt_bias is not None and dt_bias.dim() == 1:
+        dt_bias = dt_bias.unsqueeze(0)
+    _, nheads, dim, dstate = state.shape
+    batch = x.shape[0]
+    assert x.shape == (batch, nheads, dim)
+    assert dt.shape == x.shape
+    assert A.shape == (nheads, dim, dstate)
+    ngroups = B.shape[1]
+    assert nheads % ngroups == 0, "nheads must be divisible by ngroups"
+    assert B.shape == (batch, ngroups, dstate)
+    assert C.shape == B.shape and C.dtype == B.dtype
+    if D is not None:
+        assert D.shape == (nheads, dim)
+    if z is not None:
+        assert z.shape == x.shape and z.dtype == x.dtype
+    if dt_bias is not None:
+        assert dt_bias.shape == (nheads, dim)
+    if state_batch_indices is not None:
+        assert state_batch_indices.shape == (batch,)
+        if state_batch_indices.dtype != torch.int32:
+            state_batch_indices = state_batch_indices.to(torch.int32)
+        state_batch_indices = state_batch_indices.contiguous()
+    else:
+        assert state.shape[0] == batch
+    A, D, dt_bias = _fp32(A), _fp32(D), _fp32(dt_bias)
+    out = torch.empty_like(x)
+
+    a = L.SsuArgs()
+    a.state, a.x, a.dt, a.A, a.B, a.C = L.ptr(state), L.ptr(x), L.ptr(dt), L.ptr(A), L.ptr(B), L.ptr(C)
+    a.D, a.z, a.dt_bias, a.out = L.ptr(D), L.ptr(z), L.ptr(dt_bias), L.ptr(out)
+    a.state_batch_indices = L.ptr(state_batch_indices)
+    a.batch, a.nheads, a.dim, a.dstate, a.ngroups = batch, nheads, dim, dstate, ngroups
+    a.state_dtype, a.x_dtype = L.dtype_code(state.dtype), L.dtype_code(x.dtype)
+    a.dt_dtype, a.bc_dtype = L.dtype_code(dt.dtype), L.dtype_code(B.dtype)
+    a.dt_softplus = int(bool(dt_softplus))
+    a.device = x.device.index
+    L.set_strides(a.state_stride, state, 4)
+    L.set_strides(a.x_stride, x, 3)
+    L.set_strides(a.dt_stride, dt, 3)
+    L.set_strides(a.out_stride, out, 3)
+    L.set_strides(a.A_stride, A, 3)
+    L.set_strides(a.B_stride, B, 3)
+    L.set_strides(a.C_stride, C, 3)
+    if z is not None:
+        L.set_strides(a.z_stride, z, 3)
+    if D is not None:
+        L.set_strides(a.D_stride, D, 2)
+    if dt_bias is not None:
+        L.set_strides(a.dt_bias_stride, dt_bias, 2)
+    L.check(L.lib().mb200_selective_state_update(ctypes.byref(a), L.stream_ptr(x.device)))
+    return out if has_heads else out.squeeze(1)
+
+
+# --------------------------------------------------------------------------------------- SSD
+def _ssd_args(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit):
+    batch, seqlen, nheads, headdim = x.shape
+    _, _, ngroups, dstate = B.shape
+    assert nheads % ngroups == 0
+    assert B.shape == (batch, seqlen, ngroups, dstate)
+    assert dt.shape == (batch, seqlen, nheads)
+    assert A.shape == (nheads,)
+    assert C.shape == B.shape
+    assert B.dtype == x.dtype and C.dtype == x.dtype, "B and C must have the dtype of x"
+    if z is not None:
+        assert z.shape == x.shape and z.dtype == x.dtype
+    if D is not None:
+        assert D.shape == (nheads, headdim) or D.shape == (nheads,)
+    if seq_idx is not None:
+        assert seq_idx.shape == (batch, seqlen)
+    if initial_states is not None:
+        assert initial_states.shape == (batch, nheads, headdim, dstate)
+    a = L.SsdArgs()
+    a.batch, a.seqlen, a.nheads, a.headdim = batch, seqlen, nheads, headdim
+    a.ngroups, a.dstate, a.chunk_size = ngroups, dstate, int(chunk_size)
+    a.io_dtype, a.dt_dtype = L.dtype_code(x.dtype), L.dtype_code(dt.dtype)
+    a.dt_softplus = int(bool(dt_softplus))
+    a.D_has_hdim = int(D is not None and D.dim() == 2)
+    a.dt_min, a.dt_max = float(dt_limit[0]), min(float(dt_limit[1]), 3.0e38)
+    a.device = x.device.index
+    return a
+
+
+def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit,
+                phases, out=None, final_states=None, range_decay=None, scratch=None):
+    L.require_cuda(x, dt, A, B, C, D, z, dt_bias, initial_states, seq_idx)
+    B, C = _last_dim_contiguous(B), _last_dim_contiguous(C)
+    x, z = _last_dim_contiguous(x), _last_dim_contiguous(z)
+    A, dt_bias = _fp32(A).contiguous(), None if dt_bias is None else _fp32(dt_bias).contiguous()
+    D = None if D is None else _fp32(D).contiguous()
+    initial_states = None if initial_states is None else _fp32(initial_states).contiguous()
+    if seq_idx is not None:
+        seq_idx = seq_idx.to(torch.int32).contiguous()
+    a = _ssd_args(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit)
+    a.phases = phases
+    need = ctypes.c_size_t(0)
+    L.check(L.lib().mb200_ssd_scratch_bytes(ctypes.byref(a), ctypes.byref(need)))
+    if scratch is None:
+        scratch = torch.empty(max(need.value, 256), dtype=torch.uint8, device=x.device)
+    if out is None and phases & L.PHASE_OUTPUT:
+        out = torch.empty_like(x)
+    a.x, a.dt, a.A, a.B, a.C = L.ptr(x), L.ptr(dt), L.ptr(A), L.ptr(B), L.ptr(C)
+    a.D, a.z, a.dt_bias, a.seq_idx = L.ptr(D), L.ptr(z), L.ptr(dt_bias), L.ptr(seq_idx)
+    a.initial_states, a.out, a.final_states = L.ptr(initial_states), L.ptr(out), L.ptr(final_states)
+    a.range_decay, a.scratch, a.scratch_bytes = L.ptr(range_decay), L.ptr(scratch), scratch.numel()
+    L.set_strides(a.x_stride, x, 3)
+    L.set_strides(a.dt_stride, dt, 3)
+    L.set_strides(a.B_stride, B, 3)
+    L.set_strides(a.C_stride, C, 3)
+    if out is not None:
+        L.set_strides(a.out_stride, out, 3)
+    if z is not None:
+        L.set_strides(a.z_stride, z, 3)
+    L.check(L.lib().mb200_ssd_chunk_scan_fwd(ctypes.byref(a), L.stream_ptr(x.device)))
+    return out, scratch
+
+
+def mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
+                              seq_idx=None, cu_seqlens=None, dt_softplus=False, dt_limit=(0.0, float("inf")),
+                              return_final_states=False, return_varlen_states=False, state_dtype=None):
+    """Mamba-2 SSD chunked scan forward.
+
+    x, z: (batch, seqlen, nheads, headdim); dt: (batch, seqlen, nheads); A, dt_bias: (nheads);
+    B, C: (batch, seqlen, ngroups, dstate); D: (nheads,) or (nheads, headdim);
+    initial_states: (batch, nheads, headdim, dstate).
+    Returns ``out`` or ``(out, final_states)`` with final_states fp32 (batch, nheads, headdim, dstate).
+    Inter-chunk states are kept in fp32 whatever ``state_dtype`` asks for.
+    """
+    if return_varlen_states:
+        assert cu_seqlens is not None, "cu_seqlens must be provided if return_varlen_states is True"
+        raise NotImplementedError("mamba_b200: return_varlen_states is not supported yet")
+    batch, seqlen, nheads, headdim = x.shape
+    dstate = B.shape[-1]
+    final_states = (torch.empty(batch, nheads, headdim, dstate, device=x.device, dtype=torch.float32)
+                    if return_final_states else None)
+    out, _ = _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus,
+                         dt_limit, L.PHASE_ALL, final_states=final_states)
+    return out if not return_final_states else (out, final_states)
+
+
+def ssd_local_states(x, dt, A, B, chunk_size, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf"))):
+    """First half of a sequence-split SSD scan on this device's contiguous chunk range.
+
+    Returns ``(range_state, range_decay, scratch)``: the state at the end of the range given a zero
+    incoming state (batch, nheads, headdim, dstate) fp32, the product of the range's chunk decays
+    (batch, nheads) fp32, and the scratch buffer that ``ssd_finish`` must be handed back unchanged.
+    C does not enter this half; B doubles for it in the call.
+    """
+    batch, seqlen, nheads, headdim = x.shape
+    dstate = B.shape[-1]
+    range_state = torch.empty(batch, nheads, headdim, dstate, device=x.device, dtype=torch.float32)
+    range_decay = torch.empty(batch, nheads, device=x.device, dtype=torch.float32)
+    _, scratch = _ssd_launch(x, dt, A, B, B, chunk_size, None, None, dt_bias, None, None, dt_softplus, dt_limit,
+                             L.PHASE_LOCAL, final_states=range_state, range_decay=range_decay)
+    return range_state, range_decay, scratch
+
+
+def ssd_finish(x, dt, A, B, C, chunk_size, scratch, D=None, z=None, dt_bias=None, incoming_state=None,
+               dt_softplus=False, dt_limit=(0.0, float("inf")), return_final_states=False):
+    """Second half of a sequence-split SSD scan: inter-chunk recurrence from ``incoming_state`` and
+    the chunk outputs, reusing the scratch ``ssd_local_states`` filled."""
+    batch, seqlen, nheads, headdim = x.shape
+    dstate = B.shape[-1]
+    final_states = (torch.empty(batch, nheads, headdim, dstate, device=x.device, dtype=torch.float32)
+                    if return_final_states else None)
+    out, _ = _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, incoming_state, None, dt_softplus, dt_limit,
+                         L.PHASE_OUTPUT, final_states=final_states, scratch=scratch)
+    return out if not return_final_states else (out, final_states)
+
+
+def ssd_fold_state(incoming_state, range_decay, range_state):
+    """``range_decay[..., None, None] * incoming_state + range_state`` on the device (fp32)."""
+    L.require_cuda(range_decay, range_state, incoming_state)
+    out = torch.empty_like(range_state)
+    rows = range_decay.numel()
+    row = range_state.numel() // max(rows, 1)
+    s_in = None if incoming_state is None else incoming_state.contiguous()
+    L.check(L.lib().mb200_ssd_fold_state(L.ptr(s_in), L.ptr(range_decay.contiguous()), L.ptr(range_state.contiguous()),
+                                         L.ptr(out), rows, row, range_state.device.index,
+                                         L.stream_ptr(range_state.device)))
+    return out

@@ -1,0 +1,66 @@
+"""The C-ABI library loads and exports every symbol include/mamba_b200.h declares (no GPU needed)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def built():
+    from mamba_b200 import _build
+    return _build.build()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "mamba_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(built):
+    lib = ctypes.CDLL(built)
+    names = declared_symbols()
+    assert "mb200_selective_scan_fwd" in names and "mb200_ssd_chunk_scan_fwd" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/mamba_b200.h but not exported"
+
+
+def test_binding_covers_header(built):
+    from mamba_b200 import _lib
+    assert sorted(_lib.EXPORTED_SYMBOLS) == declared_symbols()
+    assert _lib.lib().mb200_version() >= 100
+
+
+def test_struct_sizes_match_header(built, tmp_path):
+    """ctypes mirrors must have the C compiler's layout of the argument structs."""
+    import subprocess
+    from mamba_b200 import _lib
+    src = tmp_path / "sz.c"
+    src.write_text('#include <stdio.h>\n#include "mamba_b200.h"\nint main(void){printf("%zu %zu %zu\\n",'
+                   'sizeof(mb200_scan_args),sizeof(mb200_ssu_args),sizeof(mb200_ssd_args));return 0;}\n')
+    exe = tmp_path / "sz"
+    subprocess.check_call(["/usr/bin/gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    sizes = [int(v) for v in subprocess.check_output([str(exe)]).split()]
+    assert sizes == [ctypes.sizeof(_lib.ScanArgs), ctypes.sizeof(_lib.SsuArgs), ctypes.sizeof(_lib.SsdArgs)]
+
+
+def test_argument_errors_without_gpu(built):
+    """Argument validation happens before any CUDA call, so it is testable on a CPU-only host."""
+    from mamba_b200 import _lib
+    a = _lib.ScanArgs()
+    rc = _lib.lib().mb200_selective_scan_fwd(ctypes.byref(a), None)
+    assert rc == _lib.ERR_BAD_ARG
+    assert b"NULL" in _lib.lib().mb200_last_error()
+    with pytest.raises(AssertionError):
+        _lib.check(rc)
+
+
+def test_cpu_tensors_are_rejected():
+    import torch
+    from mamba_b200 import selective_state_update
+    s = torch.zeros(1, 4, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        selective_state_update(s, torch.zeros(1, 4), torch.zeros(1, 4), torch.zeros(4, 8), torch.zeros(1, 8), torch.zeros(1, 8))

@@ -1,0 +1,209 @@
+"""GPU parity of the Mamba-1 selective scan (through the C ABI) against the golden vectors and the oracle."""
+import math
+
+import pytest
+import torch
+
+import oracle
+from helpers import TOL_BF16, TOL_FP32, assert_close, golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _fn():
+    from mamba_b200 import selective_scan_fn
+    return selective_scan_fn
+
+
+def _cuda(d, k, dtype=None):
+    t = d.get(k)
+    if t is None:
+        return None
+    t = t.to(DEV)
+    return t.to(dtype) if dtype is not None else t
+
+
+@pytest.mark.parametrize("name", golden_names("m1_"))
+def test_golden(name):
+    d = load_golden(name)
+    io = torch.bfloat16 if d["bf16"] else torch.float32
+    const_bc = d["B"].dim() == 2
+    out, last = _fn()(_cuda(d, "u", io), _cuda(d, "delta", io), _cuda(d, "A"),
+                      _cuda(d, "B", None if const_bc else io), _cuda(d, "C", None if const_bc else io),
+                      _cuda(d, "D"), _cuda(d, "z", io), _cuda(d, "delta_bias"), delta_softplus=True,
+                      return_last_state=True)
+    tol = TOL_BF16 if d["bf16"] else TOL_FP32
+    assert out.dtype == io and last.dtype == torch.float32
+    assert_close(out, d["out"], tol, name + " out")
+    assert_close(last, d["last_state"], tol, name + " last_state")
+
+
+def make_inputs(seed, batch, dim, L, N, groups, dtype, has_z=True, has_D=True, bench_style=False, const_b=False,
+                const_c=False):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    if bench_style:
+        A = -torch.exp(r(dim, N))
+        delta = r(batch, dim, L)
+        bias = -4 + 2 * torch.rand(dim, generator=g)
+    else:
+        A = -0.5 * torch.rand(dim, N, generator=g)
+        delta = 0.5 * torch.rand(batch, dim, L, generator=g)
+        bias = 0.5 * torch.rand(dim, generator=g)
+    u = r(batch, dim, L).to(dtype)
+    delta = delta.to(dtype)
+    B = r(dim, N) if const_b else r(batch, groups, N, L).to(dtype)
+    C = r(dim, N) if const_c else r(batch, groups, N, L).to(dtype)
+    D = r(dim) if has_D else None
+    z = r(batch, dim, L).to(dtype) if has_z else None
+    return dict(u=u, delta=delta, A=A, B=B, C=C, D=D, z=z, delta_bias=bias)
+
+
+def run_both(inp, tol, what):
+    want, want_last = oracle.selective_scan(inp["u"].float(), inp["delta"].float(), inp["A"], inp["B"].float(),
+                                            inp["C"].float(), inp["D"], None if inp["z"] is None else inp["z"].float(),
+                                            inp["delta_bias"], delta_softplus=True, return_last_state=True)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    got, got_last = _fn()(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], c["z"], c["delta_bias"],
+                          delta_softplus=True, return_last_state=True)
+    assert_close(got, want, tol, what + " out")
+    assert_close(got_last, want_last, tol, what + " last_state")
+    return got, got_last
+
+
+@pytest.mark.parametrize("L", [128, 256, 512, 1024, 2048, 4096, 372, 784, 1134, 1, 17])
+@pytest.mark.parametrize("groups", [1, 2])
+def test_reference_test_shapes_fp32(L, groups):
+    """batch 2, dim 4, dstate 8 and the sequence lengths of the reference's own scan test."""
+    run_both(make_inputs(100 + L, 2, 4, L, 8, groups, torch.float32), TOL_FP32, f"L{L} g{groups}")
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, TOL_BF16), (torch.float16, TOL_BF16)])
+@pytest.mark.parametrize("L", [512, 1000])
+def test_half_dtypes(dtype, tol, L):
+    run_both(make_inputs(7, 2, 24, L, 16, 1, dtype, bench_style=True), tol, f"{dtype} L{L}")
+
+
+@pytest.mark.parametrize("N", [1, 5, 16, 24, 64, 256])
+def test_state_sizes(N):
+    run_both(make_inputs(9 + N, 1, 20, 600, N, 2, torch.float32), TOL_FP32, f"N{N}")
+
+
+@pytest.mark.parametrize("const_b,const_c", [(True, True), (True, False), (False, True)])
+def test_constant_bc(const_b, const_c):
+    run_both(make_inputs(21, 2, 12, 300, 8, 1, torch.float32, const_b=const_b, const_c=const_c), TOL_FP32, "const B/C")
+
+
+def test_optional_tensors_absent():
+    inp = make_inputs(23, 2, 8, 200, 8, 1, torch.float32, has_z=False, has_D=False)
+    inp["delta_bias"] = None
+    want = oracle.selective_scan(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], delta_softplus=False)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    got = _fn()(c["u"], c["delta"], c["A"], c["B"], c["C"])
+    assert_close(got, want, TOL_FP32, "no D/z/bias")
+
+
+def test_bench_config0_full():
+    """batch 2, d_inner 256, seqlen 512, d_state 16, fp32: the CPU-runnable benchmark configuration."""
+    run_both(make_inputs(1000, 2, 256, 512, 16, 1, torch.float32, bench_style=True), TOL_FP32, "config 0")
+
+
+def test_strided_views_like_the_mixer():
+    """u and z as the two halves of one xz buffer and delta as a permuted view, as Mamba.forward passes
+    them (mamba_ssm/modules/mamba_simple.py:141-200); out inherits delta's strides."""
+    b, d, L, N = 2, 16, 256, 16
+    g = torch.Generator().manual_seed(3)
+    xz = torch.randn(b, 2 * d, L, generator=g).to(DEV)
+    u, z = xz.chunk(2, dim=1)
+    delta_flat = (0.5 * torch.rand(d, b * L, generator=g)).to(DEV)
+    delta = delta_flat.view(d, b, L).permute(1, 0, 2)
+    A = (-0.5 * torch.rand(d, N, generator=g)).to(DEV)
+    B = torch.randn(b, N, L, generator=g).to(DEV)
+    C = torch.randn(b, N, L, generator=g).to(DEV)
+    assert not delta.is_contiguous() and not u.is_contiguous()
+    got, last = _fn()(u, delta, A, B, C, None, z, None, delta_softplus=True, return_last_state=True)
+    assert got.stride() == delta.stride()
+    want, wl = oracle.selective_scan(u.cpu(), delta.cpu(), A.cpu(), B.cpu(), C.cpu(), None, z.cpu(), None,
+                                     delta_softplus=True, return_last_state=True)
+    assert_close(got, want, TOL_FP32, "strided out")
+    assert_close(last, wl, TOL_FP32, "strided last")
+
+
+def test_unaligned_rows_take_the_scalar_path():
+    inp = make_inputs(31, 1, 6, 333, 8, 1, torch.bfloat16)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    # shift every row by one element so no 16-byte packet is aligned
+    pad = lambda t: torch.cat([t.new_zeros(*t.shape[:-1], 1), t], dim=-1)[..., 1:]
+    got = _fn()(pad(c["u"]), pad(c["delta"]), c["A"], pad(c["B"]), pad(c["C"]), c["D"], pad(c["z"]), c["delta_bias"],
+                delta_softplus=True)
+    want = oracle.selective_scan(inp["u"].float(), inp["delta"].float(), inp["A"], inp["B"].float(), inp["C"].float(),
+                                 inp["D"], inp["z"].float(), inp["delta_bias"], delta_softplus=True)
+    assert_close(got, want, TOL_BF16, "unaligned")
+
+
+def test_softplus_threshold_and_large_decay():
+    """delta straddling the softplus threshold of 20 and strongly negative dt*A."""
+    inp = make_inputs(41, 1, 8, 64, 8, 1, torch.float32)
+    inp["delta"] = torch.linspace(-30, 30, 64).repeat(1, 8, 1).contiguous()
+    inp["delta_bias"] = None
+    inp["A"] = -torch.linspace(0.01, 40.0, 8).repeat(8, 1).contiguous()
+    run_both(inp, TOL_FP32, "softplus threshold")
+
+
+def test_errors_mirror_the_reference():
+    inp = make_inputs(51, 1, 4, 32, 8, 1, torch.float32)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    with pytest.raises(AssertionError, match="256"):
+        A_big = torch.zeros(4, 257, device=DEV)
+        _fn()(c["u"], c["delta"], A_big, torch.zeros(1, 1, 257, 32, device=DEV), torch.zeros(1, 1, 257, 32, device=DEV))
+    with pytest.raises(NotImplementedError):
+        _fn()(c["u"], c["delta"], torch.zeros(4, 8, dtype=torch.complex64, device=DEV), c["B"], c["C"])
+    with pytest.raises(AssertionError):
+        _fn()(c["u"], c["delta"].half(), c["A"], c["B"], c["C"])
+
+
+def test_empty_batch():
+    out = _fn()(torch.zeros(0, 4, 16, device=DEV), torch.zeros(0, 4, 16, device=DEV), torch.zeros(4, 8, device=DEV),
+                torch.zeros(0, 1, 8, 16, device=DEV), torch.zeros(0, 1, 8, 16, device=DEV))
+    assert out.shape == (0, 4, 16)
+
+
+def bench_config1_inputs(batch, dim, L=2048, N=16, seed=1001):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    u, delta, z = r(batch, dim, L).bfloat16(), r(batch, dim, L).bfloat16(), r(batch, dim, L).bfloat16()
+    A = -torch.exp(r(dim, N))
+    B, C = r(batch, 1, N, L).bfloat16(), r(batch, 1, N, L).bfloat16()
+    D = r(dim)
+    dt = torch.exp(torch.rand(dim, generator=g) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
+    bias = dt + torch.log(-torch.expm1(-dt))
+    return dict(u=u, delta=delta, A=A, B=B, C=C, D=D, z=z, delta_bias=bias)
+
+
+def test_bench_config1_slice_against_oracle():
+    """bf16 2.8B-layer shape (seqlen 2048, d_state 16) on 96 channels of 2 batch rows."""
+    run_both(bench_config1_inputs(2, 96), TOL_BF16, "config 1 slice")
+
+
+def test_bench_config1_full_size_properties():
+    """Full benchmark size (batch 8, d_inner 5120): a channel subset against the oracle, run-to-run
+    bit identity (the forward has no atomics), and linearity in u."""
+    inp = bench_config1_inputs(8, 5120)
+    c = {k: v.to(DEV) for k, v in inp.items()}
+    f = _fn()
+    args = (c["delta"], c["A"], c["B"], c["C"], c["D"], c["z"], c["delta_bias"])
+    out1, last1 = f(c["u"], *args, delta_softplus=True, return_last_state=True)
+    out2, last2 = f(c["u"], *args, delta_softplus=True, return_last_state=True)
+    assert torch.equal(out1, out2) and torch.equal(last1, last2)
+    sel = torch.arange(0, 5120, 97)
+    sub = {k: (v[:, sel] if k in ("u", "delta", "z") else (v[sel] if k in ("A", "D", "delta_bias") else v))
+           for k, v in inp.items()}
+    want, wl = oracle.selective_scan(sub["u"].float(), sub["delta"].float(), sub["A"], sub["B"].float(),
+                                     sub["C"].float(), sub["D"], sub["z"].float(), sub["delta_bias"],
+                                     delta_softplus=True, return_last_state=True)
+    assert_close(out1[:, sel.to(DEV)], want, TOL_BF16, "full-size subset out")
+    assert_close(last1[:, sel.to(DEV)], wl, TOL_BF16, "full-size subset last")
+    # linearity in u (D and the gate are linear in u too): f(2u) == 2 f(u) exactly up to bf16 rounding
+    out3 = f(2 * c["u"], *args, delta_softplus=True)
+    assert_close(out3, 2 * out1.float(), TOL_BF16, "linearity")

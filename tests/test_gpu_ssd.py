@@ -1,0 +1,182 @@
+"""GPU parity of the Mamba-2 SSD chunked scan (through the C ABI)."""
+import math
+
+import pytest
+import torch
+
+import oracle
+from helpers import TOL_BF16, TOL_FP32, assert_close, golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _fn():
+    from mamba_b200 import mamba_chunk_scan_combined
+    return mamba_chunk_scan_combined
+
+
+def _c(t, dtype=None):
+    if t is None:
+        return None
+    t = t.to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+@pytest.mark.parametrize("name", golden_names("ssd_"))
+def test_golden(name):
+    d = load_golden(name)
+    io = torch.bfloat16 if d["bf16"] else torch.float32
+    tol = TOL_BF16 if d["bf16"] else TOL_FP32
+    out, fin = _fn()(_c(d["x"], io), _c(d["dt"], io), _c(d["A"]), _c(d["B"], io), _c(d["C"], io), int(d["chunk_size"]),
+                     D=_c(d.get("D")), z=_c(d.get("z"), io), dt_bias=_c(d["dt_bias"]),
+                     initial_states=_c(d.get("initial_states")), dt_softplus=True, return_final_states=True)
+    assert out.dtype == io and fin.dtype == torch.float32
+    assert_close(out, d["out"], tol, name + " out")
+    assert_close(fin, d["final_states"], tol, name + " final_states")
+
+
+def make(seed, b, L, H, P, G, N, dtype, has_z=True, D_hdim=False, init=False):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    dtv = torch.exp(torch.rand(H, generator=g) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
+    return dict(x=r(b, L, H, P).to(dtype), dt=r(b, L, H).to(dtype), A=-(1 + 15 * torch.rand(H, generator=g)),
+                B=r(b, L, G, N).to(dtype), C=r(b, L, G, N).to(dtype), D=r(H, P) if D_hdim else r(H),
+                z=r(b, L, H, P).to(dtype) if has_z else None, dt_bias=dtv + torch.log(-torch.expm1(-dtv)),
+                initial_states=0.5 * r(b, H, P, N) if init else None)
+
+
+def run_both(inp, Q, tol, what, **kw):
+    f = lambda t: None if t is None else t.float()
+    want, wfin = oracle.ssd_chunk_scan(f(inp["x"]), f(inp["dt"]), inp["A"], f(inp["B"]), f(inp["C"]), Q, inp["D"], f(inp["z"]),
+                                       inp["dt_bias"], inp["initial_states"], dt_softplus=True, **kw)
+    c = {k: _c(v) for k, v in inp.items()}
+    got, fin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], z=c["z"], dt_bias=c["dt_bias"],
+                     initial_states=c["initial_states"], dt_softplus=True, return_final_states=True, **kw)
+    assert_close(got, want, tol, what + " out")
+    assert_close(fin, wfin, tol, what + " final_states")
+    return got, fin
+
+
+@pytest.mark.parametrize("P", [64, 128])
+def test_determinism_test_shapes(P):
+    """batch 2, seqlen 2048, 8 heads, dstate 64, chunk 256 (tests/test_determinism.py in the reference)."""
+    run_both(make(1, 2, 2048, 8, P, 1, 64, torch.float32), 256, TOL_FP32, f"P{P}")
+
+
+def test_ssd_minimal_shape():
+    """batch 1, seqlen 2048, chunk 64, 32 heads x 64, dstate 64 (modules/ssd_minimal.py in the reference)."""
+    run_both(make(2, 1, 2048, 32, 64, 1, 64, torch.float32, has_z=False), 64, TOL_FP32, "minimal")
+
+
+@pytest.mark.parametrize("L,Q", [(1, 64), (63, 64), (65, 64), (200, 64), (300, 128), (257, 256)])
+def test_ragged_lengths(L, Q):
+    run_both(make(3 + L, 2, L, 4, 16, 2, 16, torch.float32), Q, TOL_FP32, f"L{L} Q{Q}")
+
+
+@pytest.mark.parametrize("P,N,G,H", [(8, 8, 1, 3), (40, 24, 2, 6), (96, 80, 3, 3), (64, 128, 4, 8)])
+def test_odd_head_and_state_sizes(P, N, G, H):
+    run_both(make(9, 1, 192, H, P, G, N, torch.float32, D_hdim=True, init=True), 64, TOL_FP32, f"P{P} N{N}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_half_dtypes(dtype):
+    run_both(make(10, 2, 512, 4, 64, 1, 128, dtype), 256, TOL_BF16, str(dtype))
+
+
+def test_dt_limit_and_no_softplus():
+    inp = make(11, 1, 128, 2, 16, 1, 16, torch.float32)
+    inp["dt"] = inp["dt"].abs() * 0.1
+    inp["dt_bias"] = None
+    f = lambda t: None if t is None else t.float()
+    want, wfin = oracle.ssd_chunk_scan(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], 64, inp["D"], inp["z"], None, None,
+                                       dt_softplus=False, dt_limit=(0.01, 0.1))
+    c = {k: _c(v) for k, v in inp.items()}
+    got, fin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 64, D=c["D"], z=c["z"], dt_limit=(0.01, 0.1),
+                     return_final_states=True)
+    assert_close(got, want, TOL_FP32, "dt_limit out")
+    assert_close(fin, wfin, TOL_FP32, "dt_limit final")
+
+
+def test_strided_views_like_the_mixer():
+    """x, B, C as slices of one xBC buffer and z, dt as slices of zxbcdt (mamba_ssm/modules/mamba2.py:210-260)."""
+    b, L, H, P, G, N = 2, 256, 4, 32, 1, 64
+    g = torch.Generator().manual_seed(12)
+    xBC = torch.randn(b, L, H * P + 2 * G * N, generator=g).to(DEV)
+    zdt = torch.randn(b, L, H * P + H, generator=g).to(DEV)
+    x = xBC[..., :H * P].view(b, L, H, P)
+    B = xBC[..., H * P:H * P + G * N].view(b, L, G, N)
+    C = xBC[..., H * P + G * N:].view(b, L, G, N)
+    z = zdt[..., :H * P].view(b, L, H, P)
+    dt = zdt[..., H * P:]
+    A = -(1 + torch.rand(H, generator=g)).to(DEV)
+    D = torch.randn(H, generator=g).to(DEV)
+    bias = (torch.rand(H, generator=g) - 4).to(DEV)
+    assert not x.is_contiguous() and not dt.is_contiguous()
+    got, fin = _fn()(x, dt, A, B, C, 128, D=D, z=z, dt_bias=bias, dt_softplus=True, return_final_states=True)
+    want, wfin = oracle.ssd_chunk_scan(x.cpu(), dt.cpu(), A.cpu(), B.cpu(), C.cpu(), 128, D.cpu(), z.cpu(), bias.cpu(), None,
+                                       dt_softplus=True)
+    assert_close(got, want, TOL_FP32, "strided out")
+    assert_close(fin, wfin, TOL_FP32, "strided final")
+
+
+def test_prefill_state_continues_in_decode():
+    """final_states of a prefill over L tokens, advanced by one decode step, equals the prefill over
+    L+1 tokens: last output row and final state."""
+    from mamba_b200 import selective_state_update
+    b, L, H, P, G, N, Q = 2, 130, 4, 16, 2, 32, 64
+    inp = make(13, b, L + 1, H, P, G, N, torch.float32)
+    c = {k: _c(v) for k, v in inp.items()}
+    full, fin_full = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], z=c["z"], dt_bias=c["dt_bias"],
+                           dt_softplus=True, return_final_states=True)
+    part, fin = _fn()(c["x"][:, :L], c["dt"][:, :L], c["A"], c["B"][:, :L], c["C"][:, :L], Q, D=c["D"], z=c["z"][:, :L],
+                      dt_bias=c["dt_bias"], dt_softplus=True, return_final_states=True)
+    assert_close(part, full[:, :L], TOL_FP32, "prefix")
+    o = selective_state_update(fin, c["x"][:, L], c["dt"][:, L, :, None].expand(b, H, P), c["A"][:, None, None].expand(H, P, N),
+                               c["B"][:, L], c["C"][:, L], c["D"][:, None].expand(H, P), c["z"][:, L],
+                               c["dt_bias"][:, None].expand(H, P), dt_softplus=True)
+    assert_close(o, full[:, L], TOL_FP32, "decode token")
+    assert_close(fin, fin_full, TOL_FP32, "decode state")
+
+
+def test_sequence_split_in_two_ranges():
+    """The two-phase entry used when a sequence is split across devices: both ranges run LOCAL, the
+    first range's summary is folded and handed to the second, then both run OUTPUT.  Equal to one call."""
+    from mamba_b200 import ssd_finish, ssd_fold_state, ssd_local_states
+    b, L, H, P, G, N, Q = 1, 512, 4, 32, 2, 64, 64
+    inp = make(14, b, L, H, P, G, N, torch.float32, has_z=False)
+    c = {k: _c(v) for k, v in inp.items()}
+    whole, wfin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], dt_bias=c["dt_bias"], dt_softplus=True,
+                        return_final_states=True)
+    half = L // 2
+    sl = [slice(0, half), slice(half, L)]
+    loc = [ssd_local_states(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], Q, dt_bias=c["dt_bias"], dt_softplus=True)
+           for s in sl]
+    incoming = [None, ssd_fold_state(None, loc[0][1], loc[0][0])]
+    outs, fin = [], None
+    for r, s in enumerate(sl):
+        o, fin = ssd_finish(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], c["C"][:, s], Q, loc[r][2], D=c["D"],
+                            dt_bias=c["dt_bias"], incoming_state=incoming[r], dt_softplus=True, return_final_states=True)
+        outs.append(o)
+    assert_close(torch.cat(outs, dim=1), whole, TOL_FP32, "split out")
+    assert_close(fin, wfin, TOL_FP32, "split final")
+    assert_close(ssd_fold_state(incoming[1], loc[1][1], loc[1][0]), wfin, TOL_FP32, "folded summary")
+
+
+def test_unsupported_features_raise():
+    inp = make(15, 1, 64, 2, 8, 1, 8, torch.float32)
+    c = {k: _c(v) for k, v in inp.items()}
+    with pytest.raises(NotImplementedError):
+        _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 64, cu_seqlens=torch.tensor([0, 64], device=DEV),
+              return_varlen_states=True)
+    with pytest.raises(AssertionError):
+        _fn()(c["x"], c["dt"], c["A"][:1], c["B"], c["C"], 64)
+
+
+def bench_config2_inputs(b, H, L=4096, P=64, N=128, seed=1002):
+    return make(seed, b, L, H, P, 1, N, torch.bfloat16)
+
+
+def test_bench_config2_slice_against_oracle():
+    """bf16, seqlen 4096, headdim 64, dstate 128, chunk 256, one group: 1 batch row x 4 heads."""
+    run_both(bench_config2_inputs(1, 4), 256, TOL_BF16, "config 2 slice")
