@@ -306,7 +306,6 @@ extern "C" int mb200_selective_scan_fwd(const mb200_scan_args *args, void *strea
     if (!args) return fail(MB200_ERR_BAD_ARG, "selective_scan_fwd: args is NULL");
     const mb200_scan_args &a = *args;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    MB200_CHECK_ARG(a.u && a.delta && a.A && a.B && a.C && a.out, "selective_scan_fwd: a required tensor is NULL");
     MB200_CHECK_ARG(a.batch >= 0 && a.dim > 0 && a.seqlen >= 0 && a.dstate > 0 && a.ngroups > 0,
                     "selective_scan_fwd: bad sizes (batch %d dim %d seqlen %d dstate %d ngroups %d)", a.batch, a.dim,
                     a.seqlen, a.dstate, a.ngroups);
@@ -316,7 +315,8 @@ extern "C" int mb200_selective_scan_fwd(const mb200_scan_args *args, void *strea
                     "selective_scan_fwd: unknown io_dtype %d", a.io_dtype);
     MB200_CHECK_ARG(a.batch <= 65535, "selective_scan_fwd: batch must be <= 65535");
     MB200_CHECK_ARG(!a.out_pregate || a.z, "selective_scan_fwd: out_pregate is only meaningful with z");
-    if (a.batch == 0) return MB200_OK;
+    if (a.batch == 0) return MB200_OK;   // nothing to do; empty tensors carry NULL pointers
+    MB200_CHECK_ARG(a.u && a.delta && a.A && a.B && a.C && a.out, "selective_scan_fwd: a required tensor is NULL");
     if (int rc = enter_device(a.device)) return rc;
     if (a.seqlen == 0) {
         if (a.last_state) {

@@ -308,7 +308,6 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
 
 int check_ssd(const mb200_ssd_args &a)
 {
-    MB200_CHECK_ARG(a.x && a.dt && a.A && a.B && a.C, "ssd: a required tensor is NULL");
     MB200_CHECK_ARG(a.batch >= 0 && a.seqlen >= 0 && a.nheads > 0 && a.headdim > 0 && a.ngroups > 0 && a.dstate > 0 && a.chunk_size > 0,
                     "ssd: bad sizes (batch %d seqlen %d nheads %d headdim %d ngroups %d dstate %d chunk %d)", a.batch, a.seqlen,
                     a.nheads, a.headdim, a.ngroups, a.dstate, a.chunk_size);
@@ -341,7 +340,8 @@ extern "C" int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream
     if (int rc = check_ssd(a)) return rc;
     MB200_CHECK_ARG(!(a.phases & MB200_SSD_PHASE_OUTPUT) || a.out, "ssd: out is NULL");
     if (a.seq_idx) return fail(MB200_ERR_UNSUPPORTED, "ssd: seq_idx is not supported yet");
-    if (a.batch == 0) return MB200_OK;
+    if (a.batch == 0) return MB200_OK;   // nothing to do; empty tensors carry NULL pointers
+    MB200_CHECK_ARG(a.x && a.dt && a.A && a.B && a.C, "ssd: a required tensor is NULL");
     if (int rc = enter_device(a.device)) return rc;
     MB200_CHECK_ARG(a.batch * (int64_t)((a.seqlen + a.chunk_size - 1) / a.chunk_size) <= 65535 && a.nheads <= 65535 && a.batch <= 65535,
                     "ssd: batch*nchunks and nheads must be <= 65535");

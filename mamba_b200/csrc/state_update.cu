@@ -218,7 +218,6 @@ extern "C" int mb200_selective_state_update(const mb200_ssu_args *args, void *st
     if (!args) return fail(MB200_ERR_BAD_ARG, "selective_state_update: args is NULL");
     const mb200_ssu_args &a = *args;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    MB200_CHECK_ARG(a.state && a.x && a.dt && a.A && a.B && a.C && a.out, "selective_state_update: a required tensor is NULL");
     MB200_CHECK_ARG(a.batch >= 0 && a.nheads > 0 && a.dim > 0 && a.dstate > 0 && a.ngroups > 0,
                     "selective_state_update: sizes must be positive (batch %d nheads %d dim %d dstate %d ngroups %d)",
                     a.batch, a.nheads, a.dim, a.dstate, a.ngroups);
@@ -226,7 +225,8 @@ extern "C" int mb200_selective_state_update(const mb200_ssu_args *args, void *st
     MB200_CHECK_ARG(valid_dtype(a.state_dtype) && valid_dtype(a.x_dtype) && valid_dtype(a.dt_dtype) && valid_dtype(a.bc_dtype),
                     "selective_state_update: unknown dtype code");
     MB200_CHECK_ARG(a.batch <= 65535 && a.nheads <= 65535, "selective_state_update: batch and nheads must be <= 65535");
-    if (a.batch == 0) return MB200_OK;
+    if (a.batch == 0) return MB200_OK;   // nothing to do; empty tensors carry NULL pointers
+    MB200_CHECK_ARG(a.state && a.x && a.dt && a.A && a.B && a.C && a.out, "selective_state_update: a required tensor is NULL");
     if (int rc = enter_device(a.device)) return rc;
 
     const bool tied = a.A_stride[1] == 0 && a.A_stride[2] == 0 && a.dt_stride[2] == 0 &&
