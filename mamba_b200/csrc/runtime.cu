@@ -1,6 +1,7 @@
 // Host-side runtime of libmamba_b200: thread-local error text, device entry, version.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -48,6 +49,25 @@ int enter_device(int device)
 }
 
 int sm_count(int device) { return g_sm_count[device]; }
+
+bool debug_sync()
+{
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("MB200_DEBUG_SYNC");
+        on = (e && e[0] == '1') ? 1 : 0;
+    }
+    return on == 1;
+}
+
+void debug_after_launch(const char *what)
+{
+    fprintf(stderr, "[mb200] launched %s ...", what);
+    fflush(stderr);
+    const cudaError_t e = cudaDeviceSynchronize();
+    fprintf(stderr, " %s\n", e == cudaSuccess ? "done" : cudaGetErrorString(e));
+    fflush(stderr);
+}
 
 }  // namespace mb200
 

@@ -99,6 +99,17 @@ __device__ __forceinline__ void stage_rows(float *dst, const T *src, int64_t n_s
     }
 }
 
+// Pulls the 16-byte packets a lane will need for steps [t0, t0+kItems) of `row` into L1 ahead of use.
+template <typename T>
+__device__ __forceinline__ void prefetch_items(const T *row, int t0, int L)
+{
+    if (t0 < L) {
+        const char *p = reinterpret_cast<const char *>(row + t0);
+#pragma unroll
+        for (int o = 0; o < (int)(kItems * sizeof(T)); o += 32) asm volatile("prefetch.global.L1 [%0];" ::"l"(p + o));
+    }
+}
+
 __device__ __forceinline__ void read_items(const float *rowbase, int lane, float (&v)[kItems])
 {
     const float4 *r = reinterpret_cast<const float4 *>(rowbase);
@@ -161,12 +172,21 @@ scan_fwd_kernel(const mb200_scan_args a, const int cpw, const int nblocks, const
 #pragma unroll
                 for (int i = 0; i < kItems; ++i) {
                     float v = dl[i] + bias;
-                    if (a.delta_softplus) v = softplus20(v);
+                    if (a.delta_softplus) v = fast_softplus20(v);
                     if (t0 + i >= L) v = 0.f;
                     dl[i] = v;
                     sum_dt += v;
                     du[i] = v * uu[i];
                     y[i] = Dd * uu[i];
+                }
+                // while this channel's states are scanned, fetch what comes next: its own z row and
+                // the u / delta rows of the warp's next (channel, tile)
+                if (a.z) prefetch_items(static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)d * a.z_stride[1], t0, L);
+                const int dn = (c + 1 < cpw) ? d + 1 : d_first + warp * cpw;
+                const int tn = (c + 1 < cpw) ? t0 : t0 + kTile;
+                if (dn < d_end) {
+                    prefetch_items(static_cast<const T *>(a.u) + (int64_t)b * a.u_stride[0] + (int64_t)dn * a.u_stride[1], tn, L);
+                    prefetch_items(static_cast<const T *>(a.delta) + (int64_t)b * a.delta_stride[0] + (int64_t)dn * a.delta_stride[1], tn, L);
                 }
             }
             for (int nb = 0; nb < nblocks; ++nb) {

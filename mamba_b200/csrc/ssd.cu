@@ -137,8 +137,10 @@ __global__ void __launch_bounds__(kT) ssd_chunk_state_kernel(const mb200_ssd_arg
 
 // ---- stage 3 ------------------------------------------------------------------------------------
 // Elementwise over P*N, serial over chunks.  Slot c of `states` receives the state entering chunk c.
+// With `prev16` the entering states go there as 16-bit values (the tensor-core chunk_scan reads
+// them by TMA) and the fp32 slots are left alone.
 __global__ void __launch_bounds__(256) ssd_state_passing_kernel(const mb200_ssd_args a, const float *dAb, float *states,
-                                                                int nchunks, bool write_prev)
+                                                                int nchunks, bool write_prev, void *prev16)
 {
     const int64_t PN = (int64_t)a.headdim * a.dstate;
     const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -150,7 +152,10 @@ __global__ void __launch_bounds__(256) ssd_state_passing_kernel(const mb200_ssd_
         for (int c = 0; c < nchunks; ++c) {
             float *slot = states + (((int64_t)b * nchunks + c) * a.nheads + h) * PN + e;
             const float s = *slot;
-            if (write_prev) *slot = run;
+            if (write_prev) {
+                if (prev16) store_any(prev16, a.io_dtype, (((int64_t)b * nchunks + c) * a.nheads + h) * PN + e, run);
+                else *slot = run;
+            }
             run = fmaf(__expf(dA_last[(int64_t)c * Q]), run, s);
         }
         if (a.final_states) a.final_states[((int64_t)b * a.nheads + h) * PN + e] = run;
@@ -273,6 +278,12 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     float *cb = reinterpret_cast<float *>(base + lay.off_cb);
     const int nc = lay.nchunks, Q = a.chunk_size;
     const int64_t PN = (int64_t)a.headdim * a.dstate;
+    const bool tc = ssd_tc_eligible(a);
+    void *prev16 = tc ? static_cast<void *>(base + lay.off_prev16) : nullptr;
+    {
+        cudaError_t e = cudaMemsetAsync(base + lay.off_status, 0, sizeof(int), stream);
+        if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: status reset: %s", cudaGetErrorString(e));
+    }
     if (a.phases & MB200_SSD_PHASE_LOCAL) {
         const size_t cs_smem = sizeof(float) * Q * 33;
         if (cs_smem > 48 * 1024) {
@@ -281,27 +292,35 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         }
         ssd_cumsum_kernel<<<dim3(nc, a.batch, (a.nheads + 31) / 32), 256, cs_smem, stream>>>(a, dtb, dAb, nc);
         MB200_CHECK_LAUNCH("ssd chunk_cumsum");
-        ssd_chunk_state_kernel<T><<<dim3(((a.headdim + 63) / 64) * ((a.dstate + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(
-            a, dtb, dAb, states, nc);
-        MB200_CHECK_LAUNCH("ssd chunk_state");
+        if (tc) {
+            if (int rc = ssd_tc_chunk_state(a, lay, stream)) return rc;
+        } else {
+            ssd_chunk_state_kernel<T><<<dim3(((a.headdim + 63) / 64) * ((a.dstate + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(
+                a, dtb, dAb, states, nc);
+            MB200_CHECK_LAUNCH("ssd chunk_state");
+        }
         if (!(a.phases & MB200_SSD_PHASE_OUTPUT) && (a.final_states || a.range_decay)) {
             // range summary only: fold the local chunk states from a zero state, leave the slots as they are
             mb200_ssd_args z = a;
             z.initial_states = nullptr;
-            ssd_state_passing_kernel<<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(z, dAb, states, nc, false);
+            ssd_state_passing_kernel<<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(z, dAb, states, nc, false, nullptr);
             MB200_CHECK_LAUNCH("ssd range summary");
         }
     }
     if (a.phases & MB200_SSD_PHASE_OUTPUT) {
         mb200_ssd_args p = a;
         if (!(a.phases & MB200_SSD_PHASE_LOCAL)) p.range_decay = nullptr;
-        ssd_state_passing_kernel<<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true);
+        ssd_state_passing_kernel<<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
         MB200_CHECK_LAUNCH("ssd state_passing");
-        const int tq = (Q + 63) / 64;
-        ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);
-        MB200_CHECK_LAUNCH("ssd chunk_cb");
-        ssd_chunk_scan_kernel<T><<<dim3(tq * ((a.headdim + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(a, dtb, dAb, states, cb, nc);
-        MB200_CHECK_LAUNCH("ssd chunk_scan");
+        if (tc) {
+            if (int rc = ssd_tc_cb_and_scan(a, lay, stream)) return rc;
+        } else {
+            const int tq = (Q + 63) / 64;
+            ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);
+            MB200_CHECK_LAUNCH("ssd chunk_cb");
+            ssd_chunk_scan_kernel<T><<<dim3(tq * ((a.headdim + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(a, dtb, dAb, states, cb, nc);
+            MB200_CHECK_LAUNCH("ssd chunk_scan");
+        }
     }
     return MB200_OK;
 }

@@ -10,9 +10,13 @@ namespace mb200 {
 //   dA_cum  (batch, nheads, nchunks, Q)        inclusive cumsum of dt*A inside each chunk
 //   states  (batch, nchunks, nheads, P, N)     chunk states; the inter-chunk recurrence then
 //                                              overwrites slot c with the state ENTERING chunk c
-//   cb      (batch, nchunks, ngroups, Q, Q)    C.B^T per chunk (lower block triangle only)
+//   cb      (batch, nchunks, ngroups, Q, Q)    C.B^T per chunk (lower block triangle only); fp32 for the
+//                                              general kernels, 16-bit in the same region for the tensor-core ones
+//   prev16  (batch, nchunks, nheads, P, N)     16-bit copy of the state entering each chunk (tensor-core path)
+//   status  one int32 in the last 256 bytes    0 after a clean run; a kernel that gave up a bounded wait
+//                                              leaves its code here (the output is then invalid)
 struct SsdScratch {
-    size_t off_dt, off_dA, off_states, off_cb, total;
+    size_t off_dt, off_dA, off_states, off_cb, off_prev16, off_status, total;
     int nchunks;
 };
 
@@ -27,8 +31,15 @@ inline SsdScratch ssd_scratch_layout(const mb200_ssd_args &a)
     s.off_dA = align256(s.off_dt + per);
     s.off_states = align256(s.off_dA + per);
     s.off_cb = align256(s.off_states + (size_t)a.batch * s.nchunks * a.nheads * a.headdim * a.dstate * sizeof(float));
-    s.total = align256(s.off_cb + (size_t)a.batch * s.nchunks * a.ngroups * a.chunk_size * a.chunk_size * sizeof(float));
+    s.off_prev16 = align256(s.off_cb + (size_t)a.batch * s.nchunks * a.ngroups * a.chunk_size * a.chunk_size * sizeof(float));
+    s.off_status = align256(s.off_prev16 + (size_t)a.batch * s.nchunks * a.nheads * a.headdim * a.dstate * 2);
+    s.total = s.off_status + 256;
     return s;
 }
+
+// Tensor-core stages (ssd_tc.cu): whether the call qualifies, and the two launch groups.
+bool ssd_tc_eligible(const mb200_ssd_args &a);
+int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
+int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
 
 }  // namespace mb200

@@ -1,0 +1,577 @@
+// Tensor-core stages of the SSD chunked forward for sm_100a: tcgen05.mma with TMEM accumulators,
+// operands brought into 128-byte-swizzled shared memory by TMA (cp.async.bulk.tensor, no multicast).
+//
+// Shapes served here: 16-bit inputs (bf16 / fp16), headdim 64, dstate 128, chunk 256 -- the Mamba-2
+// production shape; anything else runs the general stage kernels.  Three kernels:
+//
+//   cb          CB[m,k] = C_m . B_k per (batch, chunk, group), one CTA per 128-row block, written as a
+//               16-bit [256 x 256] matrix (lower block triangle) that all heads of the group reuse from L2.
+//   chunk_state S^T[n,p] = sum_k (B[k,n] w_k) x[k,p], w_k = exp(min(dA_last - dA_k, 0)) dt_k.  The B chunk
+//               arrives by TMA, 128 threads scale its rows in place (fp32 math, one rounding), then one
+//               thread issues 16 MMAs (M=128 over n, N=64 over p, both operands MN-major).
+//   chunk_scan  per (batch, chunk, head, 128-row block):  Y1 = C . H^T (state entering the chunk),
+//               Y2 = (CB o L) . X with L[m,k] = exp(min(dA_m - dA_k, 0)) dt_k [k <= m] applied in place to
+//               the CB blocks as they land in a 3-slot ring; out = exp(dA_m) Y1 + Y2 + D x, gated by
+//               silu(z).  Y1 and Y2 live in 128 TMEM columns; two CTAs share an SM so one CTA's
+//               element-wise pass overlaps the other's loads and MMAs.
+//
+// Thread roles (160 threads): warps 0-3 own TMEM lanes 0-127 (one matrix row each) for the
+// element-wise work and the epilogue; warp 4 allocates TMEM and its lane 0 issues TMA and MMA.
+// Every mbarrier wait is bounded: on expiry the kernel records a code in the status word of the
+// scratch buffer, skips the dependent work and still releases its TMEM before it exits.
+#include "ssd_common.cuh"
+#include "tc_sm100.cuh"
+
+namespace mb200 {
+
+// ---- host: tensor-map encoding through the driver entry point ---------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static bool encode_16bit(CUtensorMap *map, int fmt, const void *base, int rank, const uint64_t *dims, const uint64_t *strides_bytes,
+                         const uint32_t *box)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t gd[5], gs[4];
+    cuuint32_t bx[5], es[5];
+    for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+    for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
+    const CUresult r = fn(map, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
+                          const_cast<void *>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+namespace {
+
+using namespace tc;
+
+constexpr int kQ = 256, kP = 64, kN = 128;
+constexpr int kThreadsTc = 160;
+
+// status codes written to the scratch status word
+enum { kStBarB = 11, kStBarX, kStBarScaled, kStBarDone, kStBarC, kStBarG1, kStBarFull, kStBarEmpty, kStBarG2 };
+
+template <typename T> struct Pack2;
+template <> struct Pack2<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 unpack(uint32_t v) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&v)); }
+    static __device__ __forceinline__ uint32_t pack(float a, float b)
+    {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+};
+template <> struct Pack2<__half> {
+    static __device__ __forceinline__ float2 unpack(uint32_t v) { return __half22float2(*reinterpret_cast<__half2 *>(&v)); }
+    static __device__ __forceinline__ uint32_t pack(float a, float b)
+    {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+};
+template <typename T> struct Fmt;
+template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
+template <> struct Fmt<__half> { static constexpr int v = 0; };
+
+__device__ __forceinline__ uint8_t *align1024(uint8_t *p)
+{
+    return reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// ====================================================================================== C . B^T
+// grid (ngroups, nchunks * 2, batch); CTA = rows [mb*128, mb*128+128) of one chunk against B rows
+// [0, (mb+1)*128).  smem: C 2 x 16 KB, B 2 x 32 KB.  TMEM: 256 columns.
+template <typename T>
+__global__ void __launch_bounds__(kThreadsTc) ssd_tc_cb_kernel(const __grid_constant__ CUtensorMap tm_C, const __grid_constant__ CUtensorMap tm_B,
+                                                              T *cb16, int nchunks, int ngroups, int *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *sm = align1024(smem_raw);
+    uint8_t *Cs = sm;               // 2 boxes [128 x 64]
+    uint8_t *Bs = sm + 32768;       // 2 boxes [256 x 64] (only (mb+1)*128 rows loaded)
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 32768 + 65536);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 4);
+    const int g = blockIdx.x, c = blockIdx.y >> 1, mb = blockIdx.y & 1, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ncols = (mb + 1) * 128;
+    if (threadIdx.x == 128) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_fence_init();
+    }
+    if (warp == 4) tmem_alloc(tmem_slot, 256);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_expect_tx(&bars[0], 32768 + 2 * ncols * 128);
+            for (int kb = 0; kb < 2; ++kb) {
+                tma_load_4d(Cs + kb * 16384, &tm_C, &bars[0], kb * 64, g, c * kQ + mb * 128, b);
+                for (int r = 0; r <= mb; ++r) tma_load_4d(Bs + kb * 32768 + r * 16384, &tm_B, &bars[0], kb * 64, g, c * kQ + r * 128, b);
+            }
+            if (mbar_wait(&bars[0], 0, status, kStBarC)) {
+                tc_fence_after_sync();
+                const uint32_t idesc = instr_desc_f16(128, ncols, Fmt<T>::v, 0, 0);
+                for (int kb = 0; kb < 2; ++kb)
+                    for (int s = 0; s < 4; ++s)
+                        mma_f16_ss(tmem, smem_desc_sw128(smem_u32(Cs + kb * 16384) + s * 32, 16, 1024),
+                                   smem_desc_sw128(smem_u32(Bs + kb * 32768) + s * 32, 16, 1024), idesc, (kb | s) != 0);
+            }
+            mma_commit(&bars[1]);
+        }
+    } else {
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(&bars[1], 0, status, kStBarDone));   // tcgen05.ld is warp-collective
+        tc_fence_after_sync();
+        const int m = mb * 128 + threadIdx.x;
+        T *row = cb16 + ((((int64_t)b * nchunks + c) * ngroups + g) * kQ + m) * kQ;
+        if (ok) {
+            for (int nb = 0; nb < ncols / 32; ++nb) {
+                float v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + nb * 32, v);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 o;
+                    o.x = Pack2<T>::pack(v[8 * q + 0], v[8 * q + 1]);
+                    o.y = Pack2<T>::pack(v[8 * q + 2], v[8 * q + 3]);
+                    o.z = Pack2<T>::pack(v[8 * q + 4], v[8 * q + 5]);
+                    o.w = Pack2<T>::pack(v[8 * q + 6], v[8 * q + 7]);
+                    *reinterpret_cast<uint4 *>(row + nb * 32 + q * 8) = o;
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem, 256);
+}
+
+// ====================================================================================== chunk state
+// grid (nheads, nchunks, batch).  smem: B 2 x 32 KB (n halves, [256 k x 64 n]), x 32 KB.  TMEM: 64 columns.
+template <typename T>
+__global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
+                                                                       const float *dtb, const float *dAb, float *states, int nchunks,
+                                                                       int nheads, int heads_per_group, int *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *sm = align1024(smem_raw);
+    uint8_t *Bs = sm;               // 2 boxes [256 x 64]
+    uint8_t *xs = sm + 65536;       // [256 x 64]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 98304);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 4);
+    const int h = blockIdx.x, c = blockIdx.y, b = blockIdx.z;
+    const int g = h / heads_per_group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 128) {
+        mbar_init(&bars[0], 1);      // B landed
+        mbar_init(&bars[1], 1);      // x landed
+        mbar_init(&bars[2], 128);    // B rows scaled
+        mbar_init(&bars[3], 1);      // MMAs done
+        mbar_fence_init();
+    }
+    if (warp == 4) tmem_alloc(tmem_slot, 64);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_expect_tx(&bars[0], 65536);
+            tma_load_4d(Bs, &tm_B, &bars[0], 0, g, c * kQ, b);
+            tma_load_4d(Bs + 32768, &tm_B, &bars[0], 64, g, c * kQ, b);
+            mbar_expect_tx(&bars[1], 32768);
+            tma_load_4d(xs, &tm_x, &bars[1], 0, h, c * kQ, b);
+            const bool ok = mbar_wait(&bars[2], 0, status, kStBarScaled) && mbar_wait(&bars[1], 0, status, kStBarX);
+            if (ok) {
+                tc_fence_after_sync();
+                const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 1, 1);
+                for (int s = 0; s < kQ / 16; ++s)
+                    mma_f16_ss(tmem, smem_desc_sw128(smem_u32(Bs) + s * 2048, 32768, 1024),
+                               smem_desc_sw128(smem_u32(xs) + s * 2048, 16, 1024), idesc, s != 0);
+            }
+            mma_commit(&bars[3]);
+        }
+    } else {
+        const float *dtc = dtb + (((int64_t)b * nheads + h) * nchunks + c) * kQ;
+        const float *dAc = dAb + (((int64_t)b * nheads + h) * nchunks + c) * kQ;
+        const float dA_last = dAc[kQ - 1];
+        float w[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int k = threadIdx.x + i * 128;
+            w[i] = __expf(fminf(dA_last - dAc[k], 0.f)) * dtc[k];
+        }
+        const bool ok = mbar_wait(&bars[0], 0, status, kStBarB);
+        if (ok) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int k = threadIdx.x + i * 128;
+#pragma unroll
+                for (int box = 0; box < 2; ++box) {
+                    const uint32_t base = smem_u32(Bs + box * 32768) + k * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        const uint32_t addr = base + ((ch ^ (k & 7)) << 4);
+                        uint4 v = lds128(addr);
+                        uint32_t *e = reinterpret_cast<uint32_t *>(&v);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = Pack2<T>::unpack(e[q]);
+                            e[q] = Pack2<T>::pack(f.x * w[i], f.y * w[i]);
+                        }
+                        sts128(addr, v);
+                    }
+                }
+            }
+        }
+        fence_proxy_async();
+        mbar_arrive(&bars[2]);
+        const bool done = mbar_wait(&bars[3], 0, status, kStBarDone);
+        tc_fence_after_sync();
+        if (__all_sync(0xffffffffu, ok && done)) {   // tcgen05.ld is warp-collective
+            float *S = states + (((int64_t)b * nchunks + c) * nheads + h) * (int64_t)(kP * kN);
+            const int n = threadIdx.x;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + half * 32, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) S[(half * 32 + j) * kN + n] = v[j];
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem, 64);
+}
+
+// ====================================================================================== chunk scan
+// grid (nheads, nchunks * 2, batch).  smem: x 32 KB | 48 KB region = {C 2 x 16 KB, H 2 x 8 KB}, reused as a
+// 3-slot ring of CB blocks once Y1 is done | dA*log2e, dt (2 KB) | barriers.  TMEM: 128 columns.
+template <typename T>
+__global__ void __launch_bounds__(kThreadsTc)
+ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_C,
+                         const __grid_constant__ CUtensorMap tm_H, const __grid_constant__ CUtensorMap tm_CB, const mb200_ssd_args a,
+                         const float *dtb, const float *dAb, int nchunks, int *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *sm = align1024(smem_raw);
+    uint8_t *xs = sm;                          // [256 x 64], rows k
+    uint8_t *R1 = sm + 32768;                  // 48 KB
+    float *dA2 = reinterpret_cast<float *>(sm + 81920);   // 256: dA_cumsum * log2(e)
+    float *dts = dA2 + 256;                               // 256
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 81920 + 2048);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    uint64_t *bar_c = &bars[0], *bar_x = &bars[1], *bar_g1 = &bars[2], *bar_g2 = &bars[3];
+    uint64_t *bar_full = &bars[4], *bar_scaled = &bars[7], *bar_empty = &bars[10];
+
+    const int h = blockIdx.x, c = blockIdx.y >> 1, mb = blockIdx.y & 1, b = blockIdx.z;
+    const int g = h / (a.nheads / a.ngroups);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nk = (mb + 1) * 2;   // 64-wide CB blocks this row block needs
+    if (threadIdx.x == 128) {
+        mbar_init(bar_c, 1);
+        mbar_init(bar_x, 1);
+        mbar_init(bar_g1, 1);
+        mbar_init(bar_g2, 1);
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&bar_full[i], 1);
+            mbar_init(&bar_scaled[i], 128);
+            mbar_init(&bar_empty[i], 1);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 4) tmem_alloc(tmem_slot, 128);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const int64_t unit_h = ((int64_t)b * nchunks + c) * a.nheads + h;
+    const int64_t unit_g = ((int64_t)b * nchunks + c) * a.ngroups + g;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(bar_c, 32768 + 16384);
+            for (int kb = 0; kb < 2; ++kb) {
+                tma_load_4d(R1 + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
+                tma_load_3d(R1 + 32768 + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
+            }
+            mbar_expect_tx(bar_x, (mb + 1) * 16384);
+            for (int r = 0; r <= mb; ++r) tma_load_4d(xs + r * 16384, &tm_x, bar_x, 0, h, c * kQ + r * 128, b);
+            // Y1 = C . H^T
+            ok = ok && mbar_wait(bar_c, 0, status, kStBarC);
+            if (ok) {
+                tc_fence_after_sync();
+                const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 0, 0);
+                for (int kb = 0; kb < 2; ++kb)
+                    for (int s = 0; s < 4; ++s)
+                        mma_f16_ss(tmem, smem_desc_sw128(smem_u32(R1 + kb * 16384) + s * 32, 16, 1024),
+                                   smem_desc_sw128(smem_u32(R1 + 32768 + kb * 8192) + s * 32, 16, 1024), idesc, (kb | s) != 0);
+            }
+            mma_commit(bar_g1);
+            ok = ok && mbar_wait(bar_g1, 0, status, kStBarG1);   // C / H no longer read: the region becomes the CB ring
+            if (ok) {
+                for (int j = 0; j < nk && j < 3; ++j) {
+                    mbar_expect_tx(&bar_full[j], 16384);
+                    tma_load_3d(R1 + j * 16384, &tm_CB, &bar_full[j], j * 64, mb * 128, (int)unit_g);
+                }
+            }
+            ok = ok && mbar_wait(bar_x, 0, status, kStBarX);
+            const uint32_t idesc2 = instr_desc_f16(128, 64, Fmt<T>::v, 0, 1);
+            for (int j = 0; j < nk; ++j) {
+                const int slot = j % 3;
+                ok = ok && mbar_wait(&bar_scaled[slot], (j / 3) & 1, status, kStBarScaled);
+                if (ok) {
+                    tc_fence_after_sync();
+                    for (int s = 0; s < 4; ++s)
+                        mma_f16_ss(tmem + 64, smem_desc_sw128(smem_u32(R1 + slot * 16384) + s * 32, 16, 1024),
+                                   smem_desc_sw128(smem_u32(xs) + (j * 64 + s * 16) * 128, 16, 1024), idesc2, (j | s) != 0);
+                }
+                mma_commit(&bar_empty[slot]);
+                if (j + 3 < nk) {
+                    ok = ok && mbar_wait(&bar_empty[slot], 0, status, kStBarEmpty);
+                    if (ok) {
+                        mbar_expect_tx(&bar_full[slot], 16384);
+                        tma_load_3d(R1 + slot * 16384, &tm_CB, &bar_full[slot], (j + 3) * 64, mb * 128, (int)unit_g);
+                    }
+                }
+            }
+            mma_commit(bar_g2);
+        }
+    } else {
+        const int r = threadIdx.x;          // row inside the block = TMEM lane
+        const int m = mb * 128 + r;         // row inside the chunk
+        const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
+        const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            dA2[r + i * 128] = dAc[r + i * 128] * kLog2e;
+            dts[r + i * 128] = dtc[r + i * 128];
+        }
+        compute_sync();
+        const float dAm = dA2[m];
+        bool ok = true;
+        for (int j = 0; j < nk; ++j) {
+            const int slot = j % 3;
+            const int k0 = j * 64;
+            ok = ok && mbar_wait(&bar_full[slot], (j / 3) & 1, status, kStBarFull);
+            const uint32_t rowaddr = smem_u32(R1 + slot * 16384) + r * 128;
+            if (ok) {
+                if (k0 > m) {
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) sts128(rowaddr + (ch << 4), make_uint4(0, 0, 0, 0));
+                } else {
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        const uint32_t addr = rowaddr + ((ch ^ (r & 7)) << 4);
+                        uint4 v = lds128(addr);
+                        uint32_t *e = reinterpret_cast<uint32_t *>(&v);
+                        const int kc = k0 + ch * 8;
+                        const float4 d0 = *reinterpret_cast<const float4 *>(dA2 + kc), d1 = *reinterpret_cast<const float4 *>(dA2 + kc + 4);
+                        const float4 t0 = *reinterpret_cast<const float4 *>(dts + kc), t1 = *reinterpret_cast<const float4 *>(dts + kc + 4);
+                        const float dk[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+                        const float tk[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = Pack2<T>::unpack(e[q]);
+                            const float l0 = (kc + 2 * q <= m) ? ex2(fminf(dAm - dk[2 * q], 0.f)) * tk[2 * q] : 0.f;
+                            const float l1 = (kc + 2 * q + 1 <= m) ? ex2(fminf(dAm - dk[2 * q + 1], 0.f)) * tk[2 * q + 1] : 0.f;
+                            e[q] = Pack2<T>::pack(f.x * l0, f.y * l1);
+                        }
+                        sts128(addr, v);
+                    }
+                }
+            }
+            fence_proxy_async();
+            mbar_arrive(&bar_scaled[slot]);
+        }
+        ok = ok && mbar_wait(bar_g2, 0, status, kStBarG2);
+        ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: the whole warp takes one path
+        tc_fence_after_sync();
+        const int t = c * kQ + m;
+        const bool live = t < a.seqlen;     // rows past the end of the sequence load TMEM with the warp but touch no memory
+        if (ok) {
+            const float scale = ex2(dAm);
+            const int tc_ = live ? t : 0;
+            const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)tc_ * a.z_stride[1] + (int64_t)h * a.z_stride[2] : nullptr;
+            T *orow = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)tc_ * a.out_stride[1] + (int64_t)h * a.out_stride[2];
+            const uint32_t xrow = smem_u32(xs) + m * 128;
+            const bool zo_vec = ((reinterpret_cast<uintptr_t>(orow) | reinterpret_cast<uintptr_t>(zrow)) & 15) == 0;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float y1[32], y2[32];
+                __syncwarp();   // rows past the end skipped the previous half's stores; rejoin before the collective load
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + half * 32, y1);
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + 64 + half * 32, y2);
+                if (!live) continue;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int p0 = half * 32 + q4 * 8;
+                    float y[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) y[i] = fmaf(scale, y1[q4 * 8 + i], y2[q4 * 8 + i]);
+                    if (a.D) {
+                        const uint4 xv = lds128(xrow + ((((p0 >> 3)) ^ (m & 7)) << 4));
+                        const uint32_t *xe = reinterpret_cast<const uint32_t *>(&xv);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = Pack2<T>::unpack(xe[q]);
+                            const float D0 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q] : a.D[h];
+                            const float D1 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q + 1] : D0;
+                            y[2 * q] = fmaf(f.x, D0, y[2 * q]);
+                            y[2 * q + 1] = fmaf(f.y, D1, y[2 * q + 1]);
+                        }
+                    }
+                    if (zrow) {
+                        if (zo_vec) {
+                            const uint4 zv = *reinterpret_cast<const uint4 *>(zrow + p0);
+                            const uint32_t *ze = reinterpret_cast<const uint32_t *>(&zv);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float2 f = Pack2<T>::unpack(ze[q]);
+                                y[2 * q] *= fast_silu(f.x);
+                                y[2 * q + 1] *= fast_silu(f.y);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) y[i] *= fast_silu(to_float(zrow[p0 + i]));
+                        }
+                    }
+                    if (zo_vec) {
+                        uint4 o;
+                        o.x = Pack2<T>::pack(y[0], y[1]);
+                        o.y = Pack2<T>::pack(y[2], y[3]);
+                        o.z = Pack2<T>::pack(y[4], y[5]);
+                        o.w = Pack2<T>::pack(y[6], y[7]);
+                        *reinterpret_cast<uint4 *>(orow + p0) = o;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) orow[p0 + i] = from_float<T>(y[i]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem, 128);
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+bool mult8(const int64_t *s, int n)
+{
+    for (int i = 0; i < n; ++i)
+        if (s[i] % 8) return false;
+    return true;
+}
+
+struct TcMaps {
+    CUtensorMap x, B, C, H, CB;
+};
+
+template <typename T>
+int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream_t stream)
+{
+    char *base = static_cast<char *>(a.scratch);
+    float *dtb = reinterpret_cast<float *>(base + lay.off_dt);
+    float *dAb = reinterpret_cast<float *>(base + lay.off_dA);
+    float *states = reinterpret_cast<float *>(base + lay.off_states);
+    T *cb16 = reinterpret_cast<T *>(base + lay.off_cb);
+    T *prev16 = reinterpret_cast<T *>(base + lay.off_prev16);
+    int *status = reinterpret_cast<int *>(base + lay.off_status);
+    const int nc = lay.nchunks, fmt = Fmt<T>::v;
+    const uint64_t L = a.seqlen;
+    CUtensorMap tx, tB, tC, tH, tCB;
+    {
+        const uint64_t d[4] = {(uint64_t)kP, (uint64_t)a.nheads, L, (uint64_t)a.batch};
+        const uint64_t s[3] = {(uint64_t)a.x_stride[2] * 2, (uint64_t)a.x_stride[1] * 2, (uint64_t)a.x_stride[0] * 2};
+        const uint32_t bx256[4] = {64, 1, 256, 1}, bx128[4] = {64, 1, 128, 1};
+        if (!encode_16bit(&tx, fmt, a.x, 4, d, s, stage == 0 ? bx256 : bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for x failed");
+    }
+    {
+        const uint64_t d[4] = {(uint64_t)kN, (uint64_t)a.ngroups, L, (uint64_t)a.batch};
+        const uint64_t sB[3] = {(uint64_t)a.B_stride[2] * 2, (uint64_t)a.B_stride[1] * 2, (uint64_t)a.B_stride[0] * 2};
+        const uint64_t sC[3] = {(uint64_t)a.C_stride[2] * 2, (uint64_t)a.C_stride[1] * 2, (uint64_t)a.C_stride[0] * 2};
+        const uint32_t bx256[4] = {64, 1, 256, 1}, bx128[4] = {64, 1, 128, 1};
+        if (!encode_16bit(&tB, fmt, a.B, 4, d, sB, stage == 0 ? bx256 : bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for B failed");
+        if (!encode_16bit(&tC, fmt, a.C, 4, d, sC, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for C failed");
+    }
+    const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = 81920 + 2048 + 256 + 1024;
+    if (stage == 0) {
+        cudaFuncSetAttribute(ssd_tc_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state);
+        ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kThreadsTc, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
+                                                                                                   a.nheads / a.ngroups, status);
+        MB200_CHECK_LAUNCH("ssd chunk_state (tensor core)");
+        return MB200_OK;
+    }
+    {
+        const uint64_t d[3] = {(uint64_t)kN, (uint64_t)kP, (uint64_t)a.batch * nc * a.nheads};
+        const uint64_t s[2] = {(uint64_t)kN * 2, (uint64_t)kN * kP * 2};
+        const uint32_t bx[3] = {64, 64, 1};
+        if (!encode_16bit(&tH, fmt, prev16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for states failed");
+    }
+    {
+        const uint64_t d[3] = {(uint64_t)kQ, (uint64_t)kQ, (uint64_t)a.batch * nc * a.ngroups};
+        const uint64_t s[2] = {(uint64_t)kQ * 2, (uint64_t)kQ * kQ * 2};
+        const uint32_t bx[3] = {64, 128, 1};
+        if (!encode_16bit(&tCB, fmt, cb16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for CB failed");
+    }
+    cudaFuncSetAttribute(ssd_tc_cb_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cb);
+    ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
+    MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
+    cudaFuncSetAttribute(ssd_tc_chunk_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scan);
+    ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kThreadsTc, smem_scan, stream>>>(tx, tC, tH, tCB, a, dtb, dAb, nc, status);
+    MB200_CHECK_LAUNCH("ssd chunk_scan (tensor core)");
+    return MB200_OK;
+}
+
+}  // namespace
+
+bool ssd_tc_eligible(const mb200_ssd_args &a)
+{
+    if (a.io_dtype != MB200_BF16 && a.io_dtype != MB200_F16) return false;
+    if (a.headdim != kP || a.dstate != kN || a.chunk_size != kQ || a.seq_idx) return false;
+    if (!aligned16(a.x) || !aligned16(a.B) || !aligned16(a.C)) return false;
+    if (!mult8(a.x_stride, 3) || !mult8(a.B_stride, 3) || !mult8(a.C_stride, 3)) return false;
+    if ((int64_t)a.batch * ((a.seqlen + kQ - 1) / kQ) * a.nheads > INT32_MAX) return false;
+    return encode_fn() != nullptr;
+}
+
+int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
+{
+    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 0, stream) : run_tc<__half>(a, lay, 0, stream);
+}
+
+int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
+{
+    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 1, stream) : run_tc<__half>(a, lay, 1, stream);
+}
+
+}  // namespace mb200

@@ -13,7 +13,7 @@ namespace mb200 {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kRowsInFlight = 4;
+constexpr int kRowsInFlight = 8;
 
 // out rows of a padding entry (state_batch_indices < 0) are defined to be zero.
 __device__ void zero_rows(const mb200_ssu_args &a, int b, int h, int p0, int rows)
@@ -49,6 +49,22 @@ __global__ void __launch_bounds__(kThreads) ssu_packet_kernel(const mb200_ssu_ar
     const int64_t zo = (int64_t)b * a.z_stride[0] + (int64_t)h * a.z_stride[1];
     const int64_t oo = (int64_t)b * a.out_stride[0] + (int64_t)h * a.out_stride[1];
 
+    // The state rows are the only real traffic: put the first round of packets in flight before
+    // the (latency-bound) per-(batch, head) set-up below.
+    Vec16<StateT> pk[kRowsInFlight][NC];
+    auto load_round = [&](int r0) {
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) {
+            const int r = r0 + u * GROUPS;
+            if (r < rows) {
+                StateT *row = state + (int64_t)(p0 + r) * a.state_stride[2];
+#pragma unroll
+                for (int c = 0; c < NC; ++c) pk[u][c].load(row + (c * LPR + lir) * VEC);
+            }
+        }
+    };
+    load_round(group);
+
     float Bv[NC][VEC], Cv[NC][VEC];
 #pragma unroll
     for (int c = 0; c < NC; ++c)
@@ -74,16 +90,7 @@ __global__ void __launch_bounds__(kThreads) ssu_packet_kernel(const mb200_ssu_ar
     // every thread runs the same number of rounds (the shuffles below need whole warps)
     for (int base = 0; base < rows; base += GROUPS * kRowsInFlight) {
         const int r0 = base + group;
-        Vec16<StateT> pk[kRowsInFlight][NC];
-#pragma unroll
-        for (int u = 0; u < kRowsInFlight; ++u) {
-            const int r = r0 + u * GROUPS;
-            if (r < rows) {
-                StateT *row = state + (int64_t)(p0 + r) * a.state_stride[2];
-#pragma unroll
-                for (int c = 0; c < NC; ++c) pk[u][c].load(row + (c * LPR + lir) * VEC);
-            }
-        }
+        if (base > 0) load_round(r0);
 #pragma unroll
         for (int u = 0; u < kRowsInFlight; ++u) {
             const int r = r0 + u * GROUPS;

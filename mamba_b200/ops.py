@@ -204,6 +204,20 @@ def _ssd_args(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx
     return a
 
 
+_last_ssd_scratch = None
+
+
+def ssd_status():
+    """Status word of the most recent SSD call on this process (synchronises the device).
+
+    0 means every kernel ran to completion.  A non-zero value means a kernel abandoned one of its
+    bounded waits (its code is the value) and the outputs of that call must not be used.  Meant for
+    tests and debugging; the operators themselves never synchronise."""
+    if _last_ssd_scratch is None:
+        return 0
+    return int(_last_ssd_scratch[-256:-252].view(torch.int32).item())
+
+
 def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit,
                 phases, out=None, final_states=None, range_decay=None, scratch=None):
     L.require_cuda(x, dt, A, B, C, D, z, dt_bias, initial_states, seq_idx)
@@ -235,6 +249,8 @@ def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_i
     if z is not None:
         L.set_strides(a.z_stride, z, 3)
     L.check(L.lib().mb200_ssd_chunk_scan_fwd(ctypes.byref(a), L.stream_ptr(x.device)))
+    global _last_ssd_scratch
+    _last_ssd_scratch = scratch
     return out, scratch
 
 

@@ -16,6 +16,11 @@ def _fn():
     return mamba_chunk_scan_combined
 
 
+def _status():
+    from mamba_b200 import ops
+    return ops.ssd_status()
+
+
 def _c(t, dtype=None):
     if t is None:
         return None
@@ -32,6 +37,7 @@ def test_golden(name):
                      D=_c(d.get("D")), z=_c(d.get("z"), io), dt_bias=_c(d["dt_bias"]),
                      initial_states=_c(d.get("initial_states")), dt_softplus=True, return_final_states=True)
     assert out.dtype == io and fin.dtype == torch.float32
+    assert _status() == 0
     assert_close(out, d["out"], tol, name + " out")
     assert_close(fin, d["final_states"], tol, name + " final_states")
 
@@ -53,6 +59,7 @@ def run_both(inp, Q, tol, what, **kw):
     c = {k: _c(v) for k, v in inp.items()}
     got, fin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], z=c["z"], dt_bias=c["dt_bias"],
                      initial_states=c["initial_states"], dt_softplus=True, return_final_states=True, **kw)
+    assert _status() == 0, f"a kernel gave up a bounded wait (code {_status()})"
     assert_close(got, want, tol, what + " out")
     assert_close(fin, wfin, tol, what + " final_states")
     return got, fin
@@ -82,6 +89,16 @@ def test_odd_head_and_state_sizes(P, N, G, H):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_half_dtypes(dtype):
     run_both(make(10, 2, 512, 4, 64, 1, 128, dtype), 256, TOL_BF16, str(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("L,G,H,init,D_hdim,has_z", [(256, 1, 2, False, False, True), (1024, 2, 4, True, True, False),
+                                                       (700, 1, 3, True, False, True), (100, 1, 1, False, False, True)])
+def test_tensor_core_shapes(dtype, L, G, H, init, D_hdim, has_z):
+    """headdim 64, dstate 128, chunk 256, 16-bit inputs: the shapes the tcgen05 kernels serve, with ragged
+    tails, several groups, initial states and both D layouts."""
+    run_both(make(40 + L, 2, L, H, 64, G, 128, dtype, has_z=has_z, D_hdim=D_hdim, init=init), 256, TOL_BF16,
+             f"tc L{L} G{G} H{H}")
 
 
 def test_dt_limit_and_no_softplus():
