@@ -12,6 +12,8 @@
 // The state carried between tiles lives in shared memory (one float per channel and state), so any
 // dstate <= 256 works; states are processed in blocks of kStateBlock with B/C re-staged per block.
 // Steps past seqlen get dt = 0, u = 0, i.e. the identity (1, 0), so the final state is exact.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace mb200 {
@@ -278,6 +280,189 @@ scan_fwd_kernel(const mb200_scan_args a, const int cpw, const int nblocks, const
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Channel-parallel variant for dstate <= 16 with input-dependent B and C: one lane per channel, time
+// sequential.  All 32 lanes of a warp are at the same step, so B_t and C_t are warp-uniform
+// (broadcast reads of a tiny per-warp shared tile) and the only loop-carried dependence is the one
+// FMA per state; there is no scan tree and no re-evaluation, i.e. 4 FMA-pipe + 1 MUFU instruction
+// per (step, state).  Each lane streams its own row 32 bytes at a time (whole sectors), one block
+// ahead of use; warps never synchronise with each other, so a CTA is a single warp and the grid
+// spreads evenly over the SMs.
+constexpr int kSeqBytes = 32;   // bytes of one row a lane moves per block (two 16-byte packets)
+
+template <typename T> struct SeqRaw { uint4 v[2]; };
+
+template <typename T>
+__device__ __forceinline__ float seq_get(const SeqRaw<T> &r, int i)
+{
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(r.v);
+    if constexpr (sizeof(T) == 4) {
+        return __uint_as_float(w[i]);
+    } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        const uint32_t x = w[i >> 1];
+        return __uint_as_float((i & 1) ? (x & 0xffff0000u) : (x << 16));
+    } else {
+        const uint32_t x = w[i >> 1];
+        return __half2float(__ushort_as_half((unsigned short)((i & 1) ? (x >> 16) : (x & 0xffffu))));
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ SeqRaw<T> seq_load(const T *row, int t0, int L, bool vec_ok)
+{
+    constexpr int TB = kSeqBytes / sizeof(T);
+    SeqRaw<T> r;
+    if (vec_ok && t0 + TB <= L) {
+        r.v[0] = __ldg(reinterpret_cast<const uint4 *>(row + t0));
+        r.v[1] = __ldg(reinterpret_cast<const uint4 *>(row + t0) + 1);
+    } else {
+        T *e = reinterpret_cast<T *>(r.v);
+#pragma unroll
+        for (int i = 0; i < TB; ++i) e[i] = (t0 + i < L) ? row[t0 + i] : from_float<T>(0.f);
+    }
+    return r;
+}
+
+template <typename T, int NS>
+__global__ void __launch_bounds__(32) scan_seq_kernel(const mb200_scan_args a, const int vec_flags)
+{
+    constexpr int TB = kSeqBytes / sizeof(T);          // steps per block: 16 (16-bit) or 8 (fp32)
+    __shared__ __align__(16) float Bs[TB * NS], Cs[TB * NS];
+    const int lane = threadIdx.x;
+    const int N = a.dstate, L = a.seqlen;
+    const int per_group = a.dim / a.ngroups;
+    const int blocks_per_group = (per_group + 31) / 32;
+    const int b = blockIdx.y;
+    const int g = blockIdx.x / blocks_per_group;
+    const int d = g * per_group + (blockIdx.x % blocks_per_group) * 32 + lane;
+    const bool live = d < (g + 1) * per_group;
+    const int dc = live ? d : g * per_group;            // idle lanes shadow a valid channel, store nothing
+    const bool io_vec = vec_flags & 1, bc_vec = vec_flags & 2;
+
+    float A2[NS], h[NS];
+#pragma unroll
+    for (int n = 0; n < NS; ++n) {
+        A2[n] = n < N ? a.A[(int64_t)dc * a.A_stride[0] + (int64_t)n * a.A_stride[1]] * kLog2e : 0.f;
+        h[n] = 0.f;
+    }
+    const float bias = a.delta_bias ? a.delta_bias[dc] : 0.f;
+    const float Dd = a.D ? a.D[dc] : 0.f;
+    const T *urow = static_cast<const T *>(a.u) + (int64_t)b * a.u_stride[0] + (int64_t)dc * a.u_stride[1];
+    const T *drow = static_cast<const T *>(a.delta) + (int64_t)b * a.delta_stride[0] + (int64_t)dc * a.delta_stride[1];
+    const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)dc * a.z_stride[1] : nullptr;
+    T *orow = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)dc * a.out_stride[1];
+    T *prow = (a.z && a.out_pregate) ? static_cast<T *>(a.out_pregate) + (int64_t)b * a.pregate_stride[0] + (int64_t)dc * a.pregate_stride[1] : nullptr;
+
+    // B/C staging: the block's tile is N rows x 32 bytes = N x 2 packets; lane -> (row lane/2, packet lane%2)
+    const int sn = lane >> 1, sh = lane & 1;
+    const T *Bsrc = static_cast<const T *>(a.B) + (int64_t)b * a.B_stride[0] + (int64_t)g * a.B_stride[1] + (int64_t)sn * a.B_stride[2];
+    const T *Csrc = static_cast<const T *>(a.C) + (int64_t)b * a.C_stride[0] + (int64_t)g * a.C_stride[1] + (int64_t)sn * a.C_stride[2];
+    constexpr int HP = TB / 2;                          // steps per packet
+    auto bc_load = [&](const T *src, int t0) {
+        uint4 r = make_uint4(0, 0, 0, 0);
+        if (sn < N) {
+            const int ts = t0 + sh * HP;
+            if (bc_vec && ts + HP <= L) {
+                r = __ldg(reinterpret_cast<const uint4 *>(src + ts));
+            } else {
+                T *e = reinterpret_cast<T *>(&r);
+#pragma unroll
+                for (int i = 0; i < HP; ++i) e[i] = (ts + i < L) ? src[ts + i] : from_float<T>(0.f);
+            }
+        }
+        return r;
+    };
+    auto bc_store = [&](float *dst, const uint4 &r) {
+        if (sn < NS) {
+            const T *e = reinterpret_cast<const T *>(&r);
+#pragma unroll
+            for (int i = 0; i < HP; ++i) dst[(sh * HP + i) * NS + sn] = to_float(e[i]);
+        }
+    };
+
+    const int nblk = (L + TB - 1) / TB;
+    SeqRaw<T> ru = seq_load(urow, 0, L, io_vec), rd = seq_load(drow, 0, L, io_vec), rz;
+    if (zrow) rz = seq_load(zrow, 0, L, io_vec);
+    {
+        const uint4 b0 = bc_load(Bsrc, 0), c0 = bc_load(Csrc, 0);
+        bc_store(Bs, b0);
+        bc_store(Cs, c0);
+    }
+    __syncwarp();
+    for (int blk = 0; blk < nblk; ++blk) {
+        const int t0 = blk * TB;
+        // next block's operands are requested before this block's arithmetic
+        SeqRaw<T> nu, nd, nz;
+        uint4 nb = make_uint4(0, 0, 0, 0), ncc = make_uint4(0, 0, 0, 0);
+        const bool more = blk + 1 < nblk;
+        if (more) {
+            nu = seq_load(urow, t0 + TB, L, io_vec);
+            nd = seq_load(drow, t0 + TB, L, io_vec);
+            if (zrow) nz = seq_load(zrow, t0 + TB, L, io_vec);
+            nb = bc_load(Bsrc, t0 + TB);
+            ncc = bc_load(Csrc, t0 + TB);
+        }
+        float yo[TB], yp[TB];
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+            const float uu = seq_get<T>(ru, i);
+            float dl = seq_get<T>(rd, i) + bias;
+            if (a.delta_softplus) dl = fast_softplus20(dl);
+            if (t0 + i >= L) dl = 0.f;
+            const float du = dl * uu;
+            float y = Dd * uu;
+            const float4 *Bt = reinterpret_cast<const float4 *>(Bs + i * NS);
+            const float4 *Ct = reinterpret_cast<const float4 *>(Cs + i * NS);
+#pragma unroll
+            for (int q = 0; q < NS / 4; ++q) {
+                const float4 bb = Bt[q], cc = Ct[q];
+                const float bq[4] = {bb.x, bb.y, bb.z, bb.w}, cq[4] = {cc.x, cc.y, cc.z, cc.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int n = q * 4 + j;
+                    h[n] = fmaf(ex2(dl * A2[n]), h[n], du * bq[j]);
+                    y = fmaf(h[n], cq[j], y);
+                }
+            }
+            yp[i] = y;
+            yo[i] = zrow ? y * fast_silu(seq_get<T>(rz, i)) : y;
+        }
+        if (live) {
+            auto put = [&](T *row, const float (&v)[TB]) {
+                if (io_vec && t0 + TB <= L) {
+                    SeqRaw<T> o;
+                    T *e = reinterpret_cast<T *>(o.v);
+#pragma unroll
+                    for (int i = 0; i < TB; ++i) e[i] = from_float<T>(v[i]);
+                    reinterpret_cast<uint4 *>(row + t0)[0] = o.v[0];
+                    reinterpret_cast<uint4 *>(row + t0)[1] = o.v[1];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                        if (t0 + i < L) row[t0 + i] = from_float<T>(v[i]);
+                }
+            };
+            put(orow, yo);
+            if (prow) put(prow, yp);
+        }
+        __syncwarp();            // every lane is done reading this block's B/C tile
+        if (more) {
+            bc_store(Bs, nb);
+            bc_store(Cs, ncc);
+            ru = nu;
+            rd = nd;
+            if (zrow) rz = nz;
+        }
+        __syncwarp();
+    }
+    if (a.last_state && live) {
+        float *ls = a.last_state + ((int64_t)b * a.dim + d) * N;
+#pragma unroll
+        for (int n = 0; n < NS; ++n)
+            if (n < N) ls[n] = h[n];
+    }
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <typename T>
@@ -307,6 +492,17 @@ int launch_scan(const mb200_scan_args &a, cudaStream_t stream)
         bc_vec = bc_vec && (reinterpret_cast<uintptr_t>(a.C) % bc_align == 0) && a.C_stride[0] % 4 == 0 &&
                  a.C_stride[1] % 4 == 0 && a.C_stride[2] % 4 == 0;
     const int vec_flags = (io_vec ? 1 : 0) | (bc_vec ? 2 : 0);
+    // Enough independent channels to give every SM a few warps: one lane per channel, time sequential.
+    if (N <= 16 && a.B_variable && a.C_variable && (int64_t)a.batch * a.dim >= 2LL * 32 * 148) {
+        // the B/C tile is fetched in 16-byte packets here
+        const bool bc16 = bc_vec && aligned16(a.B) && aligned16(a.C) && a.B_stride[0] % VEC == 0 && a.B_stride[1] % VEC == 0 &&
+                          a.B_stride[2] % VEC == 0 && a.C_stride[0] % VEC == 0 && a.C_stride[1] % VEC == 0 && a.C_stride[2] % VEC == 0;
+        const int flags = (io_vec ? 1 : 0) | (bc16 ? 2 : 0);
+        dim3 grid(a.ngroups * ((per_group + 31) / 32), a.batch);
+        if (N <= 8) scan_seq_kernel<T, 8><<<grid, 32, 0, stream>>>(a, flags);
+        else scan_seq_kernel<T, 16><<<grid, 32, 0, stream>>>(a, flags);
+        return MB200_OK;
+    }
     const size_t smem = sizeof(float) * (2 * kStateBlock * kTile + 2 * (size_t)chans * npad);
     static_assert(2 * kStateBlock * kTile * sizeof(float) + 2 * kWarps * 2 * 256 * sizeof(float) <= 227 * 1024, "smem budget");
     cudaError_t e = cudaFuncSetAttribute(scan_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -136,29 +136,61 @@ __global__ void __launch_bounds__(kT) ssd_chunk_state_kernel(const mb200_ssd_arg
 }
 
 // ---- stage 3 ------------------------------------------------------------------------------------
-// Elementwise over P*N, serial over chunks.  Slot c of `states` receives the state entering chunk c.
-// With `prev16` the entering states go there as 16-bit values (the tensor-core chunk_scan reads
-// them by TMA) and the fp32 slots are left alone.
+// Elementwise over P*N, serial over chunks.  Slot c of `states` receives the state entering chunk c;
+// with `prev16` the entering states go there as 16-bit values (the tensor-core chunk_scan reads them
+// by TMA) and the fp32 slots are left alone.  VEC elements per thread and kAhead chunks of loads in
+// flight keep enough bytes in the air to stream at HBM speed.
+template <int VEC>
 __global__ void __launch_bounds__(256) ssd_state_passing_kernel(const mb200_ssd_args a, const float *dAb, float *states,
                                                                 int nchunks, bool write_prev, void *prev16)
 {
+    constexpr int kAhead = 4;
     const int64_t PN = (int64_t)a.headdim * a.dstate;
-    const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int64_t e = ((int64_t)blockIdx.x * 256 + threadIdx.x) * VEC;
     const int h = blockIdx.y, b = blockIdx.z;
     const int Q = a.chunk_size;
     const float *dA_last = dAb + ((int64_t)b * a.nheads + h) * nchunks * Q + (Q - 1);
     if (e < PN) {
-        float run = a.initial_states ? a.initial_states[((int64_t)b * a.nheads + h) * PN + e] : 0.f;
-        for (int c = 0; c < nchunks; ++c) {
-            float *slot = states + (((int64_t)b * nchunks + c) * a.nheads + h) * PN + e;
-            const float s = *slot;
-            if (write_prev) {
-                if (prev16) store_any(prev16, a.io_dtype, (((int64_t)b * nchunks + c) * a.nheads + h) * PN + e, run);
-                else *slot = run;
+        float run[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) run[i] = a.initial_states ? a.initial_states[((int64_t)b * a.nheads + h) * PN + e + i] : 0.f;
+        for (int c0 = 0; c0 < nchunks; c0 += kAhead) {
+            float s[kAhead][VEC], dec[kAhead];
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int c = c0 + u;
+                if (c < nchunks) {
+                    const float *slot = states + (((int64_t)b * nchunks + c) * a.nheads + h) * PN + e;
+                    if (VEC == 4) {
+                        const float4 v = *reinterpret_cast<const float4 *>(slot);
+                        s[u][0] = v.x; s[u][1 % VEC] = v.y; s[u][2 % VEC] = v.z; s[u][3 % VEC] = v.w;
+                    } else {
+                        s[u][0] = slot[0];
+                    }
+                    dec[u] = __expf(dA_last[(int64_t)c * Q]);
+                }
             }
-            run = fmaf(__expf(dA_last[(int64_t)c * Q]), run, s);
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int c = c0 + u;
+                if (c < nchunks) {
+                    const int64_t o = (((int64_t)b * nchunks + c) * a.nheads + h) * PN + e;
+                    if (write_prev) {
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) {
+                            if (prev16) store_any(prev16, a.io_dtype, o + i, run[i]);
+                            else states[o + i] = run[i];
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) run[i] = fmaf(dec[u], run[i], s[u][i]);
+                }
+            }
         }
-        if (a.final_states) a.final_states[((int64_t)b * a.nheads + h) * PN + e] = run;
+        if (a.final_states) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) a.final_states[((int64_t)b * a.nheads + h) * PN + e + i] = run[i];
+        }
     }
     if (a.range_decay && blockIdx.x == 0 && threadIdx.x == 0) {
         float tot = 0.f;
@@ -303,14 +335,20 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
             // range summary only: fold the local chunk states from a zero state, leave the slots as they are
             mb200_ssd_args z = a;
             z.initial_states = nullptr;
-            ssd_state_passing_kernel<<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(z, dAb, states, nc, false, nullptr);
+            if (PN % 4 == 0)
+                ssd_state_passing_kernel<4><<<dim3((unsigned)((PN / 4 + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(z, dAb, states, nc, false, nullptr);
+            else
+                ssd_state_passing_kernel<1><<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(z, dAb, states, nc, false, nullptr);
             MB200_CHECK_LAUNCH("ssd range summary");
         }
     }
     if (a.phases & MB200_SSD_PHASE_OUTPUT) {
         mb200_ssd_args p = a;
         if (!(a.phases & MB200_SSD_PHASE_LOCAL)) p.range_decay = nullptr;
-        ssd_state_passing_kernel<<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
+        if (PN % 4 == 0)
+            ssd_state_passing_kernel<4><<<dim3((unsigned)((PN / 4 + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
+        else
+            ssd_state_passing_kernel<1><<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
         MB200_CHECK_LAUNCH("ssd state_passing");
         if (tc) {
             if (int rc = ssd_tc_cb_and_scan(a, lay, stream)) return rc;

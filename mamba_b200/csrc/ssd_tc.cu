@@ -272,10 +272,22 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __
 }
 
 // ====================================================================================== chunk scan
-// grid (nheads, nchunks * 2, batch).  smem: x 32 KB | 48 KB region = {C 2 x 16 KB, H 2 x 8 KB}, reused as a
-// 3-slot ring of CB blocks once Y1 is done | dA*log2e, dt (2 KB) | barriers.  TMEM: 128 columns.
+// grid (nheads, nchunks * 2, batch), 288 threads: warps 0-7 element-wise + epilogue (thread = one row and one
+// 32-column half), warp 8 TMA + MMA.  smem: x 32 KB | 48 KB region = {C 2 x 16 KB, H 2 x 8 KB}, reused as a
+// 3-slot ring of CB blocks once Y1 is done | dA*log2e, dt, column factors (3 KB) | barriers.  TMEM: 128 columns.
+//
+// Decay mask.  A thread owns 32 consecutive columns k of one row m per CB block.  Three cases:
+//   all k > m           zeros
+//   all k <= m          L[m,k] = exp(dA_m - dA_ref) * (exp(dA_ref - dA_k) dt_k), ref = last k of the range: one
+//                       exponential per thread, the column factors are computed once per CTA.  Both exponents
+//                       are <= 0 because dA_cumsum is non-increasing (A <= 0, dt >= 0); a chunk where that does
+//                       not hold is detected and sent down the exact path.
+//   range holds k = m   exact: exp(min(dA_m - dA_k, 0)) dt_k [k <= m] per element
+constexpr int kScanThreads = 288;
+__device__ __forceinline__ void scan_compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
 template <typename T>
-__global__ void __launch_bounds__(kThreadsTc)
+__global__ void __launch_bounds__(kScanThreads)
 ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_C,
                          const __grid_constant__ CUtensorMap tm_H, const __grid_constant__ CUtensorMap tm_CB, const mb200_ssd_args a,
                          const float *dtb, const float *dAb, int nchunks, int *status)
@@ -285,8 +297,10 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     uint8_t *xs = sm;                          // [256 x 64], rows k
     uint8_t *R1 = sm + 32768;                  // 48 KB
     float *dA2 = reinterpret_cast<float *>(sm + 81920);   // 256: dA_cumsum * log2(e)
-    float *dts = dA2 + 256;                               // 256
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 81920 + 2048);
+    float *dts = dA2 + 256;                               // 256: dt
+    float *cks = dts + 256;                               // 256: exp(dA_ref(k) - dA_k) dt_k, ref(k) = k | 31
+    int *mono = reinterpret_cast<int *>(cks + 256);       // 1 while dA_cumsum is non-increasing over the chunk
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 81920 + 3072 + 64);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
     uint64_t *bar_c = &bars[0], *bar_x = &bars[1], *bar_g1 = &bars[2], *bar_g2 = &bars[3];
     uint64_t *bar_full = &bars[4], *bar_scaled = &bars[7], *bar_empty = &bars[10];
@@ -295,19 +309,20 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     const int g = h / (a.nheads / a.ngroups);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nk = (mb + 1) * 2;   // 64-wide CB blocks this row block needs
-    if (threadIdx.x == 128) {
+    if (threadIdx.x == 256) {
         mbar_init(bar_c, 1);
         mbar_init(bar_x, 1);
         mbar_init(bar_g1, 1);
         mbar_init(bar_g2, 1);
         for (int i = 0; i < 3; ++i) {
             mbar_init(&bar_full[i], 1);
-            mbar_init(&bar_scaled[i], 128);
+            mbar_init(&bar_scaled[i], 256);
             mbar_init(&bar_empty[i], 1);
         }
+        *mono = 1;
         mbar_fence_init();
     }
-    if (warp == 4) tmem_alloc(tmem_slot, 128);
+    if (warp == 8) tmem_alloc(tmem_slot, 128);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -315,7 +330,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     const int64_t unit_h = ((int64_t)b * nchunks + c) * a.nheads + h;
     const int64_t unit_g = ((int64_t)b * nchunks + c) * a.ngroups + g;
 
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) {
             bool ok = true;
             mbar_expect_tx(bar_c, 32768 + 16384);
@@ -366,34 +381,56 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             mma_commit(bar_g2);
         }
     } else {
-        const int r = threadIdx.x;          // row inside the block = TMEM lane
+        const int r = threadIdx.x & 127;    // row inside the block = TMEM lane
+        const int kh = threadIdx.x >> 7;    // which 32-column half of every 64-wide block
         const int m = mb * 128 + r;         // row inside the chunk
         const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
         const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            dA2[r + i * 128] = dAc[r + i * 128] * kLog2e;
-            dts[r + i * 128] = dtc[r + i * 128];
+        {
+            const int k = threadIdx.x;
+            const float dk = dAc[k], tk = dtc[k];
+            dA2[k] = dk * kLog2e;
+            dts[k] = tk;
+            cks[k] = __expf(dAc[k | 31] - dk) * tk;
+            if (k > 0 && dk > dAc[k - 1]) *mono = 0;
         }
-        compute_sync();
+        scan_compute_sync();
         const float dAm = dA2[m];
+        const bool factor_ok = *mono != 0;
         bool ok = true;
         for (int j = 0; j < nk; ++j) {
             const int slot = j % 3;
-            const int k0 = j * 64;
+            const int klo = j * 64 + kh * 32;       // first column of this thread's range
             ok = ok && mbar_wait(&bar_full[slot], (j / 3) & 1, status, kStBarFull);
             const uint32_t rowaddr = smem_u32(R1 + slot * 16384) + r * 128;
             if (ok) {
-                if (k0 > m) {
+                if (klo > m) {
 #pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) sts128(rowaddr + (ch << 4), make_uint4(0, 0, 0, 0));
-                } else {
+                    for (int ch = 0; ch < 4; ++ch) sts128(rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4), make_uint4(0, 0, 0, 0));
+                } else if (klo + 31 <= m && factor_ok) {
+                    const float rm = ex2(dAm - dA2[klo + 31]);
 #pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) {
-                        const uint32_t addr = rowaddr + ((ch ^ (r & 7)) << 4);
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const uint32_t addr = rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4);
                         uint4 v = lds128(addr);
                         uint32_t *e = reinterpret_cast<uint32_t *>(&v);
-                        const int kc = k0 + ch * 8;
+                        const int kc = klo + ch * 8;
+                        const float4 c0 = *reinterpret_cast<const float4 *>(cks + kc), c1 = *reinterpret_cast<const float4 *>(cks + kc + 4);
+                        const float ck[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = Pack2<T>::unpack(e[q]);
+                            e[q] = Pack2<T>::pack(f.x * (rm * ck[2 * q]), f.y * (rm * ck[2 * q + 1]));
+                        }
+                        sts128(addr, v);
+                    }
+                } else {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const uint32_t addr = rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4);
+                        uint4 v = lds128(addr);
+                        uint32_t *e = reinterpret_cast<uint32_t *>(&v);
+                        const int kc = klo + ch * 8;
                         const float4 d0 = *reinterpret_cast<const float4 *>(dA2 + kc), d1 = *reinterpret_cast<const float4 *>(dA2 + kc + 4);
                         const float4 t0 = *reinterpret_cast<const float4 *>(dts + kc), t1 = *reinterpret_cast<const float4 *>(dts + kc + 4);
                         const float dk[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
@@ -418,27 +455,24 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         const int t = c * kQ + m;
         const bool live = t < a.seqlen;     // rows past the end of the sequence load TMEM with the warp but touch no memory
         if (ok) {
-            const float scale = ex2(dAm);
-            const int tc_ = live ? t : 0;
-            const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)tc_ * a.z_stride[1] + (int64_t)h * a.z_stride[2] : nullptr;
-            T *orow = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)tc_ * a.out_stride[1] + (int64_t)h * a.out_stride[2];
-            const uint32_t xrow = smem_u32(xs) + m * 128;
-            const bool zo_vec = ((reinterpret_cast<uintptr_t>(orow) | reinterpret_cast<uintptr_t>(zrow)) & 15) == 0;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float y1[32], y2[32];
-                __syncwarp();   // rows past the end skipped the previous half's stores; rejoin before the collective load
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + half * 32, y1);
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + 64 + half * 32, y2);
-                if (!live) continue;
+            float y1[32], y2[32];
+            const uint32_t tl = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * 32;
+            tmem_ld32(tl, y1);
+            tmem_ld32(tl + 64, y2);
+            if (live) {
+                const float scale = ex2(dAm);
+                const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)t * a.z_stride[1] + (int64_t)h * a.z_stride[2] : nullptr;
+                T *orow = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)t * a.out_stride[1] + (int64_t)h * a.out_stride[2];
+                const uint32_t xrow = smem_u32(xs) + m * 128;
+                const bool zo_vec = ((reinterpret_cast<uintptr_t>(orow) | reinterpret_cast<uintptr_t>(zrow)) & 15) == 0;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int p0 = half * 32 + q4 * 8;
+                    const int p0 = kh * 32 + q4 * 8;
                     float y[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) y[i] = fmaf(scale, y1[q4 * 8 + i], y2[q4 * 8 + i]);
                     if (a.D) {
-                        const uint4 xv = lds128(xrow + ((((p0 >> 3)) ^ (m & 7)) << 4));
+                        const uint4 xv = lds128(xrow + (((p0 >> 3) ^ (m & 7)) << 4));
                         const uint32_t *xe = reinterpret_cast<const uint32_t *>(&xv);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
@@ -481,7 +515,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem, 128);
+    if (warp == 8) tmem_dealloc(tmem, 128);
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -523,7 +557,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
         if (!encode_16bit(&tB, fmt, a.B, 4, d, sB, stage == 0 ? bx256 : bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for B failed");
         if (!encode_16bit(&tC, fmt, a.C, 4, d, sC, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for C failed");
     }
-    const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = 81920 + 2048 + 256 + 1024;
+    const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = 81920 + 3072 + 64 + 256 + 1024;
     if (stage == 0) {
         cudaFuncSetAttribute(ssd_tc_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state);
         ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kThreadsTc, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
@@ -547,7 +581,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
     ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
     MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
     cudaFuncSetAttribute(ssd_tc_chunk_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scan);
-    ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kThreadsTc, smem_scan, stream>>>(tx, tC, tH, tCB, a, dtb, dAb, nc, status);
+    ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, a, dtb, dAb, nc, status);
     MB200_CHECK_LAUNCH("ssd chunk_scan (tensor core)");
     return MB200_OK;
 }

@@ -95,6 +95,26 @@ def test_constant_bc(const_b, const_c):
     run_both(make_inputs(21, 2, 12, 300, 8, 1, torch.float32, const_b=const_b, const_c=const_c), TOL_FP32, "const B/C")
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_FP32), (torch.bfloat16, TOL_BF16), (torch.float16, TOL_BF16)])
+@pytest.mark.parametrize("L,N,groups", [(700, 16, 1), (333, 8, 2), (64, 5, 1), (1, 16, 1), (1030, 12, 4)])
+def test_many_channels(dtype, tol, L, N, groups):
+    """Enough independent channels (batch x dim >= 2 x 32 x 148) for the one-lane-per-channel kernel:
+    ragged lengths, dstate below 16, several groups, a channel count that is not a multiple of 32."""
+    run_both(make_inputs(60 + L, 2, 4744, L, N, groups, dtype, bench_style=True), tol, f"many L{L} N{N} g{groups}")
+
+
+def test_many_channels_unaligned_and_ungated():
+    inp = make_inputs(71, 2, 4800, 77, 16, 1, torch.bfloat16, has_z=False, has_D=False)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    pad = lambda t: torch.cat([t.new_zeros(*t.shape[:-1], 1), t], dim=-1)[..., 1:]
+    got, last = _fn()(pad(c["u"]), pad(c["delta"]), c["A"], pad(c["B"]), pad(c["C"]), None, None, c["delta_bias"],
+                      delta_softplus=True, return_last_state=True)
+    want, wl = oracle.selective_scan(inp["u"].float(), inp["delta"].float(), inp["A"], inp["B"].float(), inp["C"].float(),
+                                     None, None, inp["delta_bias"], delta_softplus=True, return_last_state=True)
+    assert_close(got, want, TOL_BF16, "unaligned many out")
+    assert_close(last, wl, TOL_BF16, "unaligned many last")
+
+
 def test_optional_tensors_absent():
     inp = make_inputs(23, 2, 8, 200, 8, 1, torch.float32, has_z=False, has_D=False)
     inp["delta_bias"] = None
