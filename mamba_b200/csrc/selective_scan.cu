@@ -281,13 +281,15 @@ scan_fwd_kernel(const mb200_scan_args a, const int cpw, const int nblocks, const
 }
 
 // ------------------------------------------------------------------------------------------------
-// Channel-parallel variant for dstate <= 16 with input-dependent B and C: one lane per channel, time
-// sequential.  All 32 lanes of a warp are at the same step, so B_t and C_t are warp-uniform
-// (broadcast reads of a tiny per-warp shared tile) and the only loop-carried dependence is the one
-// FMA per state; there is no scan tree and no re-evaluation, i.e. 4 FMA-pipe + 1 MUFU instruction
-// per (step, state).  Each lane streams its own row 32 bytes at a time (whole sectors), one block
-// ahead of use; warps never synchronise with each other, so a CTA is a single warp and the grid
-// spreads evenly over the SMs.
+// Channel-parallel variant for dstate <= 16 with input-dependent B and C: time is sequential, a
+// channel belongs to a PAIR of lanes that split its states between them (16 channels per warp).
+// All lanes of a warp are at the same step, so B_t and C_t are warp-uniform (broadcast reads of a
+// tiny per-warp shared tile) and the only loop-carried dependence is one FMA per state: no scan tree,
+// no re-evaluation -- 4 FMA-pipe + 1 MUFU instruction per (step, state).  The pair also splits the
+// per-step scalar work: each lane evaluates softplus(dt) and silu(z) for half of the block's steps
+// and the partner gets dt by shuffle; the two partial outputs meet in one more shuffle.  A lane
+// streams its channel's rows 32 bytes at a time (whole sectors) with the next block prefetched into
+// L1; warps never synchronise with each other, so a CTA is one warp and the grid spreads evenly.
 constexpr int kSeqBytes = 32;   // bytes of one row a lane moves per block (two 16-byte packets)
 
 template <typename T> struct SeqRaw { uint4 v[2]; };
@@ -313,8 +315,8 @@ __device__ __forceinline__ SeqRaw<T> seq_load(const T *row, int t0, int L, bool 
     constexpr int TB = kSeqBytes / sizeof(T);
     SeqRaw<T> r;
     if (vec_ok && t0 + TB <= L) {
-        r.v[0] = __ldg(reinterpret_cast<const uint4 *>(row + t0));
-        r.v[1] = __ldg(reinterpret_cast<const uint4 *>(row + t0) + 1);
+        r.v[0] = *reinterpret_cast<const uint4 *>(row + t0);
+        r.v[1] = *(reinterpret_cast<const uint4 *>(row + t0) + 1);
     } else {
         T *e = reinterpret_cast<T *>(r.v);
 #pragma unroll
@@ -323,30 +325,46 @@ __device__ __forceinline__ SeqRaw<T> seq_load(const T *row, int t0, int L, bool 
     return r;
 }
 
+template <typename T>
+__device__ __forceinline__ void seq_prefetch(const T *row, int t0, int L)
+{
+    if (t0 < L) asm volatile("prefetch.global.L1 [%0];" ::"l"(row + t0));
+}
+
 template <typename T, int NS>
-__global__ void __launch_bounds__(32) scan_seq_kernel(const mb200_scan_args a, const int vec_flags)
+__global__ void __launch_bounds__(32, 18) scan_seq_kernel(const mb200_scan_args a, const int vec_flags)
 {
     constexpr int TB = kSeqBytes / sizeof(T);          // steps per block: 16 (16-bit) or 8 (fp32)
+    constexpr int HS = NS / 2;                         // states per lane
+    constexpr int HP = TB / 2;                         // steps per 16-byte packet
     __shared__ __align__(16) float Bs[TB * NS], Cs[TB * NS];
     const int lane = threadIdx.x;
+    const int half = lane & 1;                         // which half of the states / of the block's steps is mine
     const int N = a.dstate, L = a.seqlen;
     const int per_group = a.dim / a.ngroups;
-    const int blocks_per_group = (per_group + 31) / 32;
+    const int blocks_per_group = (per_group + 15) / 16;
     const int b = blockIdx.y;
     const int g = blockIdx.x / blocks_per_group;
-    const int d = g * per_group + (blockIdx.x % blocks_per_group) * 32 + lane;
+    const int d = g * per_group + (blockIdx.x % blocks_per_group) * 16 + (lane >> 1);
     const bool live = d < (g + 1) * per_group;
     const int dc = live ? d : g * per_group;            // idle lanes shadow a valid channel, store nothing
     const bool io_vec = vec_flags & 1, bc_vec = vec_flags & 2;
 
-    float A2[NS], h[NS];
+    // states live as packed fp32 pairs: every multiply / FMA of the recurrence is one f32x2 instruction
+    uint64_t A2[HS / 2], h[HS / 2];
 #pragma unroll
-    for (int n = 0; n < NS; ++n) {
-        A2[n] = n < N ? a.A[(int64_t)dc * a.A_stride[0] + (int64_t)n * a.A_stride[1]] * kLog2e : 0.f;
-        h[n] = 0.f;
+    for (int j = 0; j < HS / 2; ++j) {
+        float av[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int n = half * HS + 2 * j + e;
+            av[e] = n < N ? a.A[(int64_t)dc * a.A_stride[0] + (int64_t)n * a.A_stride[1]] * kLog2e : 0.f;
+        }
+        A2[j] = pack2(av[0], av[1]);
+        h[j] = pack2(0.f, 0.f);
     }
     const float bias = a.delta_bias ? a.delta_bias[dc] : 0.f;
-    const float Dd = a.D ? a.D[dc] : 0.f;
+    const float Dd = (a.D && half == 0) ? a.D[dc] : 0.f;   // the skip term is added once per pair
     const T *urow = static_cast<const T *>(a.u) + (int64_t)b * a.u_stride[0] + (int64_t)dc * a.u_stride[1];
     const T *drow = static_cast<const T *>(a.delta) + (int64_t)b * a.delta_stride[0] + (int64_t)dc * a.delta_stride[1];
     const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)dc * a.z_stride[1] : nullptr;
@@ -354,112 +372,119 @@ __global__ void __launch_bounds__(32) scan_seq_kernel(const mb200_scan_args a, c
     T *prow = (a.z && a.out_pregate) ? static_cast<T *>(a.out_pregate) + (int64_t)b * a.pregate_stride[0] + (int64_t)dc * a.pregate_stride[1] : nullptr;
 
     // B/C staging: the block's tile is N rows x 32 bytes = N x 2 packets; lane -> (row lane/2, packet lane%2)
-    const int sn = lane >> 1, sh = lane & 1;
+    const int sn = lane >> 1;
     const T *Bsrc = static_cast<const T *>(a.B) + (int64_t)b * a.B_stride[0] + (int64_t)g * a.B_stride[1] + (int64_t)sn * a.B_stride[2];
     const T *Csrc = static_cast<const T *>(a.C) + (int64_t)b * a.C_stride[0] + (int64_t)g * a.C_stride[1] + (int64_t)sn * a.C_stride[2];
-    constexpr int HP = TB / 2;                          // steps per packet
-    auto bc_load = [&](const T *src, int t0) {
-        uint4 r = make_uint4(0, 0, 0, 0);
-        if (sn < N) {
-            const int ts = t0 + sh * HP;
-            if (bc_vec && ts + HP <= L) {
-                r = __ldg(reinterpret_cast<const uint4 *>(src + ts));
-            } else {
-                T *e = reinterpret_cast<T *>(&r);
-#pragma unroll
-                for (int i = 0; i < HP; ++i) e[i] = (ts + i < L) ? src[ts + i] : from_float<T>(0.f);
-            }
-        }
-        return r;
-    };
-    auto bc_store = [&](float *dst, const uint4 &r) {
+    auto bc_stage = [&](float *dst, const T *src, int t0) {
         if (sn < NS) {
+            uint4 r = make_uint4(0, 0, 0, 0);
+            const int ts = t0 + half * HP;
+            if (sn < N) {
+                if (bc_vec && ts + HP <= L) {
+                    r = *reinterpret_cast<const uint4 *>(src + ts);
+                } else {
+                    T *e = reinterpret_cast<T *>(&r);
+#pragma unroll
+                    for (int i = 0; i < HP; ++i) e[i] = (ts + i < L) ? src[ts + i] : from_float<T>(0.f);
+                }
+            }
             const T *e = reinterpret_cast<const T *>(&r);
 #pragma unroll
-            for (int i = 0; i < HP; ++i) dst[(sh * HP + i) * NS + sn] = to_float(e[i]);
+            for (int i = 0; i < HP; ++i) dst[(half * HP + i) * NS + sn] = to_float(e[i]);
         }
     };
 
     const int nblk = (L + TB - 1) / TB;
-    SeqRaw<T> ru = seq_load(urow, 0, L, io_vec), rd = seq_load(drow, 0, L, io_vec), rz;
-    if (zrow) rz = seq_load(zrow, 0, L, io_vec);
-    {
-        const uint4 b0 = bc_load(Bsrc, 0), c0 = bc_load(Csrc, 0);
-        bc_store(Bs, b0);
-        bc_store(Cs, c0);
-    }
-    __syncwarp();
     for (int blk = 0; blk < nblk; ++blk) {
         const int t0 = blk * TB;
-        // next block's operands are requested before this block's arithmetic
-        SeqRaw<T> nu, nd, nz;
-        uint4 nb = make_uint4(0, 0, 0, 0), ncc = make_uint4(0, 0, 0, 0);
-        const bool more = blk + 1 < nblk;
-        if (more) {
-            nu = seq_load(urow, t0 + TB, L, io_vec);
-            nd = seq_load(drow, t0 + TB, L, io_vec);
-            if (zrow) nz = seq_load(zrow, t0 + TB, L, io_vec);
-            nb = bc_load(Bsrc, t0 + TB);
-            ncc = bc_load(Csrc, t0 + TB);
+        bc_stage(Bs, Bsrc, t0);
+        bc_stage(Cs, Csrc, t0);
+        const SeqRaw<T> ru = seq_load(urow, t0, L, io_vec), rd = seq_load(drow, t0, L, io_vec);
+        SeqRaw<T> rz;
+        if (zrow) rz = seq_load(zrow, t0, L, io_vec);
+        if (blk + 1 < nblk) {       // next block's sectors start moving while this block is computed
+            seq_prefetch(urow, t0 + TB, L);
+            seq_prefetch(drow, t0 + TB, L);
+            if (zrow) seq_prefetch(zrow, t0 + TB, L);
+            if (sn < N) {
+                seq_prefetch(Bsrc, t0 + TB + half * HP, L);
+                seq_prefetch(Csrc, t0 + TB + half * HP, L);
+            }
         }
-        float yo[TB], yp[TB];
+        // my half of the block's dt values; the partner's arrive by shuffle inside the step loop
+        float dtm[HP];
+#pragma unroll
+        for (int i = 0; i < HP; ++i) {
+            float v = (half ? seq_get<T>(rd, HP + i) : seq_get<T>(rd, i)) + bias;   // compile-time register indices
+            if (a.delta_softplus) v = fast_softplus20(v);
+            if (t0 + half * HP + i >= L) v = 0.f;
+            dtm[i] = v;
+        }
+        __syncwarp();               // B/C tile of this block is in place
+        float ym[HP];               // outputs of my half of the steps
 #pragma unroll
         for (int i = 0; i < TB; ++i) {
             const float uu = seq_get<T>(ru, i);
-            float dl = seq_get<T>(rd, i) + bias;
-            if (a.delta_softplus) dl = fast_softplus20(dl);
-            if (t0 + i >= L) dl = 0.f;
+            const float dl = __shfl_sync(0xffffffffu, dtm[i % HP], (lane & ~1) | (i / HP));
             const float du = dl * uu;
-            float y = Dd * uu;
-            const float4 *Bt = reinterpret_cast<const float4 *>(Bs + i * NS);
-            const float4 *Ct = reinterpret_cast<const float4 *>(Cs + i * NS);
+            const uint64_t dl2 = pack2(dl, dl), du2 = pack2(du, du);
+            uint64_t ya = pack2(Dd * uu, 0.f), yb = pack2(0.f, 0.f);
+            const ulonglong2 *Bt = reinterpret_cast<const ulonglong2 *>(Bs + i * NS + half * HS);
+            const ulonglong2 *Ct = reinterpret_cast<const ulonglong2 *>(Cs + i * NS + half * HS);
 #pragma unroll
-            for (int q = 0; q < NS / 4; ++q) {
-                const float4 bb = Bt[q], cc = Ct[q];
-                const float bq[4] = {bb.x, bb.y, bb.z, bb.w}, cq[4] = {cc.x, cc.y, cc.z, cc.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int n = q * 4 + j;
-                    h[n] = fmaf(ex2(dl * A2[n]), h[n], du * bq[j]);
-                    y = fmaf(h[n], cq[j], y);
-                }
+            for (int q = 0; q < HS / 4; ++q) {
+                const ulonglong2 bb = Bt[q], cc = Ct[q];
+                float x0, x1;
+                unpack2(mul2(dl2, A2[2 * q]), x0, x1);
+                h[2 * q] = fma2(pack2(ex2(x0), ex2(x1)), h[2 * q], mul2(du2, bb.x));
+                ya = fma2(h[2 * q], cc.x, ya);
+                unpack2(mul2(dl2, A2[2 * q + 1]), x0, x1);
+                h[2 * q + 1] = fma2(pack2(ex2(x0), ex2(x1)), h[2 * q + 1], mul2(du2, bb.y));
+                yb = fma2(h[2 * q + 1], cc.y, yb);
             }
-            yp[i] = y;
-            yo[i] = zrow ? y * fast_silu(seq_get<T>(rz, i)) : y;
+            float s0, s1, s2, s3;
+            unpack2(ya, s0, s1);
+            unpack2(yb, s2, s3);
+            const float y = (s0 + s1) + (s2 + s3);
+            const float yt = y + __shfl_xor_sync(0xffffffffu, y, 1);
+            if ((i / HP) == 0) { if (!half) ym[i % HP] = yt; } else { if (half) ym[i % HP] = yt; }
         }
+        __syncwarp();               // every lane is done with the B/C tile before the next block overwrites it
         if (live) {
-            auto put = [&](T *row, const float (&v)[TB]) {
-                if (io_vec && t0 + TB <= L) {
-                    SeqRaw<T> o;
-                    T *e = reinterpret_cast<T *>(o.v);
+            const int ts = t0 + half * HP;
+            float yg[HP];
 #pragma unroll
-                    for (int i = 0; i < TB; ++i) e[i] = from_float<T>(v[i]);
-                    reinterpret_cast<uint4 *>(row + t0)[0] = o.v[0];
-                    reinterpret_cast<uint4 *>(row + t0)[1] = o.v[1];
+            for (int i = 0; i < HP; ++i) {
+                float zz = 0.f;
+                if (zrow) zz = half ? seq_get<T>(rz, HP + i) : seq_get<T>(rz, i);
+                yg[i] = zrow ? ym[i] * fast_silu(zz) : ym[i];
+            }
+            auto put = [&](T *row, const float (&v)[HP]) {
+                if (io_vec && ts + HP <= L) {
+                    uint4 o;
+                    T *e = reinterpret_cast<T *>(&o);
+#pragma unroll
+                    for (int i = 0; i < HP; ++i) e[i] = from_float<T>(v[i]);
+                    *reinterpret_cast<uint4 *>(row + ts) = o;
                 } else {
 #pragma unroll
-                    for (int i = 0; i < TB; ++i)
-                        if (t0 + i < L) row[t0 + i] = from_float<T>(v[i]);
+                    for (int i = 0; i < HP; ++i)
+                        if (ts + i < L) row[ts + i] = from_float<T>(v[i]);
                 }
             };
-            put(orow, yo);
-            if (prow) put(prow, yp);
+            put(orow, yg);
+            if (prow) put(prow, ym);
         }
-        __syncwarp();            // every lane is done reading this block's B/C tile
-        if (more) {
-            bc_store(Bs, nb);
-            bc_store(Cs, ncc);
-            ru = nu;
-            rd = nd;
-            if (zrow) rz = nz;
-        }
-        __syncwarp();
     }
     if (a.last_state && live) {
         float *ls = a.last_state + ((int64_t)b * a.dim + d) * N;
 #pragma unroll
-        for (int n = 0; n < NS; ++n)
-            if (n < N) ls[n] = h[n];
+        for (int j = 0; j < HS / 2; ++j) {
+            float lo, hi;
+            unpack2(h[j], lo, hi);
+            if (half * HS + 2 * j < N) ls[half * HS + 2 * j] = lo;
+            if (half * HS + 2 * j + 1 < N) ls[half * HS + 2 * j + 1] = hi;
+        }
     }
 }
 
@@ -498,7 +523,7 @@ int launch_scan(const mb200_scan_args &a, cudaStream_t stream)
         const bool bc16 = bc_vec && aligned16(a.B) && aligned16(a.C) && a.B_stride[0] % VEC == 0 && a.B_stride[1] % VEC == 0 &&
                           a.B_stride[2] % VEC == 0 && a.C_stride[0] % VEC == 0 && a.C_stride[1] % VEC == 0 && a.C_stride[2] % VEC == 0;
         const int flags = (io_vec ? 1 : 0) | (bc16 ? 2 : 0);
-        dim3 grid(a.ngroups * ((per_group + 31) / 32), a.batch);
+        dim3 grid(a.ngroups * ((per_group + 15) / 16), a.batch);
         if (N <= 8) scan_seq_kernel<T, 8><<<grid, 32, 0, stream>>>(a, flags);
         else scan_seq_kernel<T, 16><<<grid, 32, 0, stream>>>(a, flags);
         return MB200_OK;

@@ -394,6 +394,20 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             cks[k] = __expf(dAc[k | 31] - dk) * tk;
             if (k > 0 && dk > dAc[k - 1]) *mono = 0;
         }
+        // The gate row and D do not depend on the MMAs: request them now so the epilogue finds them in
+        // registers instead of paying a DRAM round trip per packet.
+        const int t = c * kQ + m;
+        const bool live = t < a.seqlen;     // rows past the end of the sequence load TMEM with the warp but touch no memory
+        const int tcl = live ? t : 0;
+        const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)tcl * a.z_stride[1] + (int64_t)h * a.z_stride[2] + kh * 32 : nullptr;
+        T *orow = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)tcl * a.out_stride[1] + (int64_t)h * a.out_stride[2] + kh * 32;
+        const bool zo_vec = ((reinterpret_cast<uintptr_t>(orow) | reinterpret_cast<uintptr_t>(zrow)) & 15) == 0;
+        uint4 zv[4] = {};
+        if (zrow && live && zo_vec) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) zv[q4] = *reinterpret_cast<const uint4 *>(zrow + q4 * 8);
+        }
+        const float Dh = (a.D && !a.D_has_hdim) ? a.D[h] : 0.f;
         scan_compute_sync();
         const float dAm = dA2[m];
         const bool factor_ok = *mono != 0;
@@ -452,8 +466,6 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         ok = ok && mbar_wait(bar_g2, 0, status, kStBarG2);
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: the whole warp takes one path
         tc_fence_after_sync();
-        const int t = c * kQ + m;
-        const bool live = t < a.seqlen;     // rows past the end of the sequence load TMEM with the warp but touch no memory
         if (ok) {
             float y1[32], y2[32];
             const uint32_t tl = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * 32;
@@ -461,13 +473,10 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             tmem_ld32(tl + 64, y2);
             if (live) {
                 const float scale = ex2(dAm);
-                const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)t * a.z_stride[1] + (int64_t)h * a.z_stride[2] : nullptr;
-                T *orow = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)t * a.out_stride[1] + (int64_t)h * a.out_stride[2];
                 const uint32_t xrow = smem_u32(xs) + m * 128;
-                const bool zo_vec = ((reinterpret_cast<uintptr_t>(orow) | reinterpret_cast<uintptr_t>(zrow)) & 15) == 0;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int p0 = kh * 32 + q4 * 8;
+                    const int p0 = kh * 32 + q4 * 8;   // column inside the head
                     float y[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) y[i] = fmaf(scale, y1[q4 * 8 + i], y2[q4 * 8 + i]);
@@ -477,16 +486,15 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             const float2 f = Pack2<T>::unpack(xe[q]);
-                            const float D0 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q] : a.D[h];
-                            const float D1 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q + 1] : D0;
+                            const float D0 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q] : Dh;
+                            const float D1 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q + 1] : Dh;
                             y[2 * q] = fmaf(f.x, D0, y[2 * q]);
                             y[2 * q + 1] = fmaf(f.y, D1, y[2 * q + 1]);
                         }
                     }
                     if (zrow) {
                         if (zo_vec) {
-                            const uint4 zv = *reinterpret_cast<const uint4 *>(zrow + p0);
-                            const uint32_t *ze = reinterpret_cast<const uint32_t *>(&zv);
+                            const uint32_t *ze = reinterpret_cast<const uint32_t *>(&zv[q4]);
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 const float2 f = Pack2<T>::unpack(ze[q]);
@@ -495,7 +503,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                             }
                         } else {
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) y[i] *= fast_silu(to_float(zrow[p0 + i]));
+                            for (int i = 0; i < 8; ++i) y[i] *= fast_silu(to_float(zrow[q4 * 8 + i]));
                         }
                     }
                     if (zo_vec) {
@@ -504,10 +512,10 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         o.y = Pack2<T>::pack(y[2], y[3]);
                         o.z = Pack2<T>::pack(y[4], y[5]);
                         o.w = Pack2<T>::pack(y[6], y[7]);
-                        *reinterpret_cast<uint4 *>(orow + p0) = o;
+                        *reinterpret_cast<uint4 *>(orow + q4 * 8) = o;
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) orow[p0 + i] = from_float<T>(y[i]);
+                        for (int i = 0; i < 8; ++i) orow[q4 * 8 + i] = from_float<T>(y[i]);
                     }
                 }
             }
