@@ -126,7 +126,9 @@ int mb200_selective_state_update(const mb200_ssu_args *args, void *stream);
  * initial_states : optional (batch, nheads, headdim, dstate) fp32 contiguous.
  * final_states   : optional (batch, nheads, headdim, dstate) fp32 contiguous.
  * scratch : caller-owned device buffer of at least mb200_ssd_scratch_bytes() bytes, 256-byte
- *   aligned; holds dt, the dt*A cumulative sums, the per-chunk states and C.B^T between stages.
+ *   aligned; holds dt, the dt*A cumulative sums, the per-chunk states and C.B^T between stages.  Its
+ *   last 256 bytes hold an int32 status word, cleared at the start of every call: 0 after a clean run,
+ *   non-zero if a kernel abandoned one of its bounded waits (the outputs of that call are then invalid).
  * phases : MB200_SSD_PHASE_ALL for the operator.  A sequence that is split across devices runs
  *   MB200_SSD_PHASE_LOCAL first (cumulative sums, per-chunk states, and -- with zero incoming state --
  *   the state at the end of the local range into final_states plus the product of the chunk decays
@@ -163,6 +165,29 @@ typedef struct mb200_ssd_args {
 
 int mb200_ssd_scratch_bytes(const mb200_ssd_args *args, size_t *bytes);
 int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream);
+
+/*
+ * SSD chunked scan for callers that cannot allocate device memory.
+ * No counterpart in the reference (its operator allocates its intermediates through PyTorch on every call,
+ * mamba_ssm/ops/triton/ssd_combined.py:374-387).
+ *
+ * Same operator and same argument struct as mb200_ssd_chunk_scan_fwd, but args->scratch and
+ * args->scratch_bytes are ignored: the intermediates live in a buffer of MB200_SSD_STATIC_SCRATCH_BYTES
+ * that is part of the library image, so every device that loads the library carries it until the process
+ * exits.  It is meant for code that runs where allocation is off the table -- a plugin whose host framework
+ * hands it a fixed memory plan, an enqueue callback that must not touch the allocator, a process whose
+ * memory pool is already fully committed -- and only needs modest problem sizes.  A problem whose
+ * mb200_ssd_scratch_bytes() exceeds the buffer is refused with MB200_ERR_BAD_ARG; nothing is launched.
+ * The call performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ * The first call on each device looks up the buffer's device address (one cudaGetSymbolAddress with that
+ * device current); make that first call outside any stream capture.  All calls on a device share the one
+ * buffer: it still holds the previous call's intermediates (the status word is cleared at the start of every
+ * call, nothing else needs to start from zero), and two calls whose kernels overlap on the GPU -- different
+ * streams, or different host threads -- race on it.  Serialise them.
+ */
+#define MB200_SSD_STATIC_SCRATCH_BYTES (32u << 20)
+int mb200_ssd_chunk_scan_fwd_static(const mb200_ssd_args *args, void *stream);
 
 /*
  * Folds an incoming state through a device's local range when a sequence is split across devices:

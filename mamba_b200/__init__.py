@@ -8,6 +8,7 @@ there is no CPU path and no fallback -- a missing library raises on first use.
 """
 from .ops import (  # noqa: F401
     mamba_chunk_scan_combined,
+    mamba_chunk_scan_combined_noalloc,
     selective_scan_fn,
     selective_state_update,
     ssd_finish,

@@ -16,6 +16,7 @@ _DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_NO_DEVICE = 0, -1, -2, -3, -4
 PHASE_LOCAL, PHASE_OUTPUT, PHASE_ALL = 1, 2, 3
+SSD_STATIC_SCRATCH_BYTES = 32 << 20
 
 c_i32, c_i64, c_vp, c_f = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
 
@@ -69,6 +70,7 @@ _PROTOTYPES = {
     "mb200_selective_state_update": (ctypes.c_int, [ctypes.POINTER(SsuArgs), c_vp]),
     "mb200_ssd_scratch_bytes": (ctypes.c_int, [ctypes.POINTER(SsdArgs), ctypes.POINTER(ctypes.c_size_t)]),
     "mb200_ssd_chunk_scan_fwd": (ctypes.c_int, [ctypes.POINTER(SsdArgs), c_vp]),
+    "mb200_ssd_chunk_scan_fwd_static": (ctypes.c_int, [ctypes.POINTER(SsdArgs), c_vp]),
     "mb200_ssd_fold_state": (ctypes.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_vp]),
 }
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)

@@ -419,6 +419,40 @@ extern "C" int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream
     return run_ssd<__half>(a, lay, stream);
 }
 
+// ---- the variant that allocates nothing ---------------------------------------------------------------
+// The intermediates of the SSD stages for callers that cannot allocate: a fixed buffer inside the
+// library image.  In host code this name is only a handle for the runtime, not a device address; the
+// address each device gave it is fetched once per device with cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_ssd_static_scratch[MB200_SSD_STATIC_SCRATCH_BYTES];
+
+extern "C" int mb200_ssd_chunk_scan_fwd_static(const mb200_ssd_args *args, void *stream)
+{
+    using namespace mb200;
+    if (!args) return fail(MB200_ERR_BAD_ARG, "ssd_chunk_scan_fwd_static: args is NULL");
+    if (int rc = check_ssd(*args)) return rc;
+    const size_t need = ssd_scratch_layout(*args).total;
+    if (need > MB200_SSD_STATIC_SCRATCH_BYTES)
+        return fail(MB200_ERR_BAD_ARG,
+                    "ssd_chunk_scan_fwd_static: this problem needs %zu bytes of intermediates, the built-in buffer holds %u; "
+                    "use mb200_ssd_chunk_scan_fwd with caller-owned scratch",
+                    need, (unsigned)MB200_SSD_STATIC_SCRATCH_BYTES);
+    if (args->batch == 0) return MB200_OK;
+    if (int rc = enter_device(args->device)) return rc;
+    // one look-up per device, made with that device current (enter_device did that)
+    static void *device_address[64] = {nullptr};
+    void *ptr = device_address[args->device];
+    if (!ptr) {
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_ssd_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(MB200_ERR_LAUNCH, "ssd_chunk_scan_fwd_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        device_address[args->device] = ptr;
+    }
+    mb200_ssd_args a = *args;
+    a.scratch = ptr;
+    a.scratch_bytes = MB200_SSD_STATIC_SCRATCH_BYTES;
+    return mb200_ssd_chunk_scan_fwd(&a, stream);
+}
+
 extern "C" int mb200_ssd_fold_state(const float *s_in, const float *range_decay, const float *s_local, float *s_out,
                                     int64_t rows, int64_t row, int32_t device, void *stream)
 {

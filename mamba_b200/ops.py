@@ -219,8 +219,17 @@ def ssd_status():
 
 
 def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit,
-                phases, out=None, final_states=None, range_decay=None, scratch=None):
+                phases, out=None, final_states=None, range_decay=None, scratch=None, builtin_scratch=False):
     L.require_cuda(x, dt, A, B, C, D, z, dt_bias, initial_states, seq_idx)
+    if builtin_scratch:
+        # this path must not create device tensors: the caller supplies everything in its final form
+        for name, t, want in (("A", A, torch.float32), ("dt_bias", dt_bias, torch.float32), ("D", D, torch.float32),
+                              ("initial_states", initial_states, torch.float32)):
+            assert t is None or (t.dtype == want and t.is_contiguous()), f"{name} must be contiguous {want}"
+        for name, t in (("x", x), ("z", z), ("B", B), ("C", C)):
+            assert t is None or t.stride(-1) == 1, f"{name} must have a unit last stride"
+        assert out is not None, "out must be supplied"
+        assert seq_idx is None
     B, C = _last_dim_contiguous(B), _last_dim_contiguous(C)
     x, z = _last_dim_contiguous(x), _last_dim_contiguous(z)
     A, dt_bias = _fp32(A).contiguous(), None if dt_bias is None else _fp32(dt_bias).contiguous()
@@ -232,14 +241,15 @@ def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_i
     a.phases = phases
     need = ctypes.c_size_t(0)
     L.check(L.lib().mb200_ssd_scratch_bytes(ctypes.byref(a), ctypes.byref(need)))
-    if scratch is None:
+    if scratch is None and not builtin_scratch:
         scratch = torch.empty(max(need.value, 256), dtype=torch.uint8, device=x.device)
     if out is None and phases & L.PHASE_OUTPUT:
         out = torch.empty_like(x)
     a.x, a.dt, a.A, a.B, a.C = L.ptr(x), L.ptr(dt), L.ptr(A), L.ptr(B), L.ptr(C)
     a.D, a.z, a.dt_bias, a.seq_idx = L.ptr(D), L.ptr(z), L.ptr(dt_bias), L.ptr(seq_idx)
     a.initial_states, a.out, a.final_states = L.ptr(initial_states), L.ptr(out), L.ptr(final_states)
-    a.range_decay, a.scratch, a.scratch_bytes = L.ptr(range_decay), L.ptr(scratch), scratch.numel()
+    a.range_decay = L.ptr(range_decay)
+    a.scratch, a.scratch_bytes = (None, 0) if builtin_scratch else (L.ptr(scratch), scratch.numel())
     L.set_strides(a.x_stride, x, 3)
     L.set_strides(a.dt_stride, dt, 3)
     L.set_strides(a.B_stride, B, 3)
@@ -248,7 +258,8 @@ def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_i
         L.set_strides(a.out_stride, out, 3)
     if z is not None:
         L.set_strides(a.z_stride, z, 3)
-    L.check(L.lib().mb200_ssd_chunk_scan_fwd(ctypes.byref(a), L.stream_ptr(x.device)))
+    entry = L.lib().mb200_ssd_chunk_scan_fwd_static if builtin_scratch else L.lib().mb200_ssd_chunk_scan_fwd
+    L.check(entry(ctypes.byref(a), L.stream_ptr(x.device)))
     global _last_ssd_scratch
     _last_ssd_scratch = scratch
     return out, scratch
@@ -275,6 +286,28 @@ def mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bia
     out, _ = _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus,
                          dt_limit, L.PHASE_ALL, final_states=final_states)
     return out if not return_final_states else (out, final_states)
+
+
+def mamba_chunk_scan_combined_noalloc(x, dt, A, B, C, chunk_size, out, D=None, z=None, dt_bias=None, initial_states=None,
+                                      dt_softplus=False, dt_limit=(0.0, float("inf")), final_states=None):
+    """SSD chunked scan for callers that cannot allocate device memory (mb200_ssd_chunk_scan_fwd_static).
+
+    Some callers have no allocator to turn to at the point where the scan runs: a plugin inside an
+    engine that planned all of its memory up front, a callback that runs on a stream, a process that
+    has already handed every byte of its budget to a pool.  For them the library carries a fixed
+    32 MiB buffer for the scan's intermediates.  This wrapper creates no device tensor either: ``out``
+    (and ``final_states`` fp32 (batch, nheads, headdim, dstate) if wanted) come from the caller, and
+    the parameter tensors must already be contiguous fp32.  Problems whose intermediates exceed the
+    buffer raise AssertionError.  The first call on a device performs a one-time address look-up
+    and should happen before any stream capture.  All calls share the buffer, so two calls that
+    overlap on the GPU (different streams or threads) corrupt each other: keep them in order.
+    """
+    assert out.shape == x.shape and out.dtype == x.dtype and out.stride(-1) == 1
+    if final_states is not None:
+        assert final_states.dtype == torch.float32 and final_states.is_contiguous()
+    _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, None, dt_softplus, dt_limit, L.PHASE_ALL,
+                out=out, final_states=final_states, builtin_scratch=True)
+    return out
 
 
 def ssd_local_states(x, dt, A, B, chunk_size, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf"))):

@@ -52,10 +52,20 @@ def test_argument_errors_without_gpu(built):
     from mamba_b200 import _lib
     a = _lib.ScanArgs()
     rc = _lib.lib().mb200_selective_scan_fwd(ctypes.byref(a), None)
-    assert rc == _lib.ERR_BAD_ARG
-    assert b"NULL" in _lib.lib().mb200_last_error()
+    assert rc == _lib.ERR_BAD_ARG and b"sizes" in _lib.lib().mb200_last_error()
+    a.batch, a.dim, a.seqlen, a.dstate, a.ngroups = 1, 4, 8, 4, 1
+    rc = _lib.lib().mb200_selective_scan_fwd(ctypes.byref(a), None)
+    assert rc == _lib.ERR_BAD_ARG and b"NULL" in _lib.lib().mb200_last_error()
+    a.dstate = 300
+    rc = _lib.lib().mb200_selective_scan_fwd(ctypes.byref(a), None)
+    assert rc == _lib.ERR_BAD_ARG and b"256" in _lib.lib().mb200_last_error()
     with pytest.raises(AssertionError):
         _lib.check(rc)
+    s = _lib.SsdArgs()
+    s.batch, s.seqlen, s.nheads, s.headdim, s.ngroups, s.dstate, s.chunk_size = 64, 1 << 16, 64, 64, 1, 128, 256
+    s.phases = _lib.PHASE_ALL
+    rc = _lib.lib().mb200_ssd_chunk_scan_fwd_static(ctypes.byref(s), None)
+    assert rc == _lib.ERR_BAD_ARG and b"built-in buffer" in _lib.lib().mb200_last_error()
 
 
 def test_cpu_tensors_are_rejected():
