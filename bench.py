@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the scan hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c4|c0] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c0] [--impl ours|reference]
 
 Default workload (the one the headline metric is quoted on): the Mamba-1 selective scan at the
 2.8B-layer shape -- batch 8, d_inner 5120, seqlen 2048, d_state 16, bf16 activations, one B/C group
@@ -112,6 +112,28 @@ class Workload:
             self.step_inputs = ("x", "dt", "z", "B", "C")
             self.alg_bytes = 3 * b * L * H * P * 2 + b * L * H * 2 + 2 * b * L * 128 * 2 + b * H * P * 128 * 4 + 3 * H * 4
             self.launches_per_step = 5
+        elif name == "c3":
+            # long sequence split into contiguous chunk ranges, one per rank; the whole sequence at N=1
+            from mamba_b200.seqpar import split_sequence
+            world = int(os.environ.get("WORLD_SIZE", "1"))
+            rank = int(os.environ.get("RANK", "0"))
+            Ltot, H, P, G, N = 262144, 128, 64, 8, 128
+            lo, hi = split_sequence(Ltot, 256, world, rank)
+            Lr = hi - lo
+            g = torch.Generator(device=dev).manual_seed(1003 + rank)
+            r = lambda *sh: torch.randn(*sh, generator=g, device=dev)
+            bf = torch.bfloat16
+            gh = torch.Generator().manual_seed(1003)
+            host = dict(A=-(1 + 15 * torch.rand(H, generator=gh)), D=torch.randn(H, generator=gh), dt_bias=softplus_inv_dt(H, gh))
+            self.dev_only = dict(x=r(1, Lr, H, P).to(bf), dt=r(1, Lr, H).to(bf), B=r(1, Lr, G, N).to(bf), C=r(1, Lr, G, N).to(bf))
+            self.shape = dict(batch=1, seqlen_total=Ltot, seqlen_this_gpu=Lr, nheads=H, headdim=P, ngroups=G, d_state=N, chunk_size=256)
+            self.tokens = Lr
+            self.desc = "mamba2_ssd_chunk_scan_fwd bf16 b1 L262144 h128 P64 g8 N128 Q256 (no z), sequence split over GPUs"
+            self.dtype = "bf16"
+            self.step_inputs = ("x", "dt", "B", "C")
+            self.alg_bytes = 2 * Lr * H * P * 2 + Lr * H * 2 + 2 * Lr * G * N * 2 + H * P * N * 4 + 3 * H * 4
+            self.launches_per_step = 5 if world == 1 else 7
+            self.world = world
         elif name == "c4":
             host = make_c4(256)
             b, H, P, N = host["state"].shape
@@ -126,6 +148,8 @@ class Workload:
             raise SystemExit(f"unknown workload {name}")
         self.host = host
         self.d = {k: v.to(dev) for k, v in host.items()}
+        if name == "c3":
+            self.d.update(self.dev_only)
         self.step_no = 0
         if name == "c4":
             H, P, N = self.shape["nheads"], self.shape["headdim"], self.shape["d_state"]
@@ -140,6 +164,13 @@ class Workload:
         if self.name in ("c1", "c0"):
             return mb.selective_scan_fn(d["u"], d["delta"], self.d["A"], d["B"], d["C"], self.d["D"], d["z"],
                                         self.d["delta_bias"], delta_softplus=True, return_last_state=True)[0]
+        if self.name == "c3":
+            if self.world == 1:
+                return mb.mamba_chunk_scan_combined(d["x"], d["dt"], self.d["A"], d["B"], d["C"], 256, D=self.d["D"],
+                                                    dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True)[0]
+            from mamba_b200.seqpar import mamba_chunk_scan_sequence_parallel
+            return mamba_chunk_scan_sequence_parallel(d["x"], d["dt"], self.d["A"], d["B"], d["C"], 256, D=self.d["D"],
+                                                      dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True)[0]
         if self.name == "c2":
             return mb.mamba_chunk_scan_combined(d["x"], d["dt"], self.d["A"], d["B"], d["C"], 256, D=self.d["D"], z=d["z"],
                                                 dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True)[0]
@@ -154,7 +185,10 @@ class Workload:
     def pinned_inputs(self):
         out = {}
         for k in self.step_inputs:
-            t = self.host[k] if self.name != "c4" else self.host[k][0]
+            if self.name == "c3":
+                t = self.d[k].cpu()
+            else:
+                t = self.host[k] if self.name != "c4" else self.host[k][0]
             out[k] = t.contiguous().pin_memory()
         return out
 
@@ -170,6 +204,12 @@ def cpu_sample(name, h):
         fn = lambda: tp.selective_scan(sl["u"], sl["delta"], sl["A"], sl["B"], sl["C"], sl["D"], sl["z"],
                                        sl["delta_bias"], delta_softplus=True, return_last_state=True)
         return fn, nb * h["u"].shape[2], f"{nb} of {h['u'].shape[0]} batch rows, all channels, full seqlen"
+    if name == "c3":
+        f = lambda t: t.float()
+        fn = lambda: tp.ssd_chunk_scan(f(h["x"]), f(h["dt"]), h["A"], f(h["B"]), f(h["C"]), 256, h["D"], None, h["dt_bias"],
+                                       dt_softplus=True)
+        L, nh = h["x"].shape[1], h["x"].shape[2]
+        return fn, L * nh / 128, f"first {L} of 262144 tokens x {nh} of 128 heads (one B/C group), fp32-widened inputs"
     if name == "c2":
         nh = 16
         f = lambda t: t.float()
@@ -189,7 +229,15 @@ def cpu_sample(name, h):
     return fn, nb, f"{nb} of 256 batch rows, one step"
 
 
-HOST_INPUTS = {"c0": lambda: make_c0(), "c1": lambda: make_c1(8), "c2": lambda: make_c2(8), "c4": lambda: make_c4(256)}
+def make_c3_sample(L=4096, H=16, P=64, N=128, seed=1003):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    bf = torch.bfloat16
+    return dict(x=r(1, L, H, P).to(bf), dt=r(1, L, H).to(bf), A=-(1 + 15 * torch.rand(H, generator=g)), B=r(1, L, 1, N).to(bf),
+                C=r(1, L, 1, N).to(bf), D=r(H), dt_bias=softplus_inv_dt(H, g))
+
+
+HOST_INPUTS = {"c3": make_c3_sample, "c0": lambda: make_c0(), "c1": lambda: make_c1(8), "c2": lambda: make_c2(8), "c4": lambda: make_c4(256)}
 
 
 # ----------------------------------------------------------------------------------------- clocks
@@ -308,7 +356,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c4"])
+    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -364,8 +412,10 @@ def main():
     line = {
         "metric": metric, "value": world * w.tokens * args.steps / t_dev, "unit": unit, "n_gpus": world,
         "steps": args.steps, "warmup": warmup, "ms_per_step": per_launch_s * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": w.desc, "per_gpu": w.shape, "partition": "batch rows per GPU, no collective",
+        "scaling": "strong" if args.workload == "c3" else "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": w.desc, "per_gpu": w.shape,
+                   "partition": ("contiguous chunk ranges per GPU, range states handed rank to rank by NCCL P2P"
+                                 if args.workload == "c3" else "batch rows per GPU, no collective"),
                    "l2_policy": "inputs_exceed_l2" if w.alg_bytes > 2 * 126e6 else "inputs_fit_l2_not_flushed"},
         "e2e": {"value": world * w.tokens * e2e_steps / t_e2e, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": w.launches_per_step * args.steps,
@@ -374,7 +424,7 @@ def main():
                      "algorithmic_bytes_per_launch": w.alg_bytes},
         "clocks": clk.summary(),
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "c3":
         v, sample, cores = time_cpu(w)
         line["cpu_baseline"] = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample}
     if dist:

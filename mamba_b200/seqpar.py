@@ -1,0 +1,90 @@
+"""SSD chunked scan with the SEQUENCE split across ranks (one process per GPU).
+
+The reference always runs the SSD scan on one device; its inter-chunk recurrence
+``H_{c+1} = exp(sum dA_c) H_c + S_c`` (mamba_ssm/ops/triton/ssd_state_passing.py:72-80) is linear, so a
+contiguous range of chunks can be summarised by ``(range_state, range_decay)`` and
+``initial_states`` (already an input of the operator, ssd_combined.py:368-381) carries the rest:
+
+    rank r:  1. local pass      range_state_r, range_decay_r   (zero incoming state; all ranks in parallel)
+             2. hand-off        recv S_in from r-1;  send  range_decay_r * S_in + range_state_r  to r+1
+             3. output pass     inter-chunk recurrence from S_in, chunk outputs
+
+Step 2 is the only communication: one (batch, nheads, headdim, dstate) fp32 tensor per hop, point to
+point over the process group's backend (NCCL over NVLink between GPUs).  The received state lands in
+this rank's own memory before any kernel reads it.  Every wait in the hand-off is bounded by the
+process group's timeout; a missing predecessor surfaces as ``SequenceHandoffError`` on the waiting
+rank instead of a hang.
+
+The compute steps are injectable so that the hand-off logic can be exercised by CPU ranks (gloo) in
+tests; the defaults are this package's CUDA operators.
+"""
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+
+
+class SequenceHandoffError(RuntimeError):
+    """The state hand-off between neighbouring ranks failed (peer missing, timed out, or mismatched)."""
+
+
+@dataclass
+class SsdSteps:
+    """The three compute steps of a rank; defaults are the CUDA operators of this package."""
+    local: Callable = ops.ssd_local_states
+    fold: Callable = ops.ssd_fold_state
+    finish: Callable = ops.ssd_finish
+
+
+def split_sequence(seqlen: int, chunk_size: int, world: int, rank: int):
+    """Contiguous range of whole chunks ``[start, stop)`` (in tokens) that `rank` owns."""
+    nchunks = (seqlen + chunk_size - 1) // chunk_size
+    per, extra = divmod(nchunks, world)
+    first = rank * per + min(rank, extra)
+    count = per + (1 if rank < extra else 0)
+    return min(first * chunk_size, seqlen), min((first + count) * chunk_size, seqlen)
+
+
+def _recv_state(like: torch.Tensor, src: int, group) -> torch.Tensor:
+    buf = torch.empty_like(like)
+    try:
+        dist.recv(buf, src=src, group=group)
+    except Exception as e:  # timeout, peer gone, transport error
+        raise SequenceHandoffError(f"rank {dist.get_rank(group)}: no state from rank {src}: {e}") from e
+    return buf
+
+
+def _send_state(t: torch.Tensor, dst: int, group) -> None:
+    try:
+        dist.send(t.contiguous(), dst=dst, group=group)
+    except Exception as e:
+        raise SequenceHandoffError(f"rank {dist.get_rank(group)}: could not hand the state to rank {dst}: {e}") from e
+
+
+def mamba_chunk_scan_sequence_parallel(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
+                                       dt_softplus=False, dt_limit=(0.0, float("inf")), return_final_states=False,
+                                       group=None, steps: Optional[SsdSteps] = None):
+    """Run this rank's slice of a sequence that is split over the ranks of `group`.
+
+    x, dt, B, C, z hold THIS rank's contiguous tokens (a whole number of chunks on every rank but the
+    last); A, D, dt_bias are replicated; ``initial_states`` (state before the first token of the whole
+    sequence) is only read on rank 0.  Returns this rank's ``out`` and, if asked, the state after this
+    rank's last token -- on the last rank that is the final state of the whole sequence.
+    """
+    steps = steps or SsdSteps()
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    if rank < world - 1:
+        assert x.shape[1] % chunk_size == 0, "every rank but the last must hold whole chunks"
+    range_state, range_decay, scratch = steps.local(x, dt, A, B, chunk_size, dt_bias=dt_bias, dt_softplus=dt_softplus,
+                                                    dt_limit=dt_limit)
+    if rank == 0:
+        incoming = None if initial_states is None else initial_states.to(range_state.dtype)
+    else:
+        incoming = _recv_state(range_state, rank - 1, group)
+    if rank < world - 1:
+        _send_state(steps.fold(incoming, range_decay, range_state), rank + 1, group)
+    return steps.finish(x, dt, A, B, C, chunk_size, scratch, D=D, z=z, dt_bias=dt_bias, incoming_state=incoming,
+                        dt_softplus=dt_softplus, dt_limit=dt_limit, return_final_states=return_final_states)
