@@ -11,12 +11,13 @@
 //               thread issues 16 MMAs (M=128 over n, N=64 over p, both operands MN-major).
 //   chunk_scan  per (batch, chunk, head, 128-row block):  Y1 = C . H^T (state entering the chunk),
 //               Y2 = (CB o L) . X with L[m,k] = exp(min(dA_m - dA_k, 0)) dt_k [k <= m] applied in place to
-//               the CB blocks as they land in a 3-slot ring; out = exp(dA_m) Y1 + Y2 + D x, gated by
-//               silu(z).  Y1 and Y2 live in 128 TMEM columns; two CTAs share an SM so one CTA's
-//               element-wise pass overlaps the other's loads and MMAs.
+//               the CB blocks as they land; out = exp(dA_m) Y1 + Y2 + D x, gated by silu(z).  Y1 and Y2
+//               live in 128 TMEM columns; two CTAs share an SM so one CTA's element-wise pass overlaps
+//               the other's loads and MMAs.
 //
-// Thread roles (160 threads): warps 0-3 own TMEM lanes 0-127 (one matrix row each) for the
-// element-wise work and the epilogue; warp 4 allocates TMEM and its lane 0 issues TMA and MMA.
+// Thread roles: the first warps own the TMEM lanes (one matrix row per thread; chunk_scan uses two
+// threads per row) for the element-wise work and the epilogue; the last warp allocates TMEM and its
+// lane 0 issues TMA and MMA.
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the status word of the
 // scratch buffer, skips the dependent work and still releases its TMEM before it exits.
 #include "ssd_common.cuh"
@@ -56,6 +57,12 @@ static bool encode_16bit(CUtensorMap *map, int fmt, const void *base, int rank, 
     return r == CUDA_SUCCESS;
 }
 
+#ifdef MB200_SCAN_TRACE
+// Experiment aid: nanosecond stamps of the producer lane (slots 0-7) and of compute thread 0 (slots 8-15)
+// for the first 4096 CTAs of the chunk-scan kernel, read back by the experiment harness.
+__device__ unsigned long long g_scan_trace[4096 * 16];
+#endif
+
 namespace {
 
 using namespace tc;
@@ -68,6 +75,11 @@ enum { kStBarB = 11, kStBarX, kStBarScaled, kStBarDone, kStBarC, kStBarG1, kStBa
 
 template <typename T> struct Pack2;
 template <> struct Pack2<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b)   // two 16-bit products, one instruction
+    {
+        __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
     static __device__ __forceinline__ float2 unpack(uint32_t v) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&v)); }
     static __device__ __forceinline__ uint32_t pack(float a, float b)
     {
@@ -76,6 +88,11 @@ template <> struct Pack2<__nv_bfloat16> {
     }
 };
 template <> struct Pack2<__half> {
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b)
+    {
+        __half2 r = __hmul2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
     static __device__ __forceinline__ float2 unpack(uint32_t v) { return __half22float2(*reinterpret_cast<__half2 *>(&v)); }
     static __device__ __forceinline__ uint32_t pack(float a, float b)
     {
@@ -273,8 +290,15 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __
 
 // ====================================================================================== chunk scan
 // grid (nheads, nchunks * 2, batch), 288 threads: warps 0-7 element-wise + epilogue (thread = one row and one
-// 32-column half), warp 8 TMA + MMA.  smem: x 32 KB | 48 KB region = {C 2 x 16 KB, H 2 x 8 KB}, reused as a
-// 3-slot ring of CB blocks once Y1 is done | dA*log2e, dt, column factors (3 KB) | barriers.  TMEM: 128 columns.
+// 32-column half), warp 8 TMA + MMA.  smem: C 2 x 16 KB | H 2 x 8 KB | 2 block slots, each {CB block
+// [128 x 64] 16 KB, x rows [64 x 64] 8 KB} | dA*log2e, dt, column factors (3 KB) | barriers: 100 KB, two CTAs
+// per SM.  Everything a CTA needs first (C, H, blocks 0 and 1) is requested at once; the second row block's
+// blocks 2 and 3 land in the C/H area as soon as Y1 = C.H^T has been issued and finished, so no slot is ever
+// re-used and the element-wise warps never wait for a slot to drain.  x travels with the CB block it
+// multiplies; the row block's own x rows (needed for D x) are in the last two blocks, still resident at the
+// end.  TMEM: 128 columns.
+// The mask factors are rounded to the input dtype and applied with packed 16-bit multiplies (two roundings
+// per element instead of one; far inside the 16-bit tolerance, and it halves the instruction count).
 //
 // Decay mask.  A thread owns 32 consecutive columns k of one row m per CB block.  Three cases:
 //   all k > m           zeros
@@ -284,6 +308,15 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __
 //                       not hold is detected and sent down the exact path.
 //   range holds k = m   exact: exp(min(dA_m - dA_k, 0)) dt_k [k <= m] per element
 constexpr int kScanThreads = 288;
+#ifdef MB200_SCAN_TRACE
+#define MB200_TRACE(slot)                                                                                         \
+    do {                                                                                                          \
+        const unsigned cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                     \
+        if (cta_ < 4096) g_scan_trace[cta_ * 16 + (slot)] = global_ns();                                          \
+    } while (0)
+#else
+#define MB200_TRACE(slot) do { } while (0)
+#endif
 __device__ __forceinline__ void scan_compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <typename T>
@@ -294,30 +327,42 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = align1024(smem_raw);
-    uint8_t *xs = sm;                          // [256 x 64], rows k
-    uint8_t *R1 = sm + 32768;                  // 48 KB
-    float *dA2 = reinterpret_cast<float *>(sm + 81920);   // 256: dA_cumsum * log2(e)
+    uint8_t *Cs = sm;                          // 2 boxes [128 x 64]
+    uint8_t *Hs = sm + 32768;                  // 2 boxes [64 x 64]
+    constexpr uint32_t kSlot = 24576, kSlotX = 16384;   // a slot: CB block, then 64 rows of x
+    // blocks 0,1 have their own slots; blocks 2,3 re-use the C/H area once Y1 is complete
+    auto slot_ptr = [&](int j) -> uint8_t * { return j < 2 ? sm + 49152 + j * kSlot : sm + (j - 2) * kSlot; };
+    float *dA2 = reinterpret_cast<float *>(sm + 98304);   // 256: dA_cumsum * log2(e)
     float *dts = dA2 + 256;                               // 256: dt
     float *cks = dts + 256;                               // 256: exp(dA_ref(k) - dA_k) dt_k, ref(k) = k | 31
     int *mono = reinterpret_cast<int *>(cks + 256);       // 1 while dA_cumsum is non-increasing over the chunk
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 81920 + 3072 + 64);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 98304 + 3072 + 64);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
-    uint64_t *bar_c = &bars[0], *bar_x = &bars[1], *bar_g1 = &bars[2], *bar_g2 = &bars[3];
-    uint64_t *bar_full = &bars[4], *bar_scaled = &bars[7], *bar_empty = &bars[10];
+    uint64_t *bar_c = &bars[0], *bar_g1 = &bars[1], *bar_g2 = &bars[3];
+    uint64_t *bar_full = &bars[4], *bar_scaled = &bars[8];
 
     const int h = blockIdx.x, c = blockIdx.y >> 1, mb = blockIdx.y & 1, b = blockIdx.z;
     const int g = h / (a.nheads / a.ngroups);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nk = (mb + 1) * 2;   // 64-wide CB blocks this row block needs
+    // chunk scalars are requested before the set-up barrier so their latency hides behind it
+    const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
+    const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
+    float pre_dk = 0.f, pre_tk = 0.f, pre_ref = 0.f, pre_prev = 0.f;
+    if (threadIdx.x < 256) {
+        const int k = threadIdx.x;
+        pre_dk = dAc[k];
+        pre_tk = dtc[k];
+        pre_ref = dAc[k | 31];
+        pre_prev = k > 0 ? dAc[k - 1] : pre_dk;
+    }
     if (threadIdx.x == 256) {
         mbar_init(bar_c, 1);
-        mbar_init(bar_x, 1);
         mbar_init(bar_g1, 1);
         mbar_init(bar_g2, 1);
-        for (int i = 0; i < 3; ++i) {
+        for (int i = 0; i < 4; ++i) {
             mbar_init(&bar_full[i], 1);
             mbar_init(&bar_scaled[i], 256);
-            mbar_init(&bar_empty[i], 1);
         }
         *mono = 1;
         mbar_fence_init();
@@ -333,66 +378,66 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     if (warp == 8) {
         if (lane == 0) {
             bool ok = true;
+            MB200_TRACE(0);
             mbar_expect_tx(bar_c, 32768 + 16384);
             for (int kb = 0; kb < 2; ++kb) {
-                tma_load_4d(R1 + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
-                tma_load_3d(R1 + 32768 + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
+                tma_load_4d(Cs + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
+                tma_load_3d(Hs + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
             }
-            mbar_expect_tx(bar_x, (mb + 1) * 16384);
-            for (int r = 0; r <= mb; ++r) tma_load_4d(xs + r * 16384, &tm_x, bar_x, 0, h, c * kQ + r * 128, b);
+            auto load_block = [&](int j) {
+                mbar_expect_tx(&bar_full[j], 16384 + 8192);
+                tma_load_3d(slot_ptr(j), &tm_CB, &bar_full[j], j * 64, mb * 128, (int)unit_g);
+                tma_load_4d(slot_ptr(j) + kSlotX, &tm_x, &bar_full[j], 0, h, c * kQ + j * 64, b);
+            };
+            load_block(0);
+            load_block(1);
             // Y1 = C . H^T
             ok = ok && mbar_wait(bar_c, 0, status, kStBarC);
+            MB200_TRACE(1);
             if (ok) {
                 tc_fence_after_sync();
                 const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 0, 0);
                 for (int kb = 0; kb < 2; ++kb)
                     for (int s = 0; s < 4; ++s)
-                        mma_f16_ss(tmem, smem_desc_sw128(smem_u32(R1 + kb * 16384) + s * 32, 16, 1024),
-                                   smem_desc_sw128(smem_u32(R1 + 32768 + kb * 8192) + s * 32, 16, 1024), idesc, (kb | s) != 0);
+                        mma_f16_ss(tmem, smem_desc_sw128(smem_u32(Cs + kb * 16384) + s * 32, 16, 1024),
+                                   smem_desc_sw128(smem_u32(Hs + kb * 8192) + s * 32, 16, 1024), idesc, (kb | s) != 0);
             }
-            mma_commit(bar_g1);
-            ok = ok && mbar_wait(bar_g1, 0, status, kStBarG1);   // C / H no longer read: the region becomes the CB ring
-            if (ok) {
-                for (int j = 0; j < nk && j < 3; ++j) {
-                    mbar_expect_tx(&bar_full[j], 16384);
-                    tma_load_3d(R1 + j * 16384, &tm_CB, &bar_full[j], j * 64, mb * 128, (int)unit_g);
+            if (nk > 2) {
+                mma_commit(bar_g1);
+                ok = ok && mbar_wait(bar_g1, 0, status, kStBarG1);   // C / H have been read: their area takes blocks 2, 3
+                if (ok) {
+                    load_block(2);
+                    load_block(3);
                 }
             }
-            ok = ok && mbar_wait(bar_x, 0, status, kStBarX);
+            MB200_TRACE(2);
+            // Y2 += (CB o L) . X, block by block as the element-wise warps release them
             const uint32_t idesc2 = instr_desc_f16(128, 64, Fmt<T>::v, 0, 1);
             for (int j = 0; j < nk; ++j) {
-                const int slot = j % 3;
-                ok = ok && mbar_wait(&bar_scaled[slot], (j / 3) & 1, status, kStBarScaled);
+                ok = ok && mbar_wait(&bar_scaled[j], 0, status, kStBarScaled);
+                if (j == 0) MB200_TRACE(3);
                 if (ok) {
                     tc_fence_after_sync();
+                    const uint32_t sb = smem_u32(slot_ptr(j));
                     for (int s = 0; s < 4; ++s)
-                        mma_f16_ss(tmem + 64, smem_desc_sw128(smem_u32(R1 + slot * 16384) + s * 32, 16, 1024),
-                                   smem_desc_sw128(smem_u32(xs) + (j * 64 + s * 16) * 128, 16, 1024), idesc2, (j | s) != 0);
-                }
-                mma_commit(&bar_empty[slot]);
-                if (j + 3 < nk) {
-                    ok = ok && mbar_wait(&bar_empty[slot], 0, status, kStBarEmpty);
-                    if (ok) {
-                        mbar_expect_tx(&bar_full[slot], 16384);
-                        tma_load_3d(R1 + slot * 16384, &tm_CB, &bar_full[slot], (j + 3) * 64, mb * 128, (int)unit_g);
-                    }
+                        mma_f16_ss(tmem + 64, smem_desc_sw128(sb + s * 32, 16, 1024),
+                                   smem_desc_sw128(sb + kSlotX + s * 2048, 16, 1024), idesc2, (j | s) != 0);
                 }
             }
             mma_commit(bar_g2);
+            MB200_TRACE(4);
         }
     } else {
+        if (threadIdx.x == 0) MB200_TRACE(8);
         const int r = threadIdx.x & 127;    // row inside the block = TMEM lane
         const int kh = threadIdx.x >> 7;    // which 32-column half of every 64-wide block
         const int m = mb * 128 + r;         // row inside the chunk
-        const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
-        const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
         {
             const int k = threadIdx.x;
-            const float dk = dAc[k], tk = dtc[k];
-            dA2[k] = dk * kLog2e;
-            dts[k] = tk;
-            cks[k] = __expf(dAc[k | 31] - dk) * tk;
-            if (k > 0 && dk > dAc[k - 1]) *mono = 0;
+            dA2[k] = pre_dk * kLog2e;
+            dts[k] = pre_tk;
+            cks[k] = __expf(pre_ref - pre_dk) * pre_tk;
+            if (pre_dk > pre_prev) *mono = 0;
         }
         // The gate row and D do not depend on the MMAs: request them now so the epilogue finds them in
         // registers instead of paying a DRAM round trip per packet.
@@ -409,32 +454,35 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         }
         const float Dh = (a.D && !a.D_has_hdim) ? a.D[h] : 0.f;
         scan_compute_sync();
+        if (threadIdx.x == 0) MB200_TRACE(9);
         const float dAm = dA2[m];
         const bool factor_ok = *mono != 0;
         bool ok = true;
         for (int j = 0; j < nk; ++j) {
-            const int slot = j % 3;
             const int klo = j * 64 + kh * 32;       // first column of this thread's range
-            ok = ok && mbar_wait(&bar_full[slot], (j / 3) & 1, status, kStBarFull);
-            const uint32_t rowaddr = smem_u32(R1 + slot * 16384) + r * 128;
+            ok = ok && mbar_wait(&bar_full[j], 0, status, kStBarFull);
+            if (threadIdx.x == 0 && j == 0) MB200_TRACE(10);
+            const uint32_t rowaddr = smem_u32(slot_ptr(j)) + r * 128;
             if (ok) {
                 if (klo > m) {
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) sts128(rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4), make_uint4(0, 0, 0, 0));
                 } else if (klo + 31 <= m && factor_ok) {
                     const float rm = ex2(dAm - dA2[klo + 31]);
+                    const uint64_t rm2 = pack2(rm, rm);
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) {
                         const uint32_t addr = rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4);
                         uint4 v = lds128(addr);
                         uint32_t *e = reinterpret_cast<uint32_t *>(&v);
-                        const int kc = klo + ch * 8;
-                        const float4 c0 = *reinterpret_cast<const float4 *>(cks + kc), c1 = *reinterpret_cast<const float4 *>(cks + kc + 4);
-                        const float ck[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                        const ulonglong2 *ck = reinterpret_cast<const ulonglong2 *>(cks + klo + ch * 8);
+                        const ulonglong2 c01 = ck[0], c23 = ck[1];
+                        const uint64_t cp[4] = {c01.x, c01.y, c23.x, c23.y};
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            const float2 f = Pack2<T>::unpack(e[q]);
-                            e[q] = Pack2<T>::pack(f.x * (rm * ck[2 * q]), f.y * (rm * ck[2 * q + 1]));
+                            float l0, l1;
+                            unpack2(mul2(rm2, cp[q]), l0, l1);
+                            e[q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
                         }
                         sts128(addr, v);
                     }
@@ -451,29 +499,30 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         const float tk[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            const float2 f = Pack2<T>::unpack(e[q]);
                             const float l0 = (kc + 2 * q <= m) ? ex2(fminf(dAm - dk[2 * q], 0.f)) * tk[2 * q] : 0.f;
                             const float l1 = (kc + 2 * q + 1 <= m) ? ex2(fminf(dAm - dk[2 * q + 1], 0.f)) * tk[2 * q + 1] : 0.f;
-                            e[q] = Pack2<T>::pack(f.x * l0, f.y * l1);
+                            e[q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
                         }
                         sts128(addr, v);
                     }
                 }
             }
             fence_proxy_async();
-            mbar_arrive(&bar_scaled[slot]);
+            mbar_arrive(&bar_scaled[j]);
         }
+        if (threadIdx.x == 0) MB200_TRACE(11);
         ok = ok && mbar_wait(bar_g2, 0, status, kStBarG2);
+        if (threadIdx.x == 0) MB200_TRACE(12);
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: the whole warp takes one path
         tc_fence_after_sync();
         if (ok) {
             float y1[32], y2[32];
             const uint32_t tl = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * 32;
-            tmem_ld32(tl, y1);
-            tmem_ld32(tl + 64, y2);
+            tmem_ld32_pair(tl, tl + 64, y1, y2);
             if (live) {
                 const float scale = ex2(dAm);
-                const uint32_t xrow = smem_u32(xs) + m * 128;
+                // row m of x sits in the slot that carried block m / 64 (the last two blocks stay resident)
+                const uint32_t xrow = smem_u32(slot_ptr(m >> 6) + kSlotX) + (m & 63) * 128;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     const int p0 = kh * 32 + q4 * 8;   // column inside the head
@@ -521,10 +570,12 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             }
         }
     }
+    if (threadIdx.x == 0) MB200_TRACE(13);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 8) tmem_dealloc(tmem, 128);
 }
+
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 bool mult8(const int64_t *s, int n)
@@ -554,8 +605,8 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
     {
         const uint64_t d[4] = {(uint64_t)kP, (uint64_t)a.nheads, L, (uint64_t)a.batch};
         const uint64_t s[3] = {(uint64_t)a.x_stride[2] * 2, (uint64_t)a.x_stride[1] * 2, (uint64_t)a.x_stride[0] * 2};
-        const uint32_t bx256[4] = {64, 1, 256, 1}, bx128[4] = {64, 1, 128, 1};
-        if (!encode_16bit(&tx, fmt, a.x, 4, d, s, stage == 0 ? bx256 : bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for x failed");
+        const uint32_t bx256[4] = {64, 1, 256, 1}, bx64[4] = {64, 1, 64, 1};
+        if (!encode_16bit(&tx, fmt, a.x, 4, d, s, stage == 0 ? bx256 : bx64)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for x failed");
     }
     {
         const uint64_t d[4] = {(uint64_t)kN, (uint64_t)a.ngroups, L, (uint64_t)a.batch};
@@ -565,7 +616,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
         if (!encode_16bit(&tB, fmt, a.B, 4, d, sB, stage == 0 ? bx256 : bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for B failed");
         if (!encode_16bit(&tC, fmt, a.C, 4, d, sC, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for C failed");
     }
-    const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = 81920 + 3072 + 64 + 256 + 1024;
+    const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = 98304 + 3072 + 64 + 256 + 1024;
     if (stage == 0) {
         cudaFuncSetAttribute(ssd_tc_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state);
         ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kThreadsTc, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
@@ -617,3 +668,11 @@ int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, cudaStrea
 }
 
 }  // namespace mb200
+
+#ifdef MB200_SCAN_TRACE
+// Experiment aid (only in trace builds): copies the chunk-scan time stamps to the host.
+extern "C" int mb200_debug_scan_trace(unsigned long long *host_dst)
+{
+    return cudaMemcpyFromSymbol(host_dst, mb200::g_scan_trace, sizeof(mb200::g_scan_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
