@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __
     if (threadIdx.x == 128) {
         mbar_init(&bars[0], 1);      // B landed
         mbar_init(&bars[1], 1);      // x landed
-        mbar_init(&bars[2], 128);    // B rows scaled
+        mbar_init(&bars[2], 4);      // B rows scaled: one arrival per element-wise warp
         mbar_init(&bars[3], 1);      // MMAs done
         mbar_fence_init();
     }
@@ -268,7 +268,8 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __
             }
         }
         fence_proxy_async();
-        mbar_arrive(&bars[2]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[2]);
         const bool done = mbar_wait(&bars[3], 0, status, kStBarDone);
         tc_fence_after_sync();
         if (__all_sync(0xffffffffu, ok && done)) {   // tcgen05.ld is warp-collective
@@ -320,9 +321,10 @@ constexpr int kScanThreads = 288;
 __device__ __forceinline__ void scan_compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kScanThreads, 2)
 ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_C,
-                         const __grid_constant__ CUtensorMap tm_H, const __grid_constant__ CUtensorMap tm_CB, const mb200_ssd_args a,
+                         const __grid_constant__ CUtensorMap tm_H, const __grid_constant__ CUtensorMap tm_CB,
+                         const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_out, const mb200_ssd_args a,
                          const float *dtb, const float *dAb, int nchunks, int *status)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -338,7 +340,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     int *mono = reinterpret_cast<int *>(cks + 256);       // 1 while dA_cumsum is non-increasing over the chunk
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 98304 + 3072 + 64);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
-    uint64_t *bar_c = &bars[0], *bar_g1 = &bars[1], *bar_g2 = &bars[3];
+    uint64_t *bar_c = &bars[0], *bar_g1 = &bars[1], *bar_z = &bars[2], *bar_g2 = &bars[3], *bar_e0 = &bars[12];
     uint64_t *bar_full = &bars[4], *bar_scaled = &bars[8];
 
     const int h = blockIdx.x, c = blockIdx.y >> 1, mb = blockIdx.y & 1, b = blockIdx.z;
@@ -359,10 +361,12 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     if (threadIdx.x == 256) {
         mbar_init(bar_c, 1);
         mbar_init(bar_g1, 1);
+        mbar_init(bar_z, 1);
+        mbar_init(bar_e0, 1);
         mbar_init(bar_g2, 1);
         for (int i = 0; i < 4; ++i) {
             mbar_init(&bar_full[i], 1);
-            mbar_init(&bar_scaled[i], 256);
+            mbar_init(&bar_scaled[i], 8);      // one arrival per element-wise warp
         }
         *mono = 1;
         mbar_fence_init();
@@ -379,11 +383,8 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         if (lane == 0) {
             bool ok = true;
             MB200_TRACE(0);
-            mbar_expect_tx(bar_c, 32768 + 16384);
-            for (int kb = 0; kb < 2; ++kb) {
-                tma_load_4d(Cs + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
-                tma_load_3d(Hs + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
-            }
+            // The first two mask blocks are what the element-wise warps wait for, so they are requested first;
+            // C and H (for Y1, which nothing needs before the epilogue) follow.
             auto load_block = [&](int j) {
                 mbar_expect_tx(&bar_full[j], 16384 + 8192);
                 tma_load_3d(slot_ptr(j), &tm_CB, &bar_full[j], j * 64, mb * 128, (int)unit_g);
@@ -391,6 +392,22 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             };
             load_block(0);
             load_block(1);
+            mbar_expect_tx(bar_c, 32768 + 16384);
+            for (int kb = 0; kb < 2; ++kb) {
+                tma_load_4d(Cs + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
+                tma_load_3d(Hs + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
+            }
+            const uint32_t idesc2 = instr_desc_f16(128, 64, Fmt<T>::v, 0, 1);
+            auto gemm2_block = [&](int j) {      // Y2 += (CB o L)_j . X_j once the element-wise warps release block j
+                ok = ok && mbar_wait(&bar_scaled[j], 0, status, kStBarScaled);
+                if (ok) {
+                    tc_fence_after_sync();
+                    const uint32_t sb = smem_u32(slot_ptr(j));
+                    for (int s = 0; s < 4; ++s)
+                        mma_f16_ss(tmem + 64, smem_desc_sw128(sb + s * 32, 16, 1024),
+                                   smem_desc_sw128(sb + kSlotX + s * 2048, 16, 1024), idesc2, (j | s) != 0);
+                }
+            };
             // Y1 = C . H^T
             ok = ok && mbar_wait(bar_c, 0, status, kStBarC);
             MB200_TRACE(1);
@@ -411,17 +428,19 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 }
             }
             MB200_TRACE(2);
-            // Y2 += (CB o L) . X, block by block as the element-wise warps release them
-            const uint32_t idesc2 = instr_desc_f16(128, 64, Fmt<T>::v, 0, 1);
             for (int j = 0; j < nk; ++j) {
-                ok = ok && mbar_wait(&bar_scaled[j], 0, status, kStBarScaled);
-                if (j == 0) MB200_TRACE(3);
-                if (ok) {
-                    tc_fence_after_sync();
-                    const uint32_t sb = smem_u32(slot_ptr(j));
-                    for (int s = 0; s < 4; ++s)
-                        mma_f16_ss(tmem + 64, smem_desc_sw128(sb + s * 32, 16, 1024),
-                                   smem_desc_sw128(sb + kSlotX + s * 2048, 16, 1024), idesc2, (j | s) != 0);
+                gemm2_block(j);
+                if (j == 0) {
+                    MB200_TRACE(3);
+                    if (a.z) mma_commit(bar_e0);
+                }
+                if (j == 1 && a.z) {
+                    // block 0 has been multiplied: its CB area now receives the gate tile for the epilogue
+                    ok = ok && mbar_wait(bar_e0, 0, status, kStBarEmpty);
+                    if (ok) {
+                        mbar_expect_tx(bar_z, 16384);
+                        tma_load_4d(slot_ptr(0), &tm_z, bar_z, 0, h, c * kQ + mb * 128, b);
+                    }
                 }
             }
             mma_commit(bar_g2);
@@ -439,19 +458,8 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             cks[k] = __expf(pre_ref - pre_dk) * pre_tk;
             if (pre_dk > pre_prev) *mono = 0;
         }
-        // The gate row and D do not depend on the MMAs: request them now so the epilogue finds them in
-        // registers instead of paying a DRAM round trip per packet.
         const int t = c * kQ + m;
-        const bool live = t < a.seqlen;     // rows past the end of the sequence load TMEM with the warp but touch no memory
-        const int tcl = live ? t : 0;
-        const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)tcl * a.z_stride[1] + (int64_t)h * a.z_stride[2] + kh * 32 : nullptr;
-        T *orow = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)tcl * a.out_stride[1] + (int64_t)h * a.out_stride[2] + kh * 32;
-        const bool zo_vec = ((reinterpret_cast<uintptr_t>(orow) | reinterpret_cast<uintptr_t>(zrow)) & 15) == 0;
-        uint4 zv[4] = {};
-        if (zrow && live && zo_vec) {
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) zv[q4] = *reinterpret_cast<const uint4 *>(zrow + q4 * 8);
-        }
+        const bool live = t < a.seqlen;     // rows past the end of the sequence compute garbage that the tile store clips
         const float Dh = (a.D && !a.D_has_hdim) ? a.D[h] : 0.f;
         scan_compute_sync();
         if (threadIdx.x == 0) MB200_TRACE(9);
@@ -508,66 +516,69 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 }
             }
             fence_proxy_async();
-            mbar_arrive(&bar_scaled[j]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_scaled[j]);
         }
         if (threadIdx.x == 0) MB200_TRACE(11);
         ok = ok && mbar_wait(bar_g2, 0, status, kStBarG2);
         if (threadIdx.x == 0) MB200_TRACE(12);
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: the whole warp takes one path
         tc_fence_after_sync();
+        if (a.z) ok = ok && mbar_wait(bar_z, 0, status, kStBarX);
+        ok = __all_sync(0xffffffffu, ok);
+        // Outputs are assembled as a [128 x 64] tile in the CB area of block 1 (free: every MMA has finished)
+        // and leave through one TMA store; the gate tile sits in the CB area of block 0.
+        uint8_t *ztile = slot_ptr(0), *otile = slot_ptr(1);
         if (ok) {
             float y1[32], y2[32];
             const uint32_t tl = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * 32;
             tmem_ld32_pair(tl, tl + 64, y1, y2);
-            if (live) {
-                const float scale = ex2(dAm);
-                // row m of x sits in the slot that carried block m / 64 (the last two blocks stay resident)
-                const uint32_t xrow = smem_u32(slot_ptr(m >> 6) + kSlotX) + (m & 63) * 128;
+            if (threadIdx.x == 0) MB200_TRACE(14);
+            const float scale = ex2(dAm);
+            // row m of x sits in the slot that carried block m / 64 (the last two blocks stay resident)
+            const uint32_t xrow = smem_u32(slot_ptr(m >> 6) + kSlotX) + (m & 63) * 128;
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int p0 = kh * 32 + q4 * 8;   // column inside the head
-                    float y[8];
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int p0 = kh * 32 + q4 * 8;   // column inside the head
+                const uint32_t swz = (uint32_t)(((p0 >> 3) ^ (r & 7)) << 4);
+                float y[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) y[i] = fmaf(scale, y1[q4 * 8 + i], y2[q4 * 8 + i]);
-                    if (a.D) {
-                        const uint4 xv = lds128(xrow + (((p0 >> 3) ^ (m & 7)) << 4));
-                        const uint32_t *xe = reinterpret_cast<const uint32_t *>(&xv);
+                for (int i = 0; i < 8; ++i) y[i] = fmaf(scale, y1[q4 * 8 + i], y2[q4 * 8 + i]);
+                if (a.D) {
+                    const uint4 xv = lds128(xrow + swz);
+                    const uint32_t *xe = reinterpret_cast<const uint32_t *>(&xv);
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float2 f = Pack2<T>::unpack(xe[q]);
-                            const float D0 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q] : Dh;
-                            const float D1 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q + 1] : Dh;
-                            y[2 * q] = fmaf(f.x, D0, y[2 * q]);
-                            y[2 * q + 1] = fmaf(f.y, D1, y[2 * q + 1]);
-                        }
-                    }
-                    if (zrow) {
-                        if (zo_vec) {
-                            const uint32_t *ze = reinterpret_cast<const uint32_t *>(&zv[q4]);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const float2 f = Pack2<T>::unpack(ze[q]);
-                                y[2 * q] *= fast_silu(f.x);
-                                y[2 * q + 1] *= fast_silu(f.y);
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) y[i] *= fast_silu(to_float(zrow[q4 * 8 + i]));
-                        }
-                    }
-                    if (zo_vec) {
-                        uint4 o;
-                        o.x = Pack2<T>::pack(y[0], y[1]);
-                        o.y = Pack2<T>::pack(y[2], y[3]);
-                        o.z = Pack2<T>::pack(y[4], y[5]);
-                        o.w = Pack2<T>::pack(y[6], y[7]);
-                        *reinterpret_cast<uint4 *>(orow + q4 * 8) = o;
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) orow[q4 * 8 + i] = from_float<T>(y[i]);
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 f = Pack2<T>::unpack(xe[q]);
+                        const float D0 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q] : Dh;
+                        const float D1 = a.D_has_hdim ? a.D[h * kP + p0 + 2 * q + 1] : Dh;
+                        y[2 * q] = fmaf(f.x, D0, y[2 * q]);
+                        y[2 * q + 1] = fmaf(f.y, D1, y[2 * q + 1]);
                     }
                 }
+                if (a.z) {
+                    const uint4 zv = lds128(smem_u32(ztile) + r * 128 + swz);
+                    const uint32_t *ze = reinterpret_cast<const uint32_t *>(&zv);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 f = Pack2<T>::unpack(ze[q]);
+                        y[2 * q] *= fast_silu(f.x);
+                        y[2 * q + 1] *= fast_silu(f.y);
+                    }
+                }
+                uint4 o;
+                o.x = Pack2<T>::pack(y[0], y[1]);
+                o.y = Pack2<T>::pack(y[2], y[3]);
+                o.z = Pack2<T>::pack(y[4], y[5]);
+                o.w = Pack2<T>::pack(y[6], y[7]);
+                sts128(smem_u32(otile) + r * 128 + swz, o);
             }
+        }
+        fence_proxy_async();
+        scan_compute_sync();
+        if (threadIdx.x == 0 && ok && live) {      // thread 0 owns the block's first row: a block wholly past the end stores nothing
+            tma_store_4d(&tm_out, otile, 0, h, c * kQ + mb * 128, b);
+            tma_store_commit_and_wait_read();
         }
     }
     if (threadIdx.x == 0) MB200_TRACE(13);
@@ -601,7 +612,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
     int *status = reinterpret_cast<int *>(base + lay.off_status);
     const int nc = lay.nchunks, fmt = Fmt<T>::v;
     const uint64_t L = a.seqlen;
-    CUtensorMap tx, tB, tC, tH, tCB;
+    CUtensorMap tx, tB, tC, tH, tCB, tz, tout;
     {
         const uint64_t d[4] = {(uint64_t)kP, (uint64_t)a.nheads, L, (uint64_t)a.batch};
         const uint64_t s[3] = {(uint64_t)a.x_stride[2] * 2, (uint64_t)a.x_stride[1] * 2, (uint64_t)a.x_stride[0] * 2};
@@ -636,11 +647,22 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
         const uint32_t bx[3] = {64, 128, 1};
         if (!encode_16bit(&tCB, fmt, cb16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for CB failed");
     }
+    {
+        const uint64_t d[4] = {(uint64_t)kP, (uint64_t)a.nheads, L, (uint64_t)a.batch};
+        const uint32_t bx128[4] = {64, 1, 128, 1};
+        const uint64_t so[3] = {(uint64_t)a.out_stride[2] * 2, (uint64_t)a.out_stride[1] * 2, (uint64_t)a.out_stride[0] * 2};
+        if (!encode_16bit(&tout, fmt, a.out, 4, d, so, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for out failed");
+        tz = tout;
+        if (a.z) {
+            const uint64_t sz[3] = {(uint64_t)a.z_stride[2] * 2, (uint64_t)a.z_stride[1] * 2, (uint64_t)a.z_stride[0] * 2};
+            if (!encode_16bit(&tz, fmt, a.z, 4, d, sz, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for z failed");
+        }
+    }
     cudaFuncSetAttribute(ssd_tc_cb_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cb);
     ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
     MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
     cudaFuncSetAttribute(ssd_tc_chunk_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scan);
-    ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, a, dtb, dAb, nc, status);
+    ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, status);
     MB200_CHECK_LAUNCH("ssd chunk_scan (tensor core)");
     return MB200_OK;
 }
@@ -653,6 +675,8 @@ bool ssd_tc_eligible(const mb200_ssd_args &a)
     if (a.headdim != kP || a.dstate != kN || a.chunk_size != kQ || a.seq_idx) return false;
     if (!aligned16(a.x) || !aligned16(a.B) || !aligned16(a.C)) return false;
     if (!mult8(a.x_stride, 3) || !mult8(a.B_stride, 3) || !mult8(a.C_stride, 3)) return false;
+    if ((a.phases & MB200_SSD_PHASE_OUTPUT) && (!aligned16(a.out) || !mult8(a.out_stride, 3))) return false;
+    if (a.z && (!aligned16(a.z) || !mult8(a.z_stride, 3))) return false;
     if ((int64_t)a.batch * ((a.seqlen + kQ - 1) / kQ) * a.nheads > INT32_MAX) return false;
     return encode_fn() != nullptr;
 }
