@@ -31,7 +31,12 @@ if ROOT not in sys.path:
 
 # dram bytes (read + write) per launch of the dominant kernel from the committed ncu capture
 # (profiles/), or None where no capture exists for that workload.
-NCU_TRAFFIC_BYTES = {"c1": None, "c2": None, "c4": None, "c0": None}
+NCU_TRAFFIC_BYTES = {
+    "c1": 656_311_808,      # scan_seq_kernel: 505.4 MB read + 150.9 MB written
+    "c2": 2_357_000_000,    # five SSD launches summed (chunk_scan alone: 881.0 MB read + 310.1 MB written)
+    "c4": 1_291_591_424,    # ssu_packet_kernel: 676.8 MB read + 614.7 MB written
+    "c0": None, "c3": None,
+}
 
 
 def measured_peak_gbs():
@@ -86,12 +91,14 @@ def make_c4(batch, H=80, P=64, N=128, seed=1004, pool=4):
 class Workload:
     """One benchmark configuration: device step, host-buffer step, CPU-baseline sample, byte counts."""
 
-    def __init__(self, name, dev):
+    def __init__(self, name, dev, batch=None):
+        """`batch` shrinks the per-GPU batch (profiling captures only; the JSON line then says so)."""
         self.name, self.dev = name, dev
+        self.reduced = batch is not None
         import mamba_b200 as mb
         self.mb = mb
         if name in ("c1", "c0"):
-            host = make_c1(8) if name == "c1" else make_c0()
+            host = make_c1(batch or 8) if name == "c1" else make_c0()
             self.shape = dict(batch=host["u"].shape[0], d_inner=host["u"].shape[1], seqlen=host["u"].shape[2], d_state=16)
             self.tokens = host["u"].shape[0] * host["u"].shape[2]
             self.desc = ("mamba1_selective_scan_fwd bf16 b8 d5120 L2048 N16 (2.8B layer)" if name == "c1"
@@ -103,7 +110,7 @@ class Workload:
             self.alg_bytes = 4 * b * d * L * esz + 2 * b * 16 * L * esz + d * 16 * 4 + 2 * d * 4 + b * d * 16 * 4
             self.launches_per_step = 1
         elif name == "c2":
-            host = make_c2(8)
+            host = make_c2(batch or 8)
             b, L, H, P = host["x"].shape
             self.shape = dict(batch=b, seqlen=L, nheads=H, headdim=P, ngroups=1, d_state=128, chunk_size=256)
             self.tokens = b * L
@@ -135,7 +142,7 @@ class Workload:
             self.launches_per_step = 5 if world == 1 else 7
             self.world = world
         elif name == "c4":
-            host = make_c4(256)
+            host = make_c4(batch or 256)
             b, H, P, N = host["state"].shape
             self.shape = dict(batch=b, nheads=H, headdim=P, ngroups=1, d_state=N, consecutive_steps=True)
             self.tokens = b
@@ -242,23 +249,58 @@ HOST_INPUTS = {"c3": make_c3_sample, "c0": lambda: make_c0(), "c1": lambda: make
 
 # ----------------------------------------------------------------------------------------- clocks
 class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs.
+
+    NVML is polled directly (a query costs well under a millisecond, so even a 20 ms timed region
+    yields several samples); if the NVML binding is missing, `nvidia-smi` is polled instead."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
-        self.index, self.samples, self.stop = index, [], threading.Event()
+        self.index, self.sm, self.max_sm, self.reasons, self.stop = index, [], None, set(), threading.Event()
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[index]) if vis and vis.split(",")[index].isdigit() else index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.nvml = pynvml
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nvml = None
         self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _poll_nvml(self):
+        n = self.nvml
+        self.sm.append(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+        bits = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+        for name, flag in (("hw_slowdown", n.nvmlClocksThrottleReasonHwSlowdown),
+                           ("hw_thermal_slowdown", n.nvmlClocksThrottleReasonHwThermalSlowdown),
+                           ("sw_thermal_slowdown", n.nvmlClocksThrottleReasonSwThermalSlowdown),
+                           ("sw_power_cap", n.nvmlClocksThrottleReasonSwPowerCap)):
+            if bits & flag:
+                self.reasons.add(name)
+
+    def _poll_smi(self):
+        out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                             capture_output=True, text=True, timeout=5).stdout.strip()
+        f = [x.strip() for x in out.split(",")]
+        if f and f[0].isdigit():
+            self.sm.append(int(f[0]))
+            self.max_sm = int(f[1]) if f[1].isdigit() else self.max_sm
+            for i, name in enumerate(self.NAMES):
+                if len(f) > 2 + i and f[2 + i].lower().startswith("active"):
+                    self.reasons.add(name)
 
     def _run(self):
         while not self.stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i",
-                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([f.strip() for f in out.split(",")])
+                self._poll_nvml() if self.nvml else self._poll_smi()
             except Exception:
                 pass
-            self.stop.wait(0.05)
+            self.stop.wait(0.002 if self.nvml else 0.05)
 
     def __enter__(self):
         self.thread.start()
@@ -269,16 +311,13 @@ class ClockSampler:
         self.thread.join(timeout=6)
 
     def summary(self):
-        sm = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
-        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_sm, "reasons": sorted(self.reasons),
+                "samples": len(sm), "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
 # ----------------------------------------------------------------------------------------- legs
-def time_device(w, steps, warmup, dist):
+def time_device(w, steps, warmup, dist, clock_index):
     for _ in range(warmup):
         w.step()
     torch.cuda.synchronize()
@@ -286,15 +325,16 @@ def time_device(w, steps, warmup, dist):
         torch.distributed.barrier()
         torch.cuda.synchronize()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
-    ev[0].record()
-    for i in range(steps):
-        w.step()
-        ev[i + 1].record()
-    torch.cuda.synchronize()
+    with ClockSampler(clock_index) as clk:       # samples are taken only while the timed steps run
+        ev[0].record()
+        for i in range(steps):
+            w.step()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
     if dist:
         torch.distributed.barrier()
         torch.cuda.synchronize()
-    return ev[0].elapsed_time(ev[steps]) / 1e3
+    return ev[0].elapsed_time(ev[steps]) / 1e3, clk.summary()
 
 
 def time_e2e(w, steps, warmup, dist):
@@ -359,6 +399,8 @@ def main():
     ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="shrink the per-GPU batch (for ncu captures of a small case; not a benchmark result)")
     args = ap.parse_args()
     warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -397,10 +439,9 @@ def main():
     dev = torch.device("cuda", local)
     if dist:
         torch.distributed.init_process_group("nccl", device_id=dev)
-    w = Workload(args.workload, dev)
+    w = Workload(args.workload, dev, args.batch)
 
-    with ClockSampler(local) as clk:
-        t_dev = time_device(w, args.steps, warmup, dist)
+    t_dev, clocks = time_device(w, args.steps, warmup, dist, local)
     t_dev = max_over_ranks(t_dev, dist, dev)
     t_e2e, h2d, d2h = time_e2e(w, max(3, min(args.steps, 10)), warmup, dist)
     e2e_steps = max(3, min(args.steps, 10))
@@ -413,7 +454,8 @@ def main():
         "metric": metric, "value": world * w.tokens * args.steps / t_dev, "unit": unit, "n_gpus": world,
         "steps": args.steps, "warmup": warmup, "ms_per_step": per_launch_s * 1e3, "higher_is_better": True,
         "scaling": "strong" if args.workload == "c3" else "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": w.desc, "per_gpu": w.shape,
+        "config": {"workload": w.desc + (" [REDUCED BATCH: profiling run, not a benchmark result]" if w.reduced else ""),
+                   "per_gpu": w.shape,
                    "partition": ("contiguous chunk ranges per GPU, range states handed rank to rank by NCCL P2P"
                                  if args.workload == "c3" else "batch rows per GPU, no collective"),
                    "l2_policy": "inputs_exceed_l2" if w.alg_bytes > 2 * 126e6 else "inputs_fit_l2_not_flushed"},
@@ -422,7 +464,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
                      "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": w.alg_bytes},
-        "clocks": clk.summary(),
+        "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "c3":
         v, sample, cores = time_cpu(w)
