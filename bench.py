@@ -339,21 +339,52 @@ def time_device(w, steps, warmup, dist, clock_index):
 
 def time_e2e(w, steps, warmup, dist):
     """Same pass through the public API from pinned host buffers: H2D of the step's inputs, the
-    kernels, D2H of the step's output, all inside the timed region."""
+    kernels, D2H of the step's output, all inside the timed region.
+
+    Batched workloads are fed one batch row at a time on three streams (copy-in, compute, copy-out), so
+    the two PCIe directions and the kernels overlap; every byte of the step's inputs still crosses the
+    bus inside the timed region, every step."""
     pinned = w.pinned_inputs()
     dev_in = {k: torch.empty_like(v, device=w.dev) for k, v in pinned.items()}
-    res_host = None
     h2d = sum(v.numel() * v.element_size() for v in pinned.values())
+    probe = w.step({k: v.to(w.dev) for k, v in pinned.items()})
+    res_host = torch.empty(probe.shape, dtype=probe.dtype).pin_memory()
+    d2h = res_host.numel() * res_host.element_size()
+    del probe
+    nb = next(iter(pinned.values())).shape[0]
+    sliceable = w.name in ("c0", "c1", "c2") and nb > 1 and all(v.shape[0] == nb for v in pinned.values())
+    cur = torch.cuda.current_stream(w.dev)
+    s_in, s_cmp, s_out = (torch.cuda.Stream(w.dev) for _ in range(3))
+    done_prev = [None] * nb
 
-    def one():
-        nonlocal res_host
+    def one_simple():
         for k, v in pinned.items():
             dev_in[k].copy_(v, non_blocking=True)
-        out = w.step(dev_in)
-        if res_host is None:
-            res_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-        res_host.copy_(out, non_blocking=True)
+        res_host.copy_(w.step(dev_in), non_blocking=True)
 
+    def one_pipelined():
+        for st in (s_in, s_cmp, s_out):
+            st.wait_stream(cur)
+        for i in range(nb):
+            sl = slice(i, i + 1)
+            with torch.cuda.stream(s_in):
+                if done_prev[i] is not None:
+                    s_in.wait_event(done_prev[i])          # the previous step's kernels have consumed this row
+                for k, v in pinned.items():
+                    dev_in[k][sl].copy_(v[sl], non_blocking=True)
+                ready = s_in.record_event()
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ready)
+                out = w.step({k: v[sl] for k, v in dev_in.items()})
+                done_prev[i] = s_cmp.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done_prev[i])
+                out.record_stream(s_out)
+                res_host[sl].copy_(out, non_blocking=True)
+        cur.wait_stream(s_out)
+        cur.wait_stream(s_cmp)
+
+    one = one_pipelined if sliceable else one_simple
     for _ in range(max(1, min(warmup, 3))):
         one()
     torch.cuda.synchronize()
@@ -367,7 +398,6 @@ def time_e2e(w, steps, warmup, dist):
     torch.cuda.synchronize()
     if dist:
         torch.distributed.barrier()
-    d2h = res_host.numel() * res_host.element_size()
     return e0.elapsed_time(e1) / 1e3, h2d, d2h
 
 

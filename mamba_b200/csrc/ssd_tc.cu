@@ -6,8 +6,8 @@
 //
 //   cb          CB[m,k] = C_m . B_k per (batch, chunk, group), one CTA per 128-row block, written as a
 //               16-bit [256 x 256] matrix (lower block triangle) that all heads of the group reuse from L2.
-//   chunk_state S^T[n,p] = sum_k (B[k,n] w_k) x[k,p], w_k = exp(min(dA_last - dA_k, 0)) dt_k.  The B chunk
-//               arrives by TMA, 128 threads scale its rows in place (fp32 math, one rounding), then one
+//   chunk_state S^T[n,p] = sum_k B[k,n] (w_k x[k,p]), w_k = exp(min(dA_last - dA_k, 0)) dt_k.  B and x
+//               arrive by TMA, 256 threads weight the x rows in place (fp32 math, one rounding), then one
 //               thread issues 16 MMAs (M=128 over n, N=64 over p, both operands MN-major).
 //   chunk_scan  per (batch, chunk, head, 128-row block):  Y1 = C . H^T (state entering the chunk),
 //               Y2 = (CB o L) . X with L[m,k] = exp(min(dA_m - dA_k, 0)) dt_k [k <= m] applied in place to
@@ -190,11 +190,15 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_cb_kernel(const __grid_cons
 }
 
 // ====================================================================================== chunk state
-// grid (nheads, nchunks, batch).  smem: B 2 x 32 KB (n halves, [256 k x 64 n]), x 32 KB.  TMEM: 64 columns.
+// grid (nheads, nchunks, batch), 288 threads.  smem: B 2 x 32 KB (n halves, [256 k x 64 n]), x 32 KB.
+// TMEM: 64 columns.  S^T[n,p] = sum_k B[k,n] (w_k x[k,p]): the per-step weight w_k is applied to the x rows
+// (half as many elements as B, and x is per head anyway), one row per thread, in place, fp32 product with
+// one rounding; B is used as TMA delivered it.
+constexpr int kStateThreads = 288;
 template <typename T>
-__global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
-                                                                       const float *dtb, const float *dAb, float *states, int nchunks,
-                                                                       int nheads, int heads_per_group, int *status)
+__global__ void __launch_bounds__(kStateThreads) ssd_tc_chunk_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
+                                                                          const float *dtb, const float *dAb, float *states, int nchunks,
+                                                                          int nheads, int heads_per_group, int *status)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = align1024(smem_raw);
@@ -205,26 +209,35 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __
     const int h = blockIdx.x, c = blockIdx.y, b = blockIdx.z;
     const int g = h / heads_per_group;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 128) {
+    // the row weight is requested before the set-up barrier so its latency hides behind it and the TMA loads
+    float pre_dA = 0.f, pre_dt = 0.f, pre_last = 0.f;
+    if (threadIdx.x < 256) {
+        const float *dtc = dtb + (((int64_t)b * nheads + h) * nchunks + c) * kQ;
+        const float *dAc = dAb + (((int64_t)b * nheads + h) * nchunks + c) * kQ;
+        pre_last = dAc[kQ - 1];
+        pre_dA = dAc[threadIdx.x];
+        pre_dt = dtc[threadIdx.x];
+    }
+    if (threadIdx.x == 256) {
         mbar_init(&bars[0], 1);      // B landed
         mbar_init(&bars[1], 1);      // x landed
-        mbar_init(&bars[2], 4);      // B rows scaled: one arrival per element-wise warp
+        mbar_init(&bars[2], 8);      // x rows weighted: one arrival per element-wise warp
         mbar_init(&bars[3], 1);      // MMAs done
         mbar_fence_init();
     }
-    if (warp == 4) tmem_alloc(tmem_slot, 64);
+    if (warp == 8) tmem_alloc(tmem_slot, 64);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) {
+            mbar_expect_tx(&bars[1], 32768);
+            tma_load_4d(xs, &tm_x, &bars[1], 0, h, c * kQ, b);
             mbar_expect_tx(&bars[0], 65536);
             tma_load_4d(Bs, &tm_B, &bars[0], 0, g, c * kQ, b);
             tma_load_4d(Bs + 32768, &tm_B, &bars[0], 64, g, c * kQ, b);
-            mbar_expect_tx(&bars[1], 32768);
-            tma_load_4d(xs, &tm_x, &bars[1], 0, h, c * kQ, b);
-            const bool ok = mbar_wait(&bars[2], 0, status, kStBarScaled) && mbar_wait(&bars[1], 0, status, kStBarX);
+            const bool ok = mbar_wait(&bars[2], 0, status, kStBarScaled) && mbar_wait(&bars[0], 0, status, kStBarB);
             if (ok) {
                 tc_fence_after_sync();
                 const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 1, 1);
@@ -235,36 +248,22 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __
             mma_commit(&bars[3]);
         }
     } else {
-        const float *dtc = dtb + (((int64_t)b * nheads + h) * nchunks + c) * kQ;
-        const float *dAc = dAb + (((int64_t)b * nheads + h) * nchunks + c) * kQ;
-        const float dA_last = dAc[kQ - 1];
-        float w[2];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int k = threadIdx.x + i * 128;
-            w[i] = __expf(fminf(dA_last - dAc[k], 0.f)) * dtc[k];
-        }
-        const bool ok = mbar_wait(&bars[0], 0, status, kStBarB);
+        const int k = threadIdx.x;
+        const float w = __expf(fminf(pre_last - pre_dA, 0.f)) * pre_dt;
+        const bool ok = mbar_wait(&bars[1], 0, status, kStBarX);
         if (ok) {
+            const uint32_t base = smem_u32(xs) + k * 128;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int k = threadIdx.x + i * 128;
+            for (int ch = 0; ch < 8; ++ch) {
+                const uint32_t addr = base + ((ch ^ (k & 7)) << 4);
+                uint4 v = lds128(addr);
+                uint32_t *e = reinterpret_cast<uint32_t *>(&v);
 #pragma unroll
-                for (int box = 0; box < 2; ++box) {
-                    const uint32_t base = smem_u32(Bs + box * 32768) + k * 128;
-#pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) {
-                        const uint32_t addr = base + ((ch ^ (k & 7)) << 4);
-                        uint4 v = lds128(addr);
-                        uint32_t *e = reinterpret_cast<uint32_t *>(&v);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float2 f = Pack2<T>::unpack(e[q]);
-                            e[q] = Pack2<T>::pack(f.x * w[i], f.y * w[i]);
-                        }
-                        sts128(addr, v);
-                    }
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = Pack2<T>::unpack(e[q]);
+                    e[q] = Pack2<T>::pack(f.x * w, f.y * w);
                 }
+                sts128(addr, v);
             }
         }
         fence_proxy_async();
@@ -274,19 +273,17 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_chunk_state_kernel(const __
         tc_fence_after_sync();
         if (__all_sync(0xffffffffu, ok && done)) {   // tcgen05.ld is warp-collective
             float *S = states + (((int64_t)b * nchunks + c) * nheads + h) * (int64_t)(kP * kN);
-            const int n = threadIdx.x;
+            const int n = (warp & 3) * 32 + lane;     // TMEM lane = state index
+            const int p0 = (warp >> 2) * 32;          // which half of the head's columns this warp stores
+            float v[32];
+            tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + p0, v);
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float v[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + half * 32, v);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) S[(half * 32 + j) * kN + n] = v[j];
-            }
+            for (int j = 0; j < 32; ++j) S[(p0 + j) * kN + n] = v[j];
         }
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem, 64);
+    if (warp == 8) tmem_dealloc(tmem, 64);
 }
 
 // ====================================================================================== chunk scan
@@ -630,7 +627,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
     const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = 98304 + 3072 + 64 + 256 + 1024;
     if (stage == 0) {
         cudaFuncSetAttribute(ssd_tc_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state);
-        ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kThreadsTc, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
+        ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kStateThreads, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
                                                                                                    a.nheads / a.ngroups, status);
         MB200_CHECK_LAUNCH("ssd chunk_state (tensor core)");
         return MB200_OK;
