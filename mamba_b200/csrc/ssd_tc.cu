@@ -71,7 +71,7 @@ constexpr int kQ = 256, kP = 64, kN = 128;
 constexpr int kThreadsTc = 160;
 
 // status codes written to the scratch status word
-enum { kStBarB = 11, kStBarX, kStBarScaled, kStBarDone, kStBarC, kStBarG1, kStBarFull, kStBarEmpty, kStBarG2 };
+enum { kStBarB = 11, kStBarX, kStBarScaled, kStBarDone, kStBarC, kStBarG1, kStBarFull, kStBarEmpty, kStBarG2, kStSmemAlign };
 
 template <typename T> struct Pack2;
 template <> struct Pack2<__nv_bfloat16> {
@@ -288,24 +288,28 @@ __global__ void __launch_bounds__(kStateThreads) ssd_tc_chunk_state_kernel(const
 
 // ====================================================================================== chunk scan
 // grid (nheads, nchunks * 2, batch), 288 threads: warps 0-7 element-wise + epilogue (thread = one row and one
-// 32-column half), warp 8 TMA + MMA.  smem: C 2 x 16 KB | H 2 x 8 KB | 2 block slots, each {CB block
-// [128 x 64] 16 KB, x rows [64 x 64] 8 KB} | dA*log2e, dt, column factors (3 KB) | barriers: 100 KB, two CTAs
-// per SM.  Everything a CTA needs first (C, H, blocks 0 and 1) is requested at once; the second row block's
-// blocks 2 and 3 land in the C/H area as soon as Y1 = C.H^T has been issued and finished, so no slot is ever
-// re-used and the element-wise warps never wait for a slot to drain.  x travels with the CB block it
-// multiplies; the row block's own x rows (needed for D x) are in the last two blocks, still resident at the
-// end.  TMEM: 128 columns.
-// The mask factors are rounded to the input dtype and applied with packed 16-bit multiplies (two roundings
-// per element instead of one; far inside the 16-bit tolerance, and it halves the instruction count).
+// 32-column half), warp 8 TMA + MMA.  A "block" is a 64-wide slice of the mask product: the CB tile [128 x 64]
+// (16 KB) followed by the 64 rows of x it multiplies (8 KB).  Shared memory (74.7 KB, three CTAs per SM):
+//   area A (48 KB)  first C (2 x 16 KB) and H (2 x 8 KB); once Y1 = C.H^T has completed it is two block slots
+//   slot S (24 KB)  block 0, later block 3
+//   scalars         dA*log2e and the column factors (fp32), dt (bf16), barriers
+// Block placement: 0 -> S, 1 -> A.0, 2 -> A.1, 3 -> S (after block 0 has been multiplied).  The gate tile z
+// lands in the CB part of a slot whose block has been multiplied (S for the first row block, A.0 for the
+// second); the output tile is assembled in the CB part of the last-but-one block's slot and leaves through
+// one TMA store.  The row block's own x rows (for D x) are the x parts of its last two blocks, which nothing
+// overwrites.  TMEM: 128 columns (Y1, Y2).
 //
-// Decay mask.  A thread owns 32 consecutive columns k of one row m per CB block.  Three cases:
+// Decay mask.  A thread owns 32 consecutive columns k of one row m per block.  Three cases:
 //   all k > m           zeros
 //   all k <= m          L[m,k] = exp(dA_m - dA_ref) * (exp(dA_ref - dA_k) dt_k), ref = last k of the range: one
 //                       exponential per thread, the column factors are computed once per CTA.  Both exponents
 //                       are <= 0 because dA_cumsum is non-increasing (A <= 0, dt >= 0); a chunk where that does
 //                       not hold is detected and sent down the exact path.
 //   range holds k = m   exact: exp(min(dA_m - dA_k, 0)) dt_k [k <= m] per element
+// The mask factors are rounded to the input dtype and applied with packed 16-bit multiplies (two roundings
+// per element instead of one; far inside the 16-bit tolerance, and it halves the instruction count).
 constexpr int kScanThreads = 288;
+constexpr uint32_t kScanSmem = 49152 + 24576 + 1024 + 1024 + 512 + 64 + 128 + 16;   // 76496 B, base must be 1 KB aligned
 #ifdef MB200_SCAN_TRACE
 #define MB200_TRACE(slot)                                                                                         \
     do {                                                                                                          \
@@ -318,32 +322,33 @@ constexpr int kScanThreads = 288;
 __device__ __forceinline__ void scan_compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads, 2)
+__global__ void __launch_bounds__(kScanThreads, 3)
 ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_C,
                          const __grid_constant__ CUtensorMap tm_H, const __grid_constant__ CUtensorMap tm_CB,
                          const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_out, const mb200_ssd_args a,
                          const float *dtb, const float *dAb, int nchunks, int *status)
 {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *sm = align1024(smem_raw);
-    uint8_t *Cs = sm;                          // 2 boxes [128 x 64]
-    uint8_t *Hs = sm + 32768;                  // 2 boxes [64 x 64]
-    constexpr uint32_t kSlot = 24576, kSlotX = 16384;   // a slot: CB block, then 64 rows of x
-    // blocks 0,1 have their own slots; blocks 2,3 re-use the C/H area once Y1 is complete
-    auto slot_ptr = [&](int j) -> uint8_t * { return j < 2 ? sm + 49152 + j * kSlot : sm + (j - 2) * kSlot; };
-    float *dA2 = reinterpret_cast<float *>(sm + 98304);   // 256: dA_cumsum * log2(e)
-    float *dts = dA2 + 256;                               // 256: dt
-    float *cks = dts + 256;                               // 256: exp(dA_ref(k) - dA_k) dt_k, ref(k) = k | 31
-    int *mono = reinterpret_cast<int *>(cks + 256);       // 1 while dA_cumsum is non-increasing over the chunk
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 98304 + 3072 + 64);
+    extern __shared__ __align__(1024) uint8_t sm[];
+    constexpr uint32_t kSlot = 24576, kSlotX = 16384;   // a slot: CB tile, then 64 rows of x
+    uint8_t *areaA = sm;                       // C | H, then slots A.0, A.1
+    uint8_t *slotS = sm + 49152;
+    uint8_t *Cs = areaA, *Hs = areaA + 32768;
+    float *dA2 = reinterpret_cast<float *>(sm + 73728);             // 256: dA_cumsum * log2(e)
+    float *cks = dA2 + 256;                                         // 256: exp(dA_ref(k) - dA_k) dt_k, ref(k) = k | 31
+    __nv_bfloat16 *dts = reinterpret_cast<__nv_bfloat16 *>(cks + 256);   // 256: dt (only the exact path reads it)
+    int *mono = reinterpret_cast<int *>(sm + 73728 + 2560);         // 1 while dA_cumsum is non-increasing over the chunk
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 73728 + 2560 + 64);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
-    uint64_t *bar_c = &bars[0], *bar_g1 = &bars[1], *bar_z = &bars[2], *bar_g2 = &bars[3], *bar_e0 = &bars[12];
-    uint64_t *bar_full = &bars[4], *bar_scaled = &bars[8];
+    uint64_t *bar_c = &bars[0], *bar_g1 = &bars[1], *bar_z = &bars[2], *bar_g2 = &bars[3];
+    uint64_t *bar_full = &bars[4], *bar_scaled = &bars[8], *bar_e = &bars[12];   // bar_e[j]: block j has been multiplied
 
     const int h = blockIdx.x, c = blockIdx.y >> 1, mb = blockIdx.y & 1, b = blockIdx.z;
     const int g = h / (a.nheads / a.ngroups);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nk = (mb + 1) * 2;   // 64-wide CB blocks this row block needs
+    const int nk = (mb + 1) * 2;   // 64-wide blocks this row block needs
+    auto slot_ptr = [&](int j) -> uint8_t * { return (j == 0 || j == 3) ? slotS : areaA + (j - 1) * kSlot; };
+    uint8_t *ztile = mb ? areaA : slotS;                  // CB part of block 1's / block 0's slot
+    uint8_t *otile = mb ? areaA + kSlot : areaA;          // CB part of block 2's / block 1's slot
     // chunk scalars are requested before the set-up barrier so their latency hides behind it
     const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
     const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
@@ -359,14 +364,16 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         mbar_init(bar_c, 1);
         mbar_init(bar_g1, 1);
         mbar_init(bar_z, 1);
-        mbar_init(bar_e0, 1);
         mbar_init(bar_g2, 1);
         for (int i = 0; i < 4; ++i) {
             mbar_init(&bar_full[i], 1);
             mbar_init(&bar_scaled[i], 8);      // one arrival per element-wise warp
         }
+        mbar_init(&bar_e[0], 1);
+        mbar_init(&bar_e[1], 1);
         *mono = 1;
         mbar_fence_init();
+        if (smem_u32(sm) & 1023u) atomicCAS(status, 0, kStSmemAlign);   // the swizzled tiles assume a 1 KB aligned base
     }
     if (warp == 8) tmem_alloc(tmem_slot, 128);
     tc_fence_before_sync();
@@ -378,22 +385,13 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 
     if (warp == 8) {
         if (lane == 0) {
-            bool ok = true;
+            bool ok = (smem_u32(sm) & 1023u) == 0;
             MB200_TRACE(0);
-            // The first two mask blocks are what the element-wise warps wait for, so they are requested first;
-            // C and H (for Y1, which nothing needs before the epilogue) follow.
             auto load_block = [&](int j) {
                 mbar_expect_tx(&bar_full[j], 16384 + 8192);
                 tma_load_3d(slot_ptr(j), &tm_CB, &bar_full[j], j * 64, mb * 128, (int)unit_g);
                 tma_load_4d(slot_ptr(j) + kSlotX, &tm_x, &bar_full[j], 0, h, c * kQ + j * 64, b);
             };
-            load_block(0);
-            load_block(1);
-            mbar_expect_tx(bar_c, 32768 + 16384);
-            for (int kb = 0; kb < 2; ++kb) {
-                tma_load_4d(Cs + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
-                tma_load_3d(Hs + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
-            }
             const uint32_t idesc2 = instr_desc_f16(128, 64, Fmt<T>::v, 0, 1);
             auto gemm2_block = [&](int j) {      // Y2 += (CB o L)_j . X_j once the element-wise warps release block j
                 ok = ok && mbar_wait(&bar_scaled[j], 0, status, kStBarScaled);
@@ -405,7 +403,20 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                                    smem_desc_sw128(sb + kSlotX + s * 2048, 16, 1024), idesc2, (j | s) != 0);
                 }
             };
-            // Y1 = C . H^T
+            auto load_z = [&]() {
+                mbar_expect_tx(bar_z, 16384);
+                tma_load_4d(ztile, &tm_z, bar_z, 0, h, c * kQ + mb * 128, b);
+            };
+            // the first mask block is what the element-wise warps wait for: request it first, then C and H
+            if (ok) {
+                load_block(0);
+                mbar_expect_tx(bar_c, 32768 + 16384);
+                for (int kb = 0; kb < 2; ++kb) {
+                    tma_load_4d(Cs + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
+                    tma_load_3d(Hs + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
+                }
+            }
+            // Y1 = C . H^T, then area A is free for blocks 1 and 2
             ok = ok && mbar_wait(bar_c, 0, status, kStBarC);
             MB200_TRACE(1);
             if (ok) {
@@ -416,29 +427,32 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         mma_f16_ss(tmem, smem_desc_sw128(smem_u32(Cs + kb * 16384) + s * 32, 16, 1024),
                                    smem_desc_sw128(smem_u32(Hs + kb * 8192) + s * 32, 16, 1024), idesc, (kb | s) != 0);
             }
-            if (nk > 2) {
-                mma_commit(bar_g1);
-                ok = ok && mbar_wait(bar_g1, 0, status, kStBarG1);   // C / H have been read: their area takes blocks 2, 3
-                if (ok) {
-                    load_block(2);
-                    load_block(3);
-                }
+            mma_commit(bar_g1);
+            ok = ok && mbar_wait(bar_g1, 0, status, kStBarG1);
+            if (ok) {
+                load_block(1);
+                if (nk > 2) load_block(2);
             }
             MB200_TRACE(2);
-            for (int j = 0; j < nk; ++j) {
-                gemm2_block(j);
-                if (j == 0) {
-                    MB200_TRACE(3);
-                    if (a.z) mma_commit(bar_e0);
+            gemm2_block(0);
+            MB200_TRACE(3);
+            if (nk > 2 || a.z) {
+                mma_commit(&bar_e[0]);
+                ok = ok && mbar_wait(&bar_e[0], 0, status, kStBarEmpty);    // slot S has been read
+                if (ok) {
+                    if (nk > 2) load_block(3);
+                    else load_z();
                 }
-                if (j == 1 && a.z) {
-                    // block 0 has been multiplied: its CB area now receives the gate tile for the epilogue
-                    ok = ok && mbar_wait(bar_e0, 0, status, kStBarEmpty);
-                    if (ok) {
-                        mbar_expect_tx(bar_z, 16384);
-                        tma_load_4d(slot_ptr(0), &tm_z, bar_z, 0, h, c * kQ + mb * 128, b);
-                    }
+            }
+            gemm2_block(1);
+            if (nk > 2) {
+                if (a.z) {
+                    mma_commit(&bar_e[1]);
+                    ok = ok && mbar_wait(&bar_e[1], 0, status, kStBarEmpty);   // block 1's CB tile has been read
+                    if (ok) load_z();
                 }
+                gemm2_block(2);
+                gemm2_block(3);
             }
             mma_commit(bar_g2);
             MB200_TRACE(4);
@@ -451,7 +465,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         {
             const int k = threadIdx.x;
             dA2[k] = pre_dk * kLog2e;
-            dts[k] = pre_tk;
+            dts[k] = __float2bfloat16_rn(pre_tk);
             cks[k] = __expf(pre_ref - pre_dk) * pre_tk;
             if (pre_dk > pre_prev) *mono = 0;
         }
@@ -462,7 +476,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         if (threadIdx.x == 0) MB200_TRACE(9);
         const float dAm = dA2[m];
         const bool factor_ok = *mono != 0;
-        bool ok = true;
+        bool ok = (smem_u32(sm) & 1023u) == 0;
         for (int j = 0; j < nk; ++j) {
             const int klo = j * 64 + kh * 32;       // first column of this thread's range
             ok = ok && mbar_wait(&bar_full[j], 0, status, kStBarFull);
@@ -499,13 +513,14 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         uint32_t *e = reinterpret_cast<uint32_t *>(&v);
                         const int kc = klo + ch * 8;
                         const float4 d0 = *reinterpret_cast<const float4 *>(dA2 + kc), d1 = *reinterpret_cast<const float4 *>(dA2 + kc + 4);
-                        const float4 t0 = *reinterpret_cast<const float4 *>(dts + kc), t1 = *reinterpret_cast<const float4 *>(dts + kc + 4);
+                        const uint4 tv = *reinterpret_cast<const uint4 *>(dts + kc);
+                        const uint32_t *tw = reinterpret_cast<const uint32_t *>(&tv);
                         const float dk[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-                        const float tk[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            const float l0 = (kc + 2 * q <= m) ? ex2(fminf(dAm - dk[2 * q], 0.f)) * tk[2 * q] : 0.f;
-                            const float l1 = (kc + 2 * q + 1 <= m) ? ex2(fminf(dAm - dk[2 * q + 1], 0.f)) * tk[2 * q + 1] : 0.f;
+                            const float2 tk = Pack2<__nv_bfloat16>::unpack(tw[q]);
+                            const float l0 = (kc + 2 * q <= m) ? ex2(fminf(dAm - dk[2 * q], 0.f)) * tk.x : 0.f;
+                            const float l1 = (kc + 2 * q + 1 <= m) ? ex2(fminf(dAm - dk[2 * q + 1], 0.f)) * tk.y : 0.f;
                             e[q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
                         }
                         sts128(addr, v);
@@ -519,20 +534,16 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         if (threadIdx.x == 0) MB200_TRACE(11);
         ok = ok && mbar_wait(bar_g2, 0, status, kStBarG2);
         if (threadIdx.x == 0) MB200_TRACE(12);
+        if (a.z) ok = ok && mbar_wait(bar_z, 0, status, kStBarX);
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: the whole warp takes one path
         tc_fence_after_sync();
-        if (a.z) ok = ok && mbar_wait(bar_z, 0, status, kStBarX);
-        ok = __all_sync(0xffffffffu, ok);
-        // Outputs are assembled as a [128 x 64] tile in the CB area of block 1 (free: every MMA has finished)
-        // and leave through one TMA store; the gate tile sits in the CB area of block 0.
-        uint8_t *ztile = slot_ptr(0), *otile = slot_ptr(1);
         if (ok) {
             float y1[32], y2[32];
             const uint32_t tl = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * 32;
             tmem_ld32_pair(tl, tl + 64, y1, y2);
             if (threadIdx.x == 0) MB200_TRACE(14);
             const float scale = ex2(dAm);
-            // row m of x sits in the slot that carried block m / 64 (the last two blocks stay resident)
+            // row m of x sits in the x part of the slot that carried block m / 64
             const uint32_t xrow = smem_u32(slot_ptr(m >> 6) + kSlotX) + (m & 63) * 128;
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
@@ -584,7 +595,6 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     if (warp == 8) tmem_dealloc(tmem, 128);
 }
 
-
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 bool mult8(const int64_t *s, int n)
 {
@@ -624,7 +634,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
         if (!encode_16bit(&tB, fmt, a.B, 4, d, sB, stage == 0 ? bx256 : bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for B failed");
         if (!encode_16bit(&tC, fmt, a.C, 4, d, sC, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for C failed");
     }
-    const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = 98304 + 3072 + 64 + 256 + 1024;
+    const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = kScanSmem;
     if (stage == 0) {
         cudaFuncSetAttribute(ssd_tc_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state);
         ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kStateThreads, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
