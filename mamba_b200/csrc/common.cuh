@@ -118,6 +118,20 @@ __device__ __forceinline__ float fast_softplus20(float x)
     return fmaf(2.f * s, p, fmaxf(x, 0.f));
 }
 
+// silu(z) = h + h tanh(h), h = z/2, with the single-MUFU tanh.approx (relative error 2^-11).  For outputs
+// that are rounded to bfloat16 (8 significant bits) the approximation stays below the rounding step.
+__device__ __forceinline__ float tanh_approx(float x)
+{
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float silu_for_bf16(float z)
+{
+    const float h = 0.5f * z;
+    return fmaf(h, tanh_approx(h), h);
+}
+
 // ---- packed fp32 pairs (sm_100 f32x2 instructions: one issue slot for two lanes of work) ----------
 __device__ __forceinline__ uint64_t pack2(float lo, float hi)
 {

@@ -570,8 +570,13 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const float2 f = Pack2<T>::unpack(ze[q]);
-                        y[2 * q] *= fast_silu(f.x);
-                        y[2 * q + 1] *= fast_silu(f.y);
+                        if constexpr (Fmt<T>::v == 1) {     // bfloat16 output: one MUFU per gate value is accurate enough
+                            y[2 * q] *= silu_for_bf16(f.x);
+                            y[2 * q + 1] *= silu_for_bf16(f.y);
+                        } else {
+                            y[2 * q] *= fast_silu(f.x);
+                            y[2 * q + 1] *= fast_silu(f.y);
+                        }
                     }
                 }
                 uint4 o;
