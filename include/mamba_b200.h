@@ -122,7 +122,12 @@ int mb200_selective_state_update(const mb200_ssu_args *args, void *stream);
  * dt : (batch, seqlen, nheads) dt_dtype, strides {batch, seq, head}.   A, dt_bias : (nheads) fp32.
  * B, C : (batch, seqlen, ngroups, dstate) io_dtype, dstate stride 1, strides {batch, seq, group}.
  * D : (nheads) fp32, or (nheads, headdim) fp32 contiguous when D_has_hdim.
- * seq_idx : optional int32 (batch, seqlen) contiguous; positions with different ids do not interact.
+ * seq_idx : optional int32 (batch, seqlen) contiguous, non-decreasing sequence ids starting at 0 for packed
+ *   sequences: positions with different ids do not interact (ssd_chunk_state.py:246-251, ssd_state_passing.py:76-79,
+ *   ssd_bmm.py:84-88, ssd_chunk_scan.py:97-113).  Calls with seq_idx or cu_seqlens run the general stage kernels.
+ * cu_seqlens / num_seqs / varlen_states : optional (batch must be 1): int32 (num_seqs + 1) cumulative sequence
+ *   lengths and an fp32 (num_seqs, nheads, headdim, dstate) output receiving the state after the last token of
+ *   every packed sequence (chunk_state_varlen, ssd_chunk_state.py:1018-1044, kernel :639-715).
  * initial_states : optional (batch, nheads, headdim, dstate) fp32 contiguous.
  * final_states   : optional (batch, nheads, headdim, dstate) fp32 contiguous.
  * scratch : caller-owned device buffer of at least mb200_ssd_scratch_bytes() bytes, 256-byte
@@ -161,6 +166,10 @@ typedef struct mb200_ssd_args {
     int32_t phases;
     int32_t device;
     int64_t x_stride[3], z_stride[3], out_stride[3], dt_stride[3], B_stride[3], C_stride[3];
+    const int32_t *cu_seqlens;
+    float *varlen_states;
+    int32_t num_seqs;
+    int32_t reserved_;
 } mb200_ssd_args;
 
 int mb200_ssd_scratch_bytes(const mb200_ssd_args *args, size_t *bytes);

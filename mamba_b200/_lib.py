@@ -59,6 +59,7 @@ class SsdArgs(ctypes.Structure):
         ("phases", c_i32), ("device", c_i32),
         ("x_stride", c_i64 * 3), ("z_stride", c_i64 * 3), ("out_stride", c_i64 * 3),
         ("dt_stride", c_i64 * 3), ("B_stride", c_i64 * 3), ("C_stride", c_i64 * 3),
+        ("cu_seqlens", c_vp), ("varlen_states", c_vp), ("num_seqs", c_i32), ("reserved_", c_i32),
     ]
 
 

@@ -53,6 +53,12 @@ __device__ __forceinline__ void tile_gemm(float (&acc)[4][4], int K, FA fa, FB f
     }
 }
 
+// Sequence id of position t of batch row b (packed sequences), or 0 when no ids were given.
+__device__ __forceinline__ int seq_at(const mb200_ssd_args &a, int b, int t)
+{
+    return a.seq_idx ? a.seq_idx[(int64_t)b * a.seqlen + t] : 0;
+}
+
 // ---- stage 1 ------------------------------------------------------------------------------------
 // One CTA per (chunk, batch, 32 heads): coalesced read of dt over heads, transposed in shared
 // memory, then a warp scan along the chunk per head.
@@ -120,9 +126,13 @@ __global__ void __launch_bounds__(kT) ssd_chunk_state_kernel(const mb200_ssd_arg
     const T *x = static_cast<const T *>(a.x) + (int64_t)b * a.x_stride[0] + (int64_t)t0 * a.x_stride[1] + (int64_t)h * a.x_stride[2];
     const T *B = static_cast<const T *>(a.B) + (int64_t)b * a.B_stride[0] + (int64_t)t0 * a.B_stride[1] + (int64_t)g * a.B_stride[2];
     float acc[4][4] = {};
+    const int seq_last = seq_at(a, b, t0 + len - 1);    // only steps of the chunk's last sequence reach its end state
     tile_gemm<false, false>(
         acc, len,
-        [&](int k, int i) { return p0 + i < P ? to_float(x[(int64_t)k * a.x_stride[1] + p0 + i]) * (__expf(fminf(dA_last - dAc[k], 0.f)) * dtc[k]) : 0.f; },
+        [&](int k, int i) {
+            if (p0 + i >= P || (a.seq_idx && seq_at(a, b, t0 + k) != seq_last)) return 0.f;
+            return to_float(x[(int64_t)k * a.x_stride[1] + p0 + i]) * (__expf(fminf(dA_last - dAc[k], 0.f)) * dtc[k]);
+        },
         [&](int k, int j) { return n0 + j < N ? to_float(B[(int64_t)k * a.B_stride[1] + n0 + j]) : 0.f; }, As, Bs);
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     float *S = states + (((int64_t)b * nchunks + c) * a.nheads + h) * (int64_t)P * N;
@@ -168,6 +178,11 @@ __global__ void __launch_bounds__(256) ssd_state_passing_kernel(const mb200_ssd_
                         s[u][0] = slot[0];
                     }
                     dec[u] = __expf(dA_last[(int64_t)c * Q]);
+                    if (a.seq_idx) {   // a new sequence at the end of this chunk: nothing carries over from the previous one
+                        const int s_new = seq_at(a, b, min((c + 1) * Q, a.seqlen) - 1);
+                        const int s_old = c > 0 ? seq_at(a, b, c * Q - 1) : 0;
+                        if (s_new != s_old) dec[u] = 0.f;
+                    }
                 }
             }
 #pragma unroll
@@ -224,7 +239,10 @@ __global__ void __launch_bounds__(kT) ssd_cb_kernel(const mb200_ssd_args a, floa
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int m = m0 + ty * 4 + i, k = k0 + tx * 4 + j;
-            if (m < Q && k < Q) out[(int64_t)m * Q + k] = acc[i][j];
+            if (m < Q && k < Q) {
+                const bool same = !a.seq_idx || (m < len && k < len && seq_at(a, b, t0 + m) == seq_at(a, b, t0 + k));
+                out[(int64_t)m * Q + k] = same ? acc[i][j] : 0.f;
+            }
         }
 }
 
@@ -258,7 +276,9 @@ __global__ void __launch_bounds__(kT) ssd_chunk_scan_kernel(const mb200_ssd_args
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int m = m0 + ty * 4 + i;
-        const float sc = m < len ? __expf(dAc[m]) : 0.f;
+        float sc = m < len ? __expf(dAc[m]) : 0.f;
+        // the entering state belongs to the sequence that ends the previous chunk
+        if (a.seq_idx && m < len && seq_at(a, b, t0 + m) != (c > 0 ? seq_at(a, b, t0 - 1) : 0)) sc = 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] *= sc;
     }
@@ -288,6 +308,40 @@ __global__ void __launch_bounds__(kT) ssd_chunk_scan_kernel(const mb200_ssd_args
             out[(int64_t)m * a.out_stride[1] + p] = from_float<T>(y);
         }
     }
+}
+
+// ---- packed sequences: state after the last token of each one ------------------------------------
+// One thread per (p, n) element of one (sequence, head): the contribution of the sequence's steps inside
+// the chunk that holds its last token, plus the state entering that chunk if the sequence began earlier.
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_varlen_state_kernel(const mb200_ssd_args a, const float *dtb, const float *dAb,
+                                                               const float *states, int nchunks)
+{
+    const int P = a.headdim, N = a.dstate, Q = a.chunk_size;
+    const int e = blockIdx.x * 256 + threadIdx.x;
+    const int s = blockIdx.y, h = blockIdx.z;
+    if (e >= P * N) return;
+    const int p = e / N, n = e % N;
+    const int g = h / (a.nheads / a.ngroups);
+    const int start = a.cu_seqlens[s], end = a.cu_seqlens[s + 1];
+    float *dst = a.varlen_states + (((int64_t)s * a.nheads + h) * P + p) * N + n;
+    if (end <= start || end > a.seqlen) {
+        *dst = 0.f;
+        return;
+    }
+    const int c = (end - 1) / Q;
+    const int t0 = c * Q;
+    const float *dtc = dtb + ((int64_t)h * nchunks + c) * Q;
+    const float *dAc = dAb + ((int64_t)h * nchunks + c) * Q;
+    const float dA_end = dAc[end - 1 - t0];
+    const T *x = static_cast<const T *>(a.x) + (int64_t)h * a.x_stride[2] + p;
+    const T *B = static_cast<const T *>(a.B) + (int64_t)g * a.B_stride[2] + n;
+    float acc = 0.f;
+    for (int t = max(start, t0); t < end; ++t)
+        acc = fmaf(to_float(x[(int64_t)t * a.x_stride[1]]) * (__expf(fminf(dA_end - dAc[t - t0], 0.f)) * dtc[t - t0]),
+                   to_float(B[(int64_t)t * a.B_stride[1]]), acc);
+    if (start < t0) acc = fmaf(states[(((int64_t)c) * a.nheads + h) * (int64_t)P * N + e], __expf(dA_end), acc);
+    *dst = acc;
 }
 
 __global__ void ssd_fold_kernel(const float *s_in, const float *decay, const float *s_local, float *s_out, int64_t rows,
@@ -359,6 +413,10 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
             ssd_chunk_scan_kernel<T><<<dim3(tq * ((a.headdim + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(a, dtb, dAb, states, cb, nc);
             MB200_CHECK_LAUNCH("ssd chunk_scan");
         }
+        if (a.cu_seqlens && a.varlen_states && a.num_seqs > 0) {
+            ssd_varlen_state_kernel<T><<<dim3((unsigned)((PN + 255) / 256), a.num_seqs, a.nheads), 256, 0, stream>>>(a, dtb, dAb, states, nc);
+            MB200_CHECK_LAUNCH("ssd varlen states");
+        }
     }
     return MB200_OK;
 }
@@ -396,7 +454,9 @@ extern "C" int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (int rc = check_ssd(a)) return rc;
     MB200_CHECK_ARG(!(a.phases & MB200_SSD_PHASE_OUTPUT) || a.out, "ssd: out is NULL");
-    if (a.seq_idx) return fail(MB200_ERR_UNSUPPORTED, "ssd: seq_idx is not supported yet");
+    MB200_CHECK_ARG(!a.cu_seqlens || a.batch == 1, "passing cu_seqlens to get the varlen states is only supported if batch dimension is 1");
+    MB200_CHECK_ARG(!a.cu_seqlens || (a.num_seqs >= 0 && a.num_seqs <= 65535), "ssd: num_seqs must be in [0, 65535]");
+    MB200_CHECK_ARG(!(a.seq_idx || a.cu_seqlens) || a.phases == MB200_SSD_PHASE_ALL, "ssd: packed sequences cannot be combined with a sequence split");
     if (a.batch == 0) return MB200_OK;   // nothing to do; empty tensors carry NULL pointers
     MB200_CHECK_ARG(a.x && a.dt && a.A && a.B && a.C, "ssd: a required tensor is NULL");
     if (int rc = enter_device(a.device)) return rc;

@@ -684,7 +684,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
 bool ssd_tc_eligible(const mb200_ssd_args &a)
 {
     if (a.io_dtype != MB200_BF16 && a.io_dtype != MB200_F16) return false;
-    if (a.headdim != kP || a.dstate != kN || a.chunk_size != kQ || a.seq_idx) return false;
+    if (a.headdim != kP || a.dstate != kN || a.chunk_size != kQ || a.seq_idx || a.cu_seqlens) return false;
     if (!aligned16(a.x) || !aligned16(a.B) || !aligned16(a.C)) return false;
     if (!mult8(a.x_stride, 3) || !mult8(a.B_stride, 3) || !mult8(a.C_stride, 3)) return false;
     if ((a.phases & MB200_SSD_PHASE_OUTPUT) && (!aligned16(a.out) || !mult8(a.out_stride, 3))) return false;

@@ -219,7 +219,8 @@ def ssd_status():
 
 
 def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit,
-                phases, out=None, final_states=None, range_decay=None, scratch=None, builtin_scratch=False):
+                phases, out=None, final_states=None, range_decay=None, scratch=None, builtin_scratch=False,
+                cu_seqlens=None, varlen_states=None):
     L.require_cuda(x, dt, A, B, C, D, z, dt_bias, initial_states, seq_idx)
     if builtin_scratch:
         # this path must not create device tensors: the caller supplies everything in its final form
@@ -249,6 +250,9 @@ def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_i
     a.D, a.z, a.dt_bias, a.seq_idx = L.ptr(D), L.ptr(z), L.ptr(dt_bias), L.ptr(seq_idx)
     a.initial_states, a.out, a.final_states = L.ptr(initial_states), L.ptr(out), L.ptr(final_states)
     a.range_decay = L.ptr(range_decay)
+    if cu_seqlens is not None:
+        cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
+        a.cu_seqlens, a.varlen_states, a.num_seqs = L.ptr(cu_seqlens), L.ptr(varlen_states), cu_seqlens.numel() - 1
     a.scratch, a.scratch_bytes = (None, 0) if builtin_scratch else (L.ptr(scratch), scratch.numel())
     L.set_strides(a.x_stride, x, 3)
     L.set_strides(a.dt_stride, dt, 3)
@@ -272,20 +276,31 @@ def mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bia
 
     x, z: (batch, seqlen, nheads, headdim); dt: (batch, seqlen, nheads); A, dt_bias: (nheads);
     B, C: (batch, seqlen, ngroups, dstate); D: (nheads,) or (nheads, headdim);
-    initial_states: (batch, nheads, headdim, dstate).
-    Returns ``out`` or ``(out, final_states)`` with final_states fp32 (batch, nheads, headdim, dstate).
-    Inter-chunk states are kept in fp32 whatever ``state_dtype`` asks for.
+    initial_states: (batch, nheads, headdim, dstate).  seq_idx: int (batch, seqlen) ids of packed sequences
+    (non-decreasing, starting at 0); cu_seqlens: int (num_sequences + 1), read only with
+    ``return_varlen_states`` (batch must then be 1).
+    Returns ``out``, ``(out, final_states)``, ``(out, varlen_states)`` or ``(out, final_states, varlen_states)``
+    like the reference; final_states fp32 (batch, nheads, headdim, dstate), varlen_states fp32
+    (num_sequences, nheads, headdim, dstate).  Inter-chunk states are kept in fp32 whatever ``state_dtype``
+    asks for.
     """
-    if return_varlen_states:
+    if not return_varlen_states:
+        cu_seqlens = None
+    else:
         assert cu_seqlens is not None, "cu_seqlens must be provided if return_varlen_states is True"
-        raise NotImplementedError("mamba_b200: return_varlen_states is not supported yet")
+        assert x.shape[0] == 1, "passing cu_seqlens to get the varlen states is only supported if batch dimension is 1"
     batch, seqlen, nheads, headdim = x.shape
     dstate = B.shape[-1]
     final_states = (torch.empty(batch, nheads, headdim, dstate, device=x.device, dtype=torch.float32)
                     if return_final_states else None)
+    varlen_states = (torch.empty(cu_seqlens.numel() - 1, nheads, headdim, dstate, device=x.device, dtype=torch.float32)
+                     if cu_seqlens is not None else None)
     out, _ = _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus,
-                         dt_limit, L.PHASE_ALL, final_states=final_states)
-    return out if not return_final_states else (out, final_states)
+                         dt_limit, L.PHASE_ALL, final_states=final_states, cu_seqlens=cu_seqlens,
+                         varlen_states=varlen_states)
+    if not return_varlen_states:
+        return out if not return_final_states else (out, final_states)
+    return (out, varlen_states) if not return_final_states else (out, final_states, varlen_states)
 
 
 def mamba_chunk_scan_combined_noalloc(x, dt, A, B, C, chunk_size, out, D=None, z=None, dt_bias=None, initial_states=None,

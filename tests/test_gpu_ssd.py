@@ -180,14 +180,60 @@ def test_sequence_split_in_two_ranges():
     assert_close(ssd_fold_state(incoming[1], loc[1][1], loc[1][0]), wfin, TOL_FP32, "folded summary")
 
 
+def _packed(seed, lens, H, P, G, N, dtype):
+    total = sum(lens)
+    inp = make(seed, 1, total, H, P, G, N, dtype)
+    seq_idx = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(lens)])[None]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    return inp, seq_idx, cu
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_FP32), (torch.bfloat16, TOL_BF16)])
+@pytest.mark.parametrize("Q,lens", [(64, [201, 56, 5]), (128, [1, 130, 127, 64, 300]), (256, [256, 512, 100]), (64, [64, 64])])
+def test_packed_sequences(dtype, tol, Q, lens):
+    """seq_idx: packed sequences must not interact -- equal to running every sequence on its own; and the
+    per-sequence end states (cu_seqlens / return_varlen_states) equal each run's final state.  This is how
+    the reference tests its varlen path (tests/ops/triton/test_ssd.py:30-78)."""
+    H, P, G, N = 4, 64, 2, 128
+    inp, seq_idx, cu = _packed(50 + Q, lens, H, P, G, N, dtype)
+    c = {k: _c(v) for k, v in inp.items()}
+    out, fin, var = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], z=c["z"], dt_bias=c["dt_bias"],
+                          seq_idx=seq_idx.to(DEV), cu_seqlens=cu.to(DEV), dt_softplus=True, return_final_states=True,
+                          return_varlen_states=True)
+    assert var.shape == (len(lens), H, P, N)
+    f = lambda t: None if t is None else t.float()
+    for i in range(len(lens)):
+        sl = slice(int(cu[i]), int(cu[i + 1]))
+        want, wfin = oracle.ssd_chunk_scan(f(inp["x"][:, sl]), f(inp["dt"][:, sl]), inp["A"], f(inp["B"][:, sl]), f(inp["C"][:, sl]),
+                                           Q, inp["D"], f(inp["z"][:, sl]), inp["dt_bias"], None, dt_softplus=True)
+        assert_close(out[:, sl], want, tol, f"packed out seq {i}")
+        assert_close(var[i:i + 1], wfin, tol, f"varlen state seq {i}")
+    assert_close(fin, var[-1:], tol, "final state is the last sequence's")
+
+
+def test_seq_idx_without_varlen_states():
+    inp, seq_idx, cu = _packed(61, [100, 92], 2, 16, 1, 16, torch.float32)
+    c = {k: _c(v) for k, v in inp.items()}
+    out = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 64, D=c["D"], z=c["z"], dt_bias=c["dt_bias"], seq_idx=seq_idx.to(DEV),
+                dt_softplus=True)
+    for i in range(2):
+        sl = slice(int(cu[i]), int(cu[i + 1]))
+        want, _ = oracle.ssd_chunk_scan(inp["x"][:, sl], inp["dt"][:, sl], inp["A"], inp["B"][:, sl], inp["C"][:, sl], 64, inp["D"],
+                                        inp["z"][:, sl], inp["dt_bias"], None, dt_softplus=True)
+        assert_close(out[:, sl], want, TOL_FP32, f"seq {i}")
+
+
 def test_unsupported_features_raise():
     inp = make(15, 1, 64, 2, 8, 1, 8, torch.float32)
     c = {k: _c(v) for k, v in inp.items()}
-    with pytest.raises(NotImplementedError):
-        _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 64, cu_seqlens=torch.tensor([0, 64], device=DEV),
-              return_varlen_states=True)
+    with pytest.raises(AssertionError, match="cu_seqlens must be provided"):
+        _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 64, return_varlen_states=True)
     with pytest.raises(AssertionError):
         _fn()(c["x"], c["dt"], c["A"][:1], c["B"], c["C"], 64)
+    two = make(15, 2, 64, 2, 8, 1, 8, torch.float32)
+    t = {k: _c(v) for k, v in two.items()}
+    with pytest.raises(AssertionError, match="batch dimension is 1"):
+        _fn()(t["x"], t["dt"], t["A"], t["B"], t["C"], 64, cu_seqlens=torch.tensor([0, 64], device=DEV), return_varlen_states=True)
 
 
 def bench_config2_inputs(b, H, L=4096, P=64, N=128, seed=1002):
