@@ -1,0 +1,73 @@
+"""Stand-in for the reference's compiled extension module ``selective_scan_cuda``.
+
+The reference's ``SelectiveScanFn.forward`` (mamba_ssm/ops/selective_scan_interface.py:36-68) calls
+``selective_scan_cuda.fwd(u, delta, A, B, C, D, z, delta_bias, delta_softplus)`` and expects
+``[out, x]`` or ``[out, x, out_z]`` back (csrc/selective_scan/selective_scan.cpp:226-336), where ``x``
+is ``(batch, dim, n_chunks, 2 * dstate)`` with the running state at the odd positions of the last chunk
+(the forward only ever reads ``x[:, :, -1, 1::2]``).  Installing this object under that name lets the
+reference's own Python run unmodified on top of libmamba_b200 for inference:
+
+    import sys, mamba_b200.compat
+    sys.modules["selective_scan_cuda"] = mamba_b200.compat.selective_scan_cuda
+
+``bwd`` is not provided (forward / inference only).
+"""
+import ctypes
+
+import torch
+
+from . import _lib as L
+
+_CHUNK = 2048   # the reference extension's chunk length (selective_scan.cpp:307)
+
+
+class _SelectiveScanCuda:
+    @staticmethod
+    def fwd(u, delta, A, B, C, D_, z_, delta_bias_, delta_softplus):
+        L.require_cuda(u, delta, A, B, C, D_, z_, delta_bias_)
+        if A.is_complex():
+            raise NotImplementedError("mamba_b200: complex A is not supported")
+        assert u.stride(-1) == 1 and delta.stride(-1) == 1, "u and delta must have a unit last stride"
+        batch, dim, seqlen = u.shape
+        dstate = A.shape[1]
+        B_var, C_var = B.dim() >= 3, C.dim() >= 3
+        assert (not B_var or B.dim() == 4) and (not C_var or C.dim() == 4), "variable B/C must be (batch, groups, dstate, seqlen)"
+        ngroups = B.shape[1] if B_var else (C.shape[1] if C_var else 1)
+        out = torch.empty_like(delta)
+        out_z = torch.empty_like(z_) if z_ is not None else None
+        n_chunks = (seqlen + _CHUNK - 1) // _CHUNK
+        x = torch.zeros(batch, dim, n_chunks, 2 * dstate, device=u.device, dtype=torch.float32)
+        last = torch.empty(batch, dim, dstate, device=u.device, dtype=torch.float32)
+        a = L.ScanArgs()
+        a.u, a.delta, a.A, a.B, a.C = L.ptr(u), L.ptr(delta), L.ptr(A.float()), L.ptr(B), L.ptr(C)
+        a.D = L.ptr(None if D_ is None else D_.float().contiguous())
+        a.delta_bias = L.ptr(None if delta_bias_ is None else delta_bias_.float().contiguous())
+        a.z = L.ptr(z_)
+        # with a gate the extension returns the ungated result as `out` and the gated one as `out_z`
+        a.out, a.out_pregate = (L.ptr(out_z), L.ptr(out)) if z_ is not None else (L.ptr(out), None)
+        a.last_state = L.ptr(last)
+        a.batch, a.dim, a.seqlen, a.dstate, a.ngroups = batch, dim, seqlen, dstate, ngroups
+        a.io_dtype = L.dtype_code(u.dtype)
+        a.B_variable, a.C_variable, a.delta_softplus = int(B_var), int(C_var), int(bool(delta_softplus))
+        a.device = u.device.index
+        L.set_strides(a.u_stride, u, 2)
+        L.set_strides(a.delta_stride, delta, 2)
+        L.set_strides(a.A_stride, A, 2)
+        L.set_strides(a.B_stride, B, 3 if B_var else 2)
+        L.set_strides(a.C_stride, C, 3 if C_var else 2)
+        if z_ is not None:
+            L.set_strides(a.z_stride, z_, 2)
+            L.set_strides(a.out_stride, out_z, 2)
+            L.set_strides(a.pregate_stride, out, 2)
+        else:
+            L.set_strides(a.out_stride, out, 2)
+        L.check(L.lib().mb200_selective_scan_fwd(ctypes.byref(a), L.stream_ptr(u.device)))
+        x[:, :, -1, 1::2] = last
+        return [out, x] if z_ is None else [out, x, out_z]
+
+    @staticmethod
+    def bwd(*args, **kwargs):
+        raise NotImplementedError("mamba_b200 serves the forward (inference) path only")
+
+
+selective_scan_cuda = _SelectiveScanCuda()

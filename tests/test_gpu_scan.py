@@ -183,6 +183,29 @@ def test_errors_mirror_the_reference():
         _fn()(c["u"], c["delta"].half(), c["A"], c["B"], c["C"])
 
 
+@pytest.mark.parametrize("many", [False, True])
+def test_extension_module_stand_in(many):
+    """mamba_b200.compat.selective_scan_cuda.fwd returns what the reference's SelectiveScanFn.forward consumes:
+    [out, x, out_z] with the ungated result in `out`, the gated one in `out_z`, and the last state at
+    x[:, :, -1, 1::2] (mamba_ssm/ops/selective_scan_interface.py:58-68)."""
+    from mamba_b200.compat import selective_scan_cuda
+    inp = make_inputs(81, 2, 4800 if many else 12, 300, 16, 1, torch.float32)
+    c = {k: v.to(DEV) for k, v in inp.items()}
+    out, x, out_z = selective_scan_cuda.fwd(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], c["z"], c["delta_bias"], True)
+    want_z, want_last = oracle.selective_scan(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"], inp["z"],
+                                              inp["delta_bias"], delta_softplus=True, return_last_state=True)
+    want = oracle.selective_scan(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"], None, inp["delta_bias"],
+                                 delta_softplus=True)
+    assert x.shape == (2, inp["u"].shape[1], 1, 32)
+    assert_close(out, want, TOL_FP32, "ungated out")
+    assert_close(out_z, want_z, TOL_FP32, "gated out_z")
+    assert_close(x[:, :, -1, 1::2], want_last, TOL_FP32, "last state slice")
+    out2, x2 = selective_scan_cuda.fwd(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], None, c["delta_bias"], True)
+    assert_close(out2, want, TOL_FP32, "no gate")
+    with pytest.raises(NotImplementedError):
+        selective_scan_cuda.bwd()
+
+
 def test_empty_batch():
     out = _fn()(torch.zeros(0, 4, 16, device=DEV), torch.zeros(0, 4, 16, device=DEV), torch.zeros(4, 8, device=DEV),
                 torch.zeros(0, 1, 8, 16, device=DEV), torch.zeros(0, 1, 8, 16, device=DEV))
