@@ -291,6 +291,18 @@ scan_fwd_kernel(const mb200_scan_args a, const int cpw, const int nblocks, const
 // streams its channel's rows 32 bytes at a time (whole sectors) with the next block prefetched into
 // L1; warps never synchronise with each other, so a CTA is one warp and the grid spreads evenly.
 constexpr int kSeqBytes = 32;   // bytes of one row a lane moves per block (two 16-byte packets)
+#ifndef MB200_SEQ_AHEAD
+#define MB200_SEQ_AHEAD 2
+#endif
+constexpr int kSeqAhead = MB200_SEQ_AHEAD;   // how many blocks ahead the L1 prefetch runs
+#ifndef MB200_SEQ_DT_UPFRONT
+#define MB200_SEQ_DT_UPFRONT 0
+#endif
+// Register cap: 2560 one-warp CTAs of the 2.8B-layer shape must all be resident at once (17.3 per SM);
+// 96 registers allow 20 per SM, 104 or more leave a second, nearly empty wave (0.70 ms -> 0.93 ms measured).
+#ifndef MB200_SEQ_MAXNREG
+#define MB200_SEQ_MAXNREG 96
+#endif
 
 template <typename T> struct SeqRaw { uint4 v[2]; };
 
@@ -332,7 +344,7 @@ __device__ __forceinline__ void seq_prefetch(const T *row, int t0, int L)
 }
 
 template <typename T, int NS>
-__global__ void __launch_bounds__(32, 18) scan_seq_kernel(const mb200_scan_args a, const int vec_flags)
+__global__ void __maxnreg__(MB200_SEQ_MAXNREG) scan_seq_kernel(const mb200_scan_args a, const int vec_flags)
 {
     constexpr int TB = kSeqBytes / sizeof(T);          // steps per block: 16 (16-bit) or 8 (fp32)
     constexpr int HS = NS / 2;                         // states per lane
@@ -402,13 +414,14 @@ __global__ void __launch_bounds__(32, 18) scan_seq_kernel(const mb200_scan_args 
         const SeqRaw<T> ru = seq_load(urow, t0, L, io_vec), rd = seq_load(drow, t0, L, io_vec);
         SeqRaw<T> rz;
         if (zrow) rz = seq_load(zrow, t0, L, io_vec);
-        if (blk + 1 < nblk) {       // next block's sectors start moving while this block is computed
-            seq_prefetch(urow, t0 + TB, L);
-            seq_prefetch(drow, t0 + TB, L);
-            if (zrow) seq_prefetch(zrow, t0 + TB, L);
+        {   // sectors of a later block start moving while this block is computed (kSeqAhead blocks of lead)
+            const int tp = t0 + kSeqAhead * TB;
+            seq_prefetch(urow, tp, L);
+            seq_prefetch(drow, tp, L);
+            if (zrow) seq_prefetch(zrow, tp, L);
             if (sn < N) {
-                seq_prefetch(Bsrc, t0 + TB + half * HP, L);
-                seq_prefetch(Csrc, t0 + TB + half * HP, L);
+                seq_prefetch(Bsrc, tp + half * HP, L);
+                seq_prefetch(Csrc, tp + half * HP, L);
             }
         }
         // my half of the block's dt values; the partner's arrive by shuffle inside the step loop
@@ -421,11 +434,26 @@ __global__ void __launch_bounds__(32, 18) scan_seq_kernel(const mb200_scan_args 
             dtm[i] = v;
         }
         __syncwarp();               // B/C tile of this block is in place
+#if MB200_SEQ_DT_UPFRONT
+        // the partner's half of the dt values, exchanged once per block so that no shuffle sits at the head of a
+        // step's dependency chain
+        float dta[TB];
+#pragma unroll
+        for (int i = 0; i < HP; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, dtm[i], 1);
+            dta[i] = half ? other : dtm[i];
+            dta[HP + i] = half ? dtm[i] : other;
+        }
+#endif
         float ym[HP];               // outputs of my half of the steps
 #pragma unroll
         for (int i = 0; i < TB; ++i) {
             const float uu = seq_get<T>(ru, i);
+#if MB200_SEQ_DT_UPFRONT
+            const float dl = dta[i];
+#else
             const float dl = __shfl_sync(0xffffffffu, dtm[i % HP], (lane & ~1) | (i / HP));
+#endif
             const float du = dl * uu;
             const uint64_t dl2 = pack2(dl, dl), du2 = pack2(du, du);
             uint64_t ya = pack2(Dd * uu, 0.f), yb = pack2(0.f, 0.f);
