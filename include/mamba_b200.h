@@ -72,6 +72,12 @@ typedef struct mb200_scan_args {
 
 int mb200_selective_scan_fwd(const mb200_scan_args *args, void *stream);
 
+/* Diagnostic, no counterpart in the reference.  The TMA-fed scan kernel bounds every wait on a copy or on
+ * another warp; when a wait runs out it stops and records a non-zero code in a per-device word instead of
+ * hanging.  This call copies that word to *status (0 = no wait has ever run out on `device`).  It
+ * synchronises with the device, so it belongs in tests and post-mortems, not on the hot path. */
+int mb200_scan_status(int device, int *status);
+
 /* ---------------------------------------------------------------------------------------------
  * Single-token decode state update, state modified in place.
  * Replaces the launch in selective_state_update (mamba_ssm/ops/triton/selective_state_update.py:

@@ -68,6 +68,7 @@ _PROTOTYPES = {
     "mb200_version": (ctypes.c_int, []),
     "mb200_last_error": (ctypes.c_char_p, []),
     "mb200_selective_scan_fwd": (ctypes.c_int, [ctypes.POINTER(ScanArgs), c_vp]),
+    "mb200_scan_status": (ctypes.c_int, [c_i32, ctypes.POINTER(c_i32)]),
     "mb200_selective_state_update": (ctypes.c_int, [ctypes.POINTER(SsuArgs), c_vp]),
     "mb200_ssd_scratch_bytes": (ctypes.c_int, [ctypes.POINTER(SsdArgs), ctypes.POINTER(ctypes.c_size_t)]),
     "mb200_ssd_chunk_scan_fwd": (ctypes.c_int, [ctypes.POINTER(SsdArgs), c_vp]),

@@ -15,6 +15,8 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "tc_sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace mb200 {
 namespace {
@@ -282,34 +284,44 @@ scan_fwd_kernel(const mb200_scan_args a, const int cpw, const int nblocks, const
 
 // ------------------------------------------------------------------------------------------------
 // Channel-parallel variant for dstate <= 16 with input-dependent B and C: time is sequential, a
-// channel belongs to a PAIR of lanes that split its states between them (16 channels per warp).
-// All lanes of a warp are at the same step, so B_t and C_t are warp-uniform (broadcast reads of a
-// tiny per-warp shared tile) and the only loop-carried dependence is one FMA per state: no scan tree,
-// no re-evaluation -- 4 FMA-pipe + 1 MUFU instruction per (step, state).  The pair also splits the
-// per-step scalar work: each lane evaluates softplus(dt) and silu(z) for half of the block's steps
-// and the partner gets dt by shuffle; the two partial outputs meet in one more shuffle.  A lane
-// streams its channel's rows 32 bytes at a time (whole sectors) with the next block prefetched into
-// L1; warps never synchronise with each other, so a CTA is one warp and the grid spreads evenly.
-constexpr int kSeqBytes = 32;   // bytes of one row a lane moves per block (two 16-byte packets)
+// channel belongs to FOUR lanes that split its states between them (8 channels per warp).  All
+// lanes of a warp are at the same step, so B_t and C_t are warp-uniform (broadcast reads of a small
+// shared tile) and the only loop-carried dependence is one FMA per state: no scan tree, no
+// re-evaluation -- 4 FMA-pipe + 1 MUFU instruction per (step, state).  Four states per lane keep a
+// lane at 56 registers, so 36 warps are resident per SM and the MUFU, FMA and load latencies of one
+// warp hide behind the others (with two lanes per channel and 96 registers the same loop ran at 17
+// warps per SM and was 2-3 % slower; one lane per channel needed 207 registers and a second wave).
+// A lane owns a quarter of each block's steps for the per-step scalars (softplus(dt), silu(z), the
+// output store: 8 bytes of each row per block); dt reaches the other three lanes by shuffle and the
+// four partial outputs meet in two butterfly shuffles.  A lane streams its channel's u row 32 bytes
+// at a time (whole sectors) with later blocks prefetched into L1.  The warps of a CTA share one
+// double-buffered B/C tile: the staging threads fetch the next block's packets into registers before
+// the block's steps and write them to the other buffer afterwards, so one CTA barrier per block
+// suffices.
+constexpr int kSeqBytes = 32;   // bytes of one u row a lane moves per block (two 16-byte packets)
 #ifndef MB200_SEQ_AHEAD
 #define MB200_SEQ_AHEAD 2
 #endif
 constexpr int kSeqAhead = MB200_SEQ_AHEAD;   // how many blocks ahead the L1 prefetch runs
-#ifndef MB200_SEQ_DT_UPFRONT
-#define MB200_SEQ_DT_UPFRONT 0
+#ifndef MB200_QUAD_WARPS
+#define MB200_QUAD_WARPS 4
 #endif
-// Register cap: 2560 one-warp CTAs of the 2.8B-layer shape must all be resident at once (17.3 per SM);
-// 96 registers allow 20 per SM, 104 or more leave a second, nearly empty wave (0.70 ms -> 0.93 ms measured).
-#ifndef MB200_SEQ_MAXNREG
-#define MB200_SEQ_MAXNREG 96
+// CTAs per SM the register allocation must allow: the 1280 four-warp CTAs of the 2.8B-layer shape must
+// all be resident at once (8.65 per SM); 9 per SM means 56 registers per lane.  With 64 registers only 8
+// fit, the last 96 CTAs form a second wave and the step takes 0.84 ms instead of 0.69 ms.
+#ifndef MB200_QUAD_MINB
+#define MB200_QUAD_MINB 9
 #endif
-
-template <typename T> struct SeqRaw { uint4 v[2]; };
 
 template <typename T>
-__device__ __forceinline__ float seq_get(const SeqRaw<T> &r, int i)
+__device__ __forceinline__ void seq_prefetch(const T *row, int t0, int L)
 {
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(r.v);
+    if (t0 < L) asm volatile("prefetch.global.L1 [%0];" ::"l"(row + t0));
+}
+
+template <typename T>
+__device__ __forceinline__ float words_get(const uint32_t *w, int i)
+{
     if constexpr (sizeof(T) == 4) {
         return __uint_as_float(w[i]);
     } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
@@ -321,179 +333,189 @@ __device__ __forceinline__ float seq_get(const SeqRaw<T> &r, int i)
     }
 }
 
-template <typename T>
-__device__ __forceinline__ SeqRaw<T> seq_load(const T *row, int t0, int L, bool vec_ok)
+// NB bytes (8, 16 or 32) of a row starting at element t0, zero-filled past L
+template <typename T, int NB>
+__device__ __forceinline__ void row_load(uint32_t (&w)[NB / 4], const T *row, int t0, int L, bool vec_ok)
 {
-    constexpr int TB = kSeqBytes / sizeof(T);
-    SeqRaw<T> r;
-    if (vec_ok && t0 + TB <= L) {
-        r.v[0] = *reinterpret_cast<const uint4 *>(row + t0);
-        r.v[1] = *(reinterpret_cast<const uint4 *>(row + t0) + 1);
-    } else {
-        T *e = reinterpret_cast<T *>(r.v);
+    constexpr int NE = NB / sizeof(T);
+    if (vec_ok && t0 + NE <= L) {
+        if constexpr (NB == 8) {
+            const uint2 r = *reinterpret_cast<const uint2 *>(row + t0);
+            w[0] = r.x; w[1] = r.y;
+        } else {
 #pragma unroll
-        for (int i = 0; i < TB; ++i) e[i] = (t0 + i < L) ? row[t0 + i] : from_float<T>(0.f);
+            for (int k = 0; k < NB / 16; ++k) {
+                const uint4 r = *(reinterpret_cast<const uint4 *>(row + t0) + k);
+                w[4 * k] = r.x; w[4 * k + 1] = r.y; w[4 * k + 2] = r.z; w[4 * k + 3] = r.w;
+            }
+        }
+    } else {
+        T *e = reinterpret_cast<T *>(w);
+#pragma unroll
+        for (int i = 0; i < NE; ++i) e[i] = (t0 + i < L) ? row[t0 + i] : from_float<T>(0.f);
     }
-    return r;
 }
 
-template <typename T>
-__device__ __forceinline__ void seq_prefetch(const T *row, int t0, int L)
+template <int HS>
+__device__ __forceinline__ void lds_pairs(const float *p, uint64_t (&v)[HS / 2])
 {
-    if (t0 < L) asm volatile("prefetch.global.L1 [%0];" ::"l"(row + t0));
+    if constexpr (HS % 4 == 0) {
+#pragma unroll
+        for (int q = 0; q < HS / 4; ++q) {
+            const ulonglong2 r = reinterpret_cast<const ulonglong2 *>(p)[q];
+            v[2 * q] = r.x;
+            v[2 * q + 1] = r.y;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < HS / 2; ++j) v[j] = reinterpret_cast<const uint64_t *>(p)[j];
+    }
 }
 
-template <typename T, int NS>
-__global__ void __maxnreg__(MB200_SEQ_MAXNREG) scan_seq_kernel(const mb200_scan_args a, const int vec_flags)
+template <typename T, int NS, int W>
+__global__ void __launch_bounds__(32 * W, MB200_QUAD_MINB) scan_quad_kernel(const mb200_scan_args a, const int vec_flags)
 {
+    constexpr int LPC = 4;                             // lanes per channel
     constexpr int TB = kSeqBytes / sizeof(T);          // steps per block: 16 (16-bit) or 8 (fp32)
-    constexpr int HS = NS / 2;                         // states per lane
-    constexpr int HP = TB / 2;                         // steps per 16-byte packet
-    __shared__ __align__(16) float Bs[TB * NS], Cs[TB * NS];
-    const int lane = threadIdx.x;
-    const int half = lane & 1;                         // which half of the states / of the block's steps is mine
+    constexpr int HS = NS / LPC;                       // states per lane
+    constexpr int HP = TB / LPC;                       // steps whose scalars this lane owns (8 bytes of a row)
+    constexpr int CPW = 32 / LPC;                      // channels per warp
+    constexpr int PK = 16 / sizeof(T);                 // elements of one 16-byte staging packet
+    static_assert(HS % 2 == 0 && HP * sizeof(T) == 8, "lane split");
+    __shared__ __align__(16) float Bs[2][TB * NS], Cs[2][TB * NS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane & (LPC - 1);                  // which quarter of the states / of the block's steps is mine
     const int N = a.dstate, L = a.seqlen;
     const int per_group = a.dim / a.ngroups;
-    const int blocks_per_group = (per_group + 15) / 16;
+    const int tiles_per_group = (per_group + CPW * W - 1) / (CPW * W);
     const int b = blockIdx.y;
-    const int g = blockIdx.x / blocks_per_group;
-    const int d = g * per_group + (blockIdx.x % blocks_per_group) * 16 + (lane >> 1);
+    const int g = blockIdx.x / tiles_per_group;
+    const int d = g * per_group + (blockIdx.x % tiles_per_group) * (CPW * W) + warp * CPW + (lane >> 2);
     const bool live = d < (g + 1) * per_group;
     const int dc = live ? d : g * per_group;            // idle lanes shadow a valid channel, store nothing
     const bool io_vec = vec_flags & 1, bc_vec = vec_flags & 2;
 
-    // states live as packed fp32 pairs: every multiply / FMA of the recurrence is one f32x2 instruction
     uint64_t A2[HS / 2], h[HS / 2];
 #pragma unroll
     for (int j = 0; j < HS / 2; ++j) {
         float av[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const int n = half * HS + 2 * j + e;
+            const int n = sub * HS + 2 * j + e;
             av[e] = n < N ? a.A[(int64_t)dc * a.A_stride[0] + (int64_t)n * a.A_stride[1]] * kLog2e : 0.f;
         }
         A2[j] = pack2(av[0], av[1]);
         h[j] = pack2(0.f, 0.f);
     }
     const float bias = a.delta_bias ? a.delta_bias[dc] : 0.f;
-    const float Dd = (a.D && half == 0) ? a.D[dc] : 0.f;   // the skip term is added once per pair
+    const float Dd = (a.D && sub == 0) ? a.D[dc] : 0.f;    // the skip term is added once per channel
     const T *urow = static_cast<const T *>(a.u) + (int64_t)b * a.u_stride[0] + (int64_t)dc * a.u_stride[1];
     const T *drow = static_cast<const T *>(a.delta) + (int64_t)b * a.delta_stride[0] + (int64_t)dc * a.delta_stride[1];
     const T *zrow = a.z ? static_cast<const T *>(a.z) + (int64_t)b * a.z_stride[0] + (int64_t)dc * a.z_stride[1] : nullptr;
     T *orow = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)dc * a.out_stride[1];
     T *prow = (a.z && a.out_pregate) ? static_cast<T *>(a.out_pregate) + (int64_t)b * a.pregate_stride[0] + (int64_t)dc * a.pregate_stride[1] : nullptr;
 
-    // B/C staging: the block's tile is N rows x 32 bytes = N x 2 packets; lane -> (row lane/2, packet lane%2)
-    const int sn = lane >> 1;
-    const T *Bsrc = static_cast<const T *>(a.B) + (int64_t)b * a.B_stride[0] + (int64_t)g * a.B_stride[1] + (int64_t)sn * a.B_stride[2];
-    const T *Csrc = static_cast<const T *>(a.C) + (int64_t)b * a.C_stride[0] + (int64_t)g * a.C_stride[1] + (int64_t)sn * a.C_stride[2];
-    auto bc_stage = [&](float *dst, const T *src, int t0) {
-        if (sn < NS) {
-            uint4 r = make_uint4(0, 0, 0, 0);
-            const int ts = t0 + half * HP;
-            if (sn < N) {
-                if (bc_vec && ts + HP <= L) {
-                    r = *reinterpret_cast<const uint4 *>(src + ts);
-                } else {
-                    T *e = reinterpret_cast<T *>(&r);
+    // B/C staging: 2 tensors x NS rows x 2 packets of 16 bytes per block; thread -> (tensor, row, packet)
+    const bool stager = tid < 4 * NS;
+    const int st_c = tid / (2 * NS), sn = (tid % (2 * NS)) >> 1, pk = tid & 1;
+    const T *ssrc = st_c ? static_cast<const T *>(a.C) + (int64_t)b * a.C_stride[0] + (int64_t)g * a.C_stride[1] + (int64_t)sn * a.C_stride[2]
+                         : static_cast<const T *>(a.B) + (int64_t)b * a.B_stride[0] + (int64_t)g * a.B_stride[1] + (int64_t)sn * a.B_stride[2];
+    auto stage_load = [&](int t0) {
+        uint4 r = make_uint4(0, 0, 0, 0);
+        const int ts = t0 + pk * PK;
+        if (stager && sn < N) {
+            if (bc_vec && ts + PK <= L) {
+                r = *reinterpret_cast<const uint4 *>(ssrc + ts);
+            } else {
+                T *e = reinterpret_cast<T *>(&r);
 #pragma unroll
-                    for (int i = 0; i < HP; ++i) e[i] = (ts + i < L) ? src[ts + i] : from_float<T>(0.f);
-                }
+                for (int i = 0; i < PK; ++i) e[i] = (ts + i < L) ? ssrc[ts + i] : from_float<T>(0.f);
             }
+        }
+        return r;
+    };
+    auto stage_store = [&](int buf, const uint4 &r) {
+        if (stager) {
+            float *dst = st_c ? Cs[buf] : Bs[buf];
             const T *e = reinterpret_cast<const T *>(&r);
 #pragma unroll
-            for (int i = 0; i < HP; ++i) dst[(half * HP + i) * NS + sn] = to_float(e[i]);
+            for (int i = 0; i < PK; ++i) dst[(pk * PK + i) * NS + sn] = to_float(e[i]);
         }
     };
 
     const int nblk = (L + TB - 1) / TB;
+    stage_store(0, stage_load(0));
+    uint32_t ru[kSeqBytes / 4], rd[2];
     for (int blk = 0; blk < nblk; ++blk) {
-        const int t0 = blk * TB;
-        bc_stage(Bs, Bsrc, t0);
-        bc_stage(Cs, Csrc, t0);
-        const SeqRaw<T> ru = seq_load(urow, t0, L, io_vec), rd = seq_load(drow, t0, L, io_vec);
-        SeqRaw<T> rz;
-        if (zrow) rz = seq_load(zrow, t0, L, io_vec);
-        {   // sectors of a later block start moving while this block is computed (kSeqAhead blocks of lead)
+        const int t0 = blk * TB, buf = blk & 1;
+        const int ts = t0 + sub * HP;                   // first of my own steps
+        __syncthreads();            // tile of this block in place; every warp is done with the other buffer
+        uint4 nbc = make_uint4(0, 0, 0, 0);
+        if (blk + 1 < nblk) nbc = stage_load(t0 + TB);
+        row_load<T, kSeqBytes>(ru, urow, t0, L, io_vec);
+        row_load<T, 8>(rd, drow, ts, L, io_vec);
+        uint32_t rz[2] = {0u, 0u};
+        if (zrow) row_load<T, 8>(rz, zrow, ts, L, io_vec);
+        {   // sectors of a later block start moving while this block is computed
             const int tp = t0 + kSeqAhead * TB;
             seq_prefetch(urow, tp, L);
-            seq_prefetch(drow, tp, L);
-            if (zrow) seq_prefetch(zrow, tp, L);
-            if (sn < N) {
-                seq_prefetch(Bsrc, tp + half * HP, L);
-                seq_prefetch(Csrc, tp + half * HP, L);
-            }
+            seq_prefetch(drow, tp + sub * HP, L);
+            if (zrow) seq_prefetch(zrow, tp + sub * HP, L);
+            if (stager && sn < N) seq_prefetch(ssrc, tp + pk * PK, L);
         }
-        // my half of the block's dt values; the partner's arrive by shuffle inside the step loop
         float dtm[HP];
 #pragma unroll
         for (int i = 0; i < HP; ++i) {
-            float v = (half ? seq_get<T>(rd, HP + i) : seq_get<T>(rd, i)) + bias;   // compile-time register indices
+            float v = words_get<T>(rd, i) + bias;
             if (a.delta_softplus) v = fast_softplus20(v);
-            if (t0 + half * HP + i >= L) v = 0.f;
+            if (ts + i >= L) v = 0.f;                   // steps past the end are the identity (1, 0)
             dtm[i] = v;
         }
-        __syncwarp();               // B/C tile of this block is in place
-#if MB200_SEQ_DT_UPFRONT
-        // the partner's half of the dt values, exchanged once per block so that no shuffle sits at the head of a
-        // step's dependency chain
-        float dta[TB];
-#pragma unroll
-        for (int i = 0; i < HP; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, dtm[i], 1);
-            dta[i] = half ? other : dtm[i];
-            dta[HP + i] = half ? dtm[i] : other;
-        }
-#endif
-        float ym[HP];               // outputs of my half of the steps
+        const float *Bt = Bs[buf] + sub * HS, *Ct = Cs[buf] + sub * HS;
+        float ym[HP];
 #pragma unroll
         for (int i = 0; i < TB; ++i) {
-            const float uu = seq_get<T>(ru, i);
-#if MB200_SEQ_DT_UPFRONT
-            const float dl = dta[i];
-#else
-            const float dl = __shfl_sync(0xffffffffu, dtm[i % HP], (lane & ~1) | (i / HP));
-#endif
+            const float uu = words_get<T>(ru, i);
+            const float dl = __shfl_sync(0xffffffffu, dtm[i % HP], (lane & ~(LPC - 1)) | (i / HP));
             const float du = dl * uu;
             const uint64_t dl2 = pack2(dl, dl), du2 = pack2(du, du);
-            uint64_t ya = pack2(Dd * uu, 0.f), yb = pack2(0.f, 0.f);
-            const ulonglong2 *Bt = reinterpret_cast<const ulonglong2 *>(Bs + i * NS + half * HS);
-            const ulonglong2 *Ct = reinterpret_cast<const ulonglong2 *>(Cs + i * NS + half * HS);
+            uint64_t bp[HS / 2], cp[HS / 2];
+            lds_pairs<HS>(Bt + i * NS, bp);
+            lds_pairs<HS>(Ct + i * NS, cp);
+            uint64_t ya = pack2(Dd * uu, 0.f);
 #pragma unroll
-            for (int q = 0; q < HS / 4; ++q) {
-                const ulonglong2 bb = Bt[q], cc = Ct[q];
+            for (int j = 0; j < HS / 2; ++j) {
                 float x0, x1;
-                unpack2(mul2(dl2, A2[2 * q]), x0, x1);
-                h[2 * q] = fma2(pack2(ex2(x0), ex2(x1)), h[2 * q], mul2(du2, bb.x));
-                ya = fma2(h[2 * q], cc.x, ya);
-                unpack2(mul2(dl2, A2[2 * q + 1]), x0, x1);
-                h[2 * q + 1] = fma2(pack2(ex2(x0), ex2(x1)), h[2 * q + 1], mul2(du2, bb.y));
-                yb = fma2(h[2 * q + 1], cc.y, yb);
+                unpack2(mul2(dl2, A2[j]), x0, x1);
+                h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(du2, bp[j]));
+                ya = fma2(h[j], cp[j], ya);
             }
-            float s0, s1, s2, s3;
+            float s0, s1;
             unpack2(ya, s0, s1);
-            unpack2(yb, s2, s3);
-            const float y = (s0 + s1) + (s2 + s3);
-            const float yt = y + __shfl_xor_sync(0xffffffffu, y, 1);
-            if ((i / HP) == 0) { if (!half) ym[i % HP] = yt; } else { if (half) ym[i % HP] = yt; }
+            float y = s0 + s1;
+            y += __shfl_xor_sync(0xffffffffu, y, 1);
+            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            if (sub == i / HP) ym[i % HP] = y;
         }
-        __syncwarp();               // every lane is done with the B/C tile before the next block overwrites it
         if (live) {
-            const int ts = t0 + half * HP;
             float yg[HP];
 #pragma unroll
             for (int i = 0; i < HP; ++i) {
-                float zz = 0.f;
-                if (zrow) zz = half ? seq_get<T>(rz, HP + i) : seq_get<T>(rz, i);
-                yg[i] = zrow ? ym[i] * fast_silu(zz) : ym[i];
+                if (zrow) {
+                    const float zz = words_get<T>(rz, i);
+                    if constexpr (std::is_same<T, __nv_bfloat16>::value) yg[i] = ym[i] * silu_for_bf16(zz);
+                    else yg[i] = ym[i] * fast_silu(zz);
+                } else {
+                    yg[i] = ym[i];
+                }
             }
             auto put = [&](T *row, const float (&v)[HP]) {
                 if (io_vec && ts + HP <= L) {
-                    uint4 o;
+                    uint2 o;
                     T *e = reinterpret_cast<T *>(&o);
 #pragma unroll
                     for (int i = 0; i < HP; ++i) e[i] = from_float<T>(v[i]);
-                    *reinterpret_cast<uint4 *>(row + ts) = o;
+                    *reinterpret_cast<uint2 *>(row + ts) = o;
                 } else {
 #pragma unroll
                     for (int i = 0; i < HP; ++i)
@@ -503,6 +525,7 @@ __global__ void __maxnreg__(MB200_SEQ_MAXNREG) scan_seq_kernel(const mb200_scan_
             put(orow, yg);
             if (prow) put(prow, ym);
         }
+        if (blk + 1 < nblk) stage_store(buf ^ 1, nbc);
     }
     if (a.last_state && live) {
         float *ls = a.last_state + ((int64_t)b * a.dim + d) * N;
@@ -510,13 +533,344 @@ __global__ void __maxnreg__(MB200_SEQ_MAXNREG) scan_seq_kernel(const mb200_scan_
         for (int j = 0; j < HS / 2; ++j) {
             float lo, hi;
             unpack2(h[j], lo, hi);
-            if (half * HS + 2 * j < N) ls[half * HS + 2 * j] = lo;
-            if (half * HS + 2 * j + 1 < N) ls[half * HS + 2 * j + 1] = hi;
+            if (sub * HS + 2 * j < N) ls[sub * HS + 2 * j] = lo;
+            if (sub * HS + 2 * j + 1 < N) ls[sub * HS + 2 * j + 1] = hi;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Warp-specialised variant of the channel-parallel scan (dstate <= 16, input-dependent B and C,
+// 16-byte aligned rows).  The lanes of a warp are 32 different CHANNELS, so B_t and C_t are read
+// from shared memory at one address per warp (a single wavefront per 128-bit load), and nothing in
+// the recurrence loop crosses lanes.  A CTA of three warps owns 32 channels of one batch row:
+//   warp 0   ("scalar" warp) streams the u, dt, z rows and the group's B/C rows as TMA tiles
+//            (32 bytes of every row per tile, SWIZZLE_32B so that each lane reads its own row without
+//            bank conflicts), evaluates softplus(dt) and hands (dt, u) for 8 steps at a time to the
+//            state warps through shared memory together with the B/C values converted to fp32; later
+//            it adds the two partial outputs, applies silu(z) and sends the output tile back with a
+//            TMA store;
+//   warps 1,2 ("state" warps) each keep half of the states of the 32 channels in registers and run
+//            the recurrence: per (step, state) one MUFU ex2 and four FMA-pipe operations, no shuffles.
+// Hand-offs are mbarriers: ready[2] (scalar -> state, 8 steps of dt/u/B/C in place) and ydone[2]
+// (state -> scalar, 8 steps of partial outputs in place), all buffers double.  The scalar warp runs
+// one hand-off ahead, and the TMA tiles two tiles ahead, of the recurrence.  Every wait is bounded;
+// on expiry the kernel records a code in g_scan_status, stops, and drains its outstanding copies.
+#ifndef MB200_SCAN_STREAM
+#define MB200_SCAN_STREAM 1
+#endif
+__device__ int g_scan_status;
+enum { kStScanFull = 31, kStScanZ, kStScanReady, kStScanYdone, kStScanAlign };
+
+constexpr int kStreamCh = 32;      // channels per CTA (lanes of a warp)
+constexpr int kHB = 8;             // steps per hand-off
+
+struct ScanMaps { CUtensorMap u, dt, z, out, B, C; };
+
+template <typename T, int NS>
+struct __align__(256) StreamSmem {
+    uint8_t u[2][kStreamCh * 32];
+    uint8_t dt[2][kStreamCh * 32];
+    uint8_t z[2][kStreamCh * 32];
+    uint8_t out[2][kStreamCh * 32];
+    uint8_t B[2][(NS * 32 + 255) / 256 * 256];
+    uint8_t C[2][(NS * 32 + 255) / 256 * 256];
+    float xd[2][2][kHB][kStreamCh];          // [buffer][dt | u][step][channel]
+    float bc[2][2][kHB * NS + 16];           // [buffer][B | C][step][state]; the pad puts B and C on different banks
+    float yp[2][2][kHB][kStreamCh];          // [buffer][state warp][step][channel]
+    uint64_t full[2], zfull[2], ready[2], ydone[2];
+};
+
+// byte offset of 16-byte chunk `chunk` of row `row` in a [rows x 32 B] SWIZZLE_32B tile (256-byte aligned)
+__device__ __forceinline__ int sw32_offset(int row, int chunk) { return row * 32 + ((chunk ^ ((row >> 2) & 1)) << 4); }
+
+template <typename T, int NS>
+__global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_args a, const __grid_constant__ ScanMaps maps)
+{
+    using namespace tc;
+    constexpr int TB = 32 / sizeof(T);                 // steps per tile (32 bytes of a row)
+    constexpr int HPT = TB / kHB;                      // hand-offs per tile: 2 (16-bit) or 1 (fp32)
+    constexpr int CPH = kHB * sizeof(T) / 16;          // 16-byte chunks per hand-off: 1 or 2
+    constexpr int HS = NS / 2;                         // states per lane of a state warp
+    extern __shared__ __align__(256) uint8_t smem_raw[];
+    StreamSmem<T, NS> &sm = *reinterpret_cast<StreamSmem<T, NS> *>(smem_raw);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int N = a.dstate, L = a.seqlen;
+    const int b = blockIdx.y;
+    const int ch0 = blockIdx.x * kStreamCh;
+    const int d = ch0 + lane;                          // my channel (dim is a multiple of 32 on this path)
+    const int g = ch0 / (a.dim / a.ngroups);
+    const int ntiles = (L + TB - 1) / TB, nhb = (L + kHB - 1) / kHB;
+    const bool has_z = a.z != nullptr;
+    int *status = &g_scan_status;
+    if (smem_u32(smem_raw) & 255u) {                   // the swizzle pattern of the tiles assumes this alignment
+        if (threadIdx.x == 0) atomicCAS(status, 0, kStScanAlign);
+        return;
+    }
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sm.full[i], 1);
+            mbar_init(&sm.zfull[i], 1);
+            mbar_init(&sm.ready[i], 1);
+            mbar_init(&sm.ydone[i], 2);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ scalar warp
+        constexpr uint32_t kTileBytes = 2 * kStreamCh * 32 + 2 * NS * 32;
+        auto issue_tile = [&](int k) {          // lane 0 only
+            const int s = k & 1;
+            mbar_expect_tx(&sm.full[s], kTileBytes);
+            tma_load_3d(sm.u[s], &maps.u, &sm.full[s], k * TB, ch0, b);
+            tma_load_3d(sm.dt[s], &maps.dt, &sm.full[s], k * TB, ch0, b);
+            tma_load_4d(sm.B[s], &maps.B, &sm.full[s], k * TB, 0, g, b);
+            tma_load_4d(sm.C[s], &maps.C, &sm.full[s], k * TB, 0, g, b);
+        };
+        auto issue_z = [&](int k) {             // lane 0 only
+            const int s = k & 1;
+            mbar_expect_tx(&sm.zfull[s], kStreamCh * 32);
+            tma_load_3d(sm.z[s], &maps.z, &sm.zfull[s], k * TB, ch0, b);
+        };
+        int issued = 0, zissued = 0, waited = 0, zwaited = 0;     // tiles requested / consumed (uniform across the warp)
+        if (lane == 0) {
+            prefetch_tmap(&maps.u); prefetch_tmap(&maps.dt); prefetch_tmap(&maps.B); prefetch_tmap(&maps.C);
+            prefetch_tmap(&maps.out);
+            if (has_z) prefetch_tmap(&maps.z);
+        }
+        for (int k = 0; k < 2 && k < ntiles; ++k) {
+            if (lane == 0) { issue_tile(k); if (has_z) issue_z(k); }
+            ++issued; ++zissued;
+        }
+        const float bias = a.delta_bias ? a.delta_bias[d] : 0.f;
+        const int st_t = lane / NS, st_n = lane % NS;     // my (tensor, state row) in the B/C conversion
+        const bool st_on = lane < 2 * NS;
+        bool ok = true;
+
+        auto prologue = [&](int hb) {
+            const int k = hb / HPT, s = k & 1, part = hb % HPT, buf = hb & 1;
+            if (part == 0) {
+                if (!mbar_wait(&sm.full[s], (k >> 1) & 1, status, kStScanFull)) { ok = false; return; }
+                ++waited;
+            }
+            uint32_t wd[CPH * 4], wu[CPH * 4];
+#pragma unroll
+            for (int c = 0; c < CPH; ++c) {
+                const int off = sw32_offset(lane, part * CPH + c);
+                const uint4 rd = *reinterpret_cast<const uint4 *>(sm.dt[s] + off);
+                const uint4 ru = *reinterpret_cast<const uint4 *>(sm.u[s] + off);
+                wd[4 * c] = rd.x; wd[4 * c + 1] = rd.y; wd[4 * c + 2] = rd.z; wd[4 * c + 3] = rd.w;
+                wu[4 * c] = ru.x; wu[4 * c + 1] = ru.y; wu[4 * c + 2] = ru.z; wu[4 * c + 3] = ru.w;
+            }
+            uint32_t wb[CPH * 4];
+            if (st_on) {
+                const uint8_t *src = st_t ? sm.C[s] : sm.B[s];
+#pragma unroll
+                for (int c = 0; c < CPH; ++c) {
+                    const uint4 r = *reinterpret_cast<const uint4 *>(src + sw32_offset(st_n, part * CPH + c));
+                    wb[4 * c] = r.x; wb[4 * c + 1] = r.y; wb[4 * c + 2] = r.z; wb[4 * c + 3] = r.w;
+                }
+            }
+            const int t0 = hb * kHB;
+#pragma unroll
+            for (int i = 0; i < kHB; ++i) {
+                float v = words_get<T>(wd, i) + bias;
+                if (a.delta_softplus) v = fast_softplus20(v);
+                if (t0 + i >= L) v = 0.f;               // steps past the end are the identity (1, 0)
+                sm.xd[buf][0][i][lane] = v;
+                sm.xd[buf][1][i][lane] = words_get<T>(wu, i);
+            }
+            if (st_on) {
+                float *dst = sm.bc[buf][st_t];
+#pragma unroll
+                for (int i = 0; i < kHB; ++i) dst[i * NS + st_n] = words_get<T>(wb, i);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                if ((part == HPT - 1 || hb == nhb - 1) && k + 2 < ntiles) issue_tile(k + 2);
+                mbar_arrive(&sm.ready[buf]);
+            }
+            if ((part == HPT - 1 || hb == nhb - 1) && k + 2 < ntiles) ++issued;
+        };
+
+        auto epilogue = [&](int hb) {
+            const int k = hb / HPT, s = k & 1, part = hb % HPT, buf = hb & 1;
+            if (!mbar_wait(&sm.ydone[buf], (hb >> 1) & 1, status, kStScanYdone)) { ok = false; return; }
+            if (part == 0) {
+                if (has_z) {
+                    if (!mbar_wait(&sm.zfull[s], (k >> 1) & 1, status, kStScanZ)) { ok = false; return; }
+                    ++zwaited;
+                }
+                if (k >= 2) {       // the store that last read this output tile has finished reading it
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
+                }
+            }
+            float y[kHB];
+#pragma unroll
+            for (int i = 0; i < kHB; ++i) y[i] = sm.yp[buf][0][i][lane] + sm.yp[buf][1][i][lane];
+            if (has_z) {
+                uint32_t wz[CPH * 4];
+#pragma unroll
+                for (int c = 0; c < CPH; ++c) {
+                    const uint4 r = *reinterpret_cast<const uint4 *>(sm.z[s] + sw32_offset(lane, part * CPH + c));
+                    wz[4 * c] = r.x; wz[4 * c + 1] = r.y; wz[4 * c + 2] = r.z; wz[4 * c + 3] = r.w;
+                }
+#pragma unroll
+                for (int i = 0; i < kHB; ++i) {
+                    const float zz = words_get<T>(wz, i);
+                    if constexpr (std::is_same<T, __nv_bfloat16>::value) y[i] *= silu_for_bf16(zz);
+                    else y[i] *= fast_silu(zz);
+                }
+            }
+            uint32_t wo[CPH * 4];
+            {
+                T *e = reinterpret_cast<T *>(wo);
+#pragma unroll
+                for (int i = 0; i < kHB; ++i) e[i] = from_float<T>(y[i]);
+            }
+#pragma unroll
+            for (int c = 0; c < CPH; ++c)
+                *reinterpret_cast<uint4 *>(sm.out[s] + sw32_offset(lane, part * CPH + c)) =
+                    make_uint4(wo[4 * c], wo[4 * c + 1], wo[4 * c + 2], wo[4 * c + 3]);
+            if (part == HPT - 1 || hb == nhb - 1) {
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&maps.out),
+                                 "r"(smem_u32(sm.out[s])), "r"(k * TB), "r"(ch0), "r"(b)
+                                 : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    if (has_z && k + 2 < ntiles) issue_z(k + 2);
+                }
+                if (has_z && k + 2 < ntiles) ++zissued;
+            }
+        };
+
+        prologue(0);
+        for (int hb = 0; hb < nhb && ok; ++hb) {
+            if (hb + 1 < nhb) prologue(hb + 1);
+            if (ok) epilogue(hb);
+        }
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (!ok) {      // stopped early: let the tiles already requested land before the CTA's shared memory goes away
+                for (int k = waited; k < issued; ++k) mbar_wait(&sm.full[k & 1], (k >> 1) & 1, status, kStScanFull);
+                if (has_z)
+                    for (int k = zwaited; k < zissued; ++k) mbar_wait(&sm.zfull[k & 1], (k >> 1) & 1, status, kStScanZ);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ state warps
+        const int w = warp - 1;
+        uint64_t A2[HS / 2], h[HS / 2];
+#pragma unroll
+        for (int j = 0; j < HS / 2; ++j) {
+            float av[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int n = w * HS + 2 * j + e;
+                av[e] = n < N ? a.A[(int64_t)d * a.A_stride[0] + (int64_t)n * a.A_stride[1]] * kLog2e : 0.f;
+            }
+            A2[j] = pack2(av[0], av[1]);
+            h[j] = pack2(0.f, 0.f);
+        }
+        const float Dd = (a.D && w == 0) ? a.D[d] : 0.f;     // the skip term is added once per channel
+        for (int hb = 0; hb < nhb; ++hb) {
+            const int buf = hb & 1;
+            if (!mbar_wait(&sm.ready[buf], (hb >> 1) & 1, status, kStScanReady)) break;
+            const float *Bt = sm.bc[buf][0] + w * HS, *Ct = sm.bc[buf][1] + w * HS;
+#pragma unroll
+            for (int i = 0; i < kHB; ++i) {
+                const float dl = sm.xd[buf][0][i][lane], uu = sm.xd[buf][1][i][lane];
+                const float du = dl * uu;
+                const uint64_t dl2 = pack2(dl, dl), du2 = pack2(du, du);
+                uint64_t bp[HS / 2], cp[HS / 2];
+                lds_pairs<HS>(Bt + i * NS, bp);
+                lds_pairs<HS>(Ct + i * NS, cp);
+                uint64_t ya = pack2(Dd * uu, 0.f), yb = pack2(0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < HS / 2; ++j) {
+                    float x0, x1;
+                    unpack2(mul2(dl2, A2[j]), x0, x1);
+                    h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(du2, bp[j]));
+                    if (j & 1) yb = fma2(h[j], cp[j], yb);
+                    else ya = fma2(h[j], cp[j], ya);
+                }
+                float s0, s1, s2, s3;
+                unpack2(ya, s0, s1);
+                unpack2(yb, s2, s3);
+                sm.yp[buf][w][i][lane] = (s0 + s1) + (s2 + s3);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.ydone[buf]);
+        }
+        if (a.last_state) {
+            float *ls = a.last_state + ((int64_t)b * a.dim + d) * N;
+#pragma unroll
+            for (int j = 0; j < HS / 2; ++j) {
+                float lo, hi;
+                unpack2(h[j], lo, hi);
+                if (w * HS + 2 * j < N) ls[w * HS + 2 * j] = lo;
+                if (w * HS + 2 * j + 1 < N) ls[w * HS + 2 * j + 1] = hi;
+            }
         }
     }
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// The warp-specialised kernel needs TMA-describable operands: 16-byte aligned bases and row strides, whole
+// groups of 32 channels, input-dependent B and C, and no separate pre-gate output.
+template <typename T>
+bool stream_eligible(const mb200_scan_args &a)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    if (a.dstate > 16 || !a.B_variable || !a.C_variable || a.out_pregate) return false;
+    if ((a.dim / a.ngroups) % kStreamCh != 0) return false;
+    if ((int64_t)a.batch * a.dim < 2LL * 32 * 148) return false;
+    auto ok2 = [&](const void *p, const int64_t *s) { return aligned16(p) && s[0] > 0 && s[1] > 0 && s[0] % VEC == 0 && s[1] % VEC == 0; };
+    auto ok3 = [&](const void *p, const int64_t *s) {
+        return aligned16(p) && s[0] > 0 && s[1] > 0 && s[2] > 0 && s[0] % VEC == 0 && s[1] % VEC == 0 && s[2] % VEC == 0;
+    };
+    if (!ok2(a.u, a.u_stride) || !ok2(a.delta, a.delta_stride) || !ok2(a.out, a.out_stride)) return false;
+    if (a.z && !ok2(a.z, a.z_stride)) return false;
+    if (!ok3(a.B, a.B_stride) || !ok3(a.C, a.C_stride)) return false;
+    return encode_fn() != nullptr;
+}
+
+template <typename T>
+int launch_stream(const mb200_scan_args &a, cudaStream_t stream)
+{
+    constexpr uint32_t TB = 32 / sizeof(T);
+    const int dtype = sizeof(T) == 4 ? MB200_F32 : (std::is_same<T, __half>::value ? MB200_F16 : MB200_BF16);
+    ScanMaps maps;
+    auto rows = [&](CUtensorMap *m, const void *p, const int64_t *st) {
+        const uint64_t dims[3] = {(uint64_t)a.seqlen, (uint64_t)a.dim, (uint64_t)a.batch};
+        const uint64_t sb[2] = {(uint64_t)st[1] * sizeof(T), (uint64_t)st[0] * sizeof(T)};
+        const uint32_t box[3] = {TB, (uint32_t)kStreamCh, 1};
+        return encode_tiled(m, dtype, p, 3, dims, sb, box, CU_TENSOR_MAP_SWIZZLE_32B);
+    };
+    auto bc = [&](CUtensorMap *m, const void *p, const int64_t *st, uint32_t ns) {
+        const uint64_t dims[4] = {(uint64_t)a.seqlen, (uint64_t)a.dstate, (uint64_t)a.ngroups, (uint64_t)a.batch};
+        const uint64_t sb[3] = {(uint64_t)st[2] * sizeof(T), (uint64_t)st[1] * sizeof(T), (uint64_t)st[0] * sizeof(T)};
+        const uint32_t box[4] = {TB, ns, 1, 1};
+        return encode_tiled(m, dtype, p, 4, dims, sb, box, CU_TENSOR_MAP_SWIZZLE_32B);
+    };
+    const uint32_t ns = a.dstate <= 8 ? 8 : 16;
+    bool ok = rows(&maps.u, a.u, a.u_stride) && rows(&maps.dt, a.delta, a.delta_stride) && rows(&maps.out, a.out, a.out_stride) &&
+              bc(&maps.B, a.B, a.B_stride, ns) && bc(&maps.C, a.C, a.C_stride, ns);
+    if (a.z) ok = ok && rows(&maps.z, a.z, a.z_stride);
+    else maps.z = maps.u;
+    if (!ok) return 1;      // the driver refused a map (unusual strides): the caller uses the register-staged kernel
+    dim3 grid(a.dim / kStreamCh, a.batch);
+    if (ns == 8) scan_stream_kernel<T, 8><<<grid, 96, sizeof(StreamSmem<T, 8>), stream>>>(a, maps);
+    else scan_stream_kernel<T, 16><<<grid, 96, sizeof(StreamSmem<T, 16>), stream>>>(a, maps);
+    return MB200_OK;
+}
 
 template <typename T>
 int launch_scan(const mb200_scan_args &a, cudaStream_t stream)
@@ -545,15 +899,22 @@ int launch_scan(const mb200_scan_args &a, cudaStream_t stream)
         bc_vec = bc_vec && (reinterpret_cast<uintptr_t>(a.C) % bc_align == 0) && a.C_stride[0] % 4 == 0 &&
                  a.C_stride[1] % 4 == 0 && a.C_stride[2] % 4 == 0;
     const int vec_flags = (io_vec ? 1 : 0) | (bc_vec ? 2 : 0);
-    // Enough independent channels to give every SM a few warps: one lane per channel, time sequential.
+#if MB200_SCAN_STREAM
+    if (stream_eligible<T>(a)) {
+        const int rc = launch_stream<T>(a, stream);
+        if (rc <= 0) return rc;
+    }
+#endif
+    // Enough independent channels to give every SM a few warps: four lanes per channel, time sequential.
     if (N <= 16 && a.B_variable && a.C_variable && (int64_t)a.batch * a.dim >= 2LL * 32 * 148) {
         // the B/C tile is fetched in 16-byte packets here
         const bool bc16 = bc_vec && aligned16(a.B) && aligned16(a.C) && a.B_stride[0] % VEC == 0 && a.B_stride[1] % VEC == 0 &&
                           a.B_stride[2] % VEC == 0 && a.C_stride[0] % VEC == 0 && a.C_stride[1] % VEC == 0 && a.C_stride[2] % VEC == 0;
         const int flags = (io_vec ? 1 : 0) | (bc16 ? 2 : 0);
-        dim3 grid(a.ngroups * ((per_group + 15) / 16), a.batch);
-        if (N <= 8) scan_seq_kernel<T, 8><<<grid, 32, 0, stream>>>(a, flags);
-        else scan_seq_kernel<T, 16><<<grid, 32, 0, stream>>>(a, flags);
+        constexpr int QW = MB200_QUAD_WARPS;
+        dim3 grid(a.ngroups * ((per_group + 8 * QW - 1) / (8 * QW)), a.batch);
+        if (N <= 8) scan_quad_kernel<T, 8, QW><<<grid, 32 * QW, 0, stream>>>(a, flags);
+        else scan_quad_kernel<T, 16, QW><<<grid, 32 * QW, 0, stream>>>(a, flags);
         return MB200_OK;
     }
     const size_t smem = sizeof(float) * (2 * kStateBlock * kTile + 2 * (size_t)chans * npad);
@@ -568,6 +929,16 @@ int launch_scan(const mb200_scan_args &a, cudaStream_t stream)
 
 }  // namespace
 }  // namespace mb200
+
+extern "C" int mb200_scan_status(int device, int *status)
+{
+    using namespace mb200;
+    if (!status) return fail(MB200_ERR_BAD_ARG, "scan_status: status is NULL");
+    if (int rc = enter_device(device)) return rc;
+    const cudaError_t e = cudaMemcpyFromSymbol(status, g_scan_status, sizeof(int));
+    if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "scan_status: %s", cudaGetErrorString(e));
+    return MB200_OK;
+}
 
 extern "C" int mb200_selective_scan_fwd(const mb200_scan_args *args, void *stream_)
 {

@@ -22,39 +22,16 @@
 // scratch buffer, skips the dependent work and still releases its TMEM before it exits.
 #include "ssd_common.cuh"
 #include "tc_sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace mb200 {
 
-// ---- host: tensor-map encoding through the driver entry point ---------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
+// ---- host: tensor maps of the 16-bit operands (SWIZZLE_128B tiles) -----------------------------------
+// fmt: 1 = bfloat16, 0 = float16 (the encoding of the MMA instruction descriptor)
 static bool encode_16bit(CUtensorMap *map, int fmt, const void *base, int rank, const uint64_t *dims, const uint64_t *strides_bytes,
                          const uint32_t *box)
 {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t gd[5], gs[4];
-    cuuint32_t bx[5], es[5];
-    for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
-    for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
-    const CUresult r = fn(map, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
-                          const_cast<void *>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    return encode_tiled(map, fmt == 1 ? MB200_BF16 : MB200_F16, base, rank, dims, strides_bytes, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 #ifdef MB200_SCAN_TRACE

@@ -35,7 +35,13 @@ def selective_scan_fn(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_
     Returns ``out`` (gated by silu(z) when z is given) or ``(out, last_state)`` with
     ``last_state`` (batch, dim, dstate) fp32.
     """
-    L.require_cuda(u, delta, A, B, C, D, z, delta_bias)
+    return _selective_scan(u, delta, A, B, C, D, z, delta_bias, delta_softplus, return_last_state)
+
+
+def _selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus=False, return_last_state=False,
+                    out=None):
+    """selective_scan_fn with an optional caller-provided ``out`` (batch, dim, seqlen; last stride 1)."""
+    L.require_cuda(u, delta, A, B, C, D, z, delta_bias, out)
     if A.is_complex():
         raise NotImplementedError("mamba_b200: complex A is not supported")
     u, delta, z = _last_dim_contiguous(u), _last_dim_contiguous(delta), _last_dim_contiguous(z)
@@ -71,7 +77,9 @@ def selective_scan_fn(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_
     if delta_bias is not None:
         assert delta_bias.shape == (dim,)
 
-    out = torch.empty_like(delta)
+    if out is None:
+        out = torch.empty_like(delta)
+    assert out.shape == u.shape and out.dtype == u.dtype and out.stride(-1) == 1, "out must match u, last stride 1"
     last_state = torch.empty(batch, dim, dstate, device=u.device, dtype=torch.float32) if return_last_state else None
 
     a = L.ScanArgs()
@@ -205,6 +213,17 @@ def _ssd_args(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx
 
 
 _last_ssd_scratch = None
+
+
+def scan_status(device=None):
+    """Status word of the TMA-fed selective-scan kernel on `device` (synchronises the device).
+
+    0 means no bounded wait of that kernel has ever run out on the device.  Meant for tests and
+    debugging; the operators themselves never synchronise."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    st = ctypes.c_int32(0)
+    L.check(L.lib().mb200_scan_status(dev, ctypes.byref(st)))
+    return int(st.value)
 
 
 def ssd_status():

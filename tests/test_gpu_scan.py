@@ -103,6 +103,39 @@ def test_many_channels(dtype, tol, L, N, groups):
     run_both(make_inputs(60 + L, 2, 4744, L, N, groups, dtype, bench_style=True), tol, f"many L{L} N{N} g{groups}")
 
 
+def _row_padded(t, mult=8):
+    """Same values in a buffer whose rows are padded to a multiple of `mult` elements (16-byte row strides with a
+    ragged length, as a slice of a larger activation buffer has)."""
+    L = t.shape[-1]
+    Lp = (L + mult - 1) // mult * mult
+    buf = t.new_zeros(*t.shape[:-1], Lp)
+    buf[..., :L] = t
+    return buf[..., :L]
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_FP32), (torch.bfloat16, TOL_BF16), (torch.float16, TOL_BF16)])
+@pytest.mark.parametrize("L,N,groups,gated", [(704, 16, 1, True), (333, 8, 2, True), (8, 16, 1, False), (1, 16, 1, True),
+                                              (1030, 12, 1, True), (23, 3, 2, False)])
+def test_tma_fed_kernel(dtype, tol, L, N, groups, gated):
+    """Whole groups of 32 channels with 16-byte aligned rows take the warp-specialised TMA-fed kernel: ragged
+    lengths (tiles that run past the end of the rows), dstate below 8 and 16, two groups, with and without gate."""
+    from mamba_b200 import ops
+    inp = make_inputs(90 + L, 2, 4800, L, N, groups, dtype, has_z=gated, has_D=gated, bench_style=True)
+    want, want_last = oracle.selective_scan(inp["u"].float(), inp["delta"].float(), inp["A"], inp["B"].float(),
+                                            inp["C"].float(), inp["D"], None if inp["z"] is None else inp["z"].float(),
+                                            inp["delta_bias"], delta_softplus=True, return_last_state=True)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    for k in ("u", "delta", "z", "B", "C"):
+        if c[k] is not None:
+            c[k] = _row_padded(c[k])
+    out = _row_padded(torch.empty_like(c["u"]))      # aligned rows for every tensor, so the TMA path is eligible
+    got, got_last = ops._selective_scan(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], c["z"], c["delta_bias"],
+                                        delta_softplus=True, return_last_state=True, out=out)
+    assert ops.scan_status() == 0
+    assert_close(got, want, tol, "tma-fed out")
+    assert_close(got_last, want_last, tol, "tma-fed last_state")
+
+
 def test_many_channels_unaligned_and_ungated():
     inp = make_inputs(71, 2, 4800, 77, 16, 1, torch.bfloat16, has_z=False, has_D=False)
     c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
