@@ -547,9 +547,9 @@ __global__ void __launch_bounds__(32 * W, MB200_QUAD_MINB) scan_quad_kernel(cons
 //   warp 0   ("scalar" warp) streams the u, dt, z rows and the group's B/C rows as TMA tiles
 //            (32 bytes of every row per tile, SWIZZLE_32B so that each lane reads its own row without
 //            bank conflicts), evaluates softplus(dt) and hands (dt, u) for 8 steps at a time to the
-//            state warps through shared memory together with the B/C values converted to fp32; later
-//            it adds the two partial outputs, applies silu(z) and sends the output tile back with a
-//            TMA store;
+//            state warps through shared memory (dt and dt*u) together with the B/C values converted to
+//            fp32; later it adds the two partial outputs and D*u, applies silu(z) and sends the output
+//            tile back with a TMA store;
 //   warps 1,2 ("state" warps) each keep half of the states of the 32 channels in registers and run
 //            the recurrence: per (step, state) one MUFU ex2 and four FMA-pipe operations, no shuffles.
 // Hand-offs are mbarriers: ready[2] (scalar -> state, 8 steps of dt/u/B/C in place) and ydone[2]
@@ -575,9 +575,12 @@ struct __align__(256) StreamSmem {
     uint8_t out[2][kStreamCh * 32];
     uint8_t B[2][(NS * 32 + 255) / 256 * 256];
     uint8_t C[2][(NS * 32 + 255) / 256 * 256];
-    float xd[2][2][kHB][kStreamCh];          // [buffer][dt | u][step][channel]
+    // per-channel rows of 8 steps (32 bytes) in the same chunk-swizzled layout as the tiles: a lane moves four
+    // steps with one conflict-free 128-bit access
+    float xd[2][2][kStreamCh * kHB];         // [buffer][dt | dt*u][channel][step]
+    float du[2][kStreamCh * kHB];            // [buffer][channel][step]: D*u, kept by the scalar warp for its epilogue
     float bc[2][2][kHB * NS + 16];           // [buffer][B | C][step][state]; the pad puts B and C on different banks
-    float yp[2][2][kHB][kStreamCh];          // [buffer][state warp][step][channel]
+    float yp[2][2][kStreamCh * kHB];         // [buffer][state warp][channel][step]
     uint64_t full[2], zfull[2], ready[2], ydone[2];
 };
 
@@ -646,6 +649,7 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
             ++issued; ++zissued;
         }
         const float bias = a.delta_bias ? a.delta_bias[d] : 0.f;
+        const float Dd = a.D ? a.D[d] : 0.f;
         const int st_t = lane / NS, st_n = lane % NS;     // my (tensor, state row) in the B/C conversion
         const bool st_on = lane < 2 * NS;
         bool ok = true;
@@ -675,13 +679,23 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
                 }
             }
             const int t0 = hb * kHB;
+            float dl[kHB], dlu[kHB], skip[kHB];
 #pragma unroll
             for (int i = 0; i < kHB; ++i) {
                 float v = words_get<T>(wd, i) + bias;
                 if (a.delta_softplus) v = fast_softplus20(v);
                 if (t0 + i >= L) v = 0.f;               // steps past the end are the identity (1, 0)
-                sm.xd[buf][0][i][lane] = v;
-                sm.xd[buf][1][i][lane] = words_get<T>(wu, i);
+                const float uu = words_get<T>(wu, i);
+                dl[i] = v;
+                dlu[i] = v * uu;
+                skip[i] = Dd * uu;
+            }
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int off = sw32_offset(lane, c);
+                *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(sm.xd[buf][0]) + off) = make_float4(dl[4 * c], dl[4 * c + 1], dl[4 * c + 2], dl[4 * c + 3]);
+                *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(sm.xd[buf][1]) + off) = make_float4(dlu[4 * c], dlu[4 * c + 1], dlu[4 * c + 2], dlu[4 * c + 3]);
+                *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(sm.du[buf]) + off) = make_float4(skip[4 * c], skip[4 * c + 1], skip[4 * c + 2], skip[4 * c + 3]);
             }
             if (st_on) {
                 float *dst = sm.bc[buf][st_t];
@@ -711,7 +725,16 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
             }
             float y[kHB];
 #pragma unroll
-            for (int i = 0; i < kHB; ++i) y[i] = sm.yp[buf][0][i][lane] + sm.yp[buf][1][i][lane];
+            for (int c = 0; c < 2; ++c) {
+                const int off = sw32_offset(lane, c);
+                const float4 p0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.yp[buf][0]) + off);
+                const float4 p1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.yp[buf][1]) + off);
+                const float4 sk = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.du[buf]) + off);
+                y[4 * c] = (p0.x + p1.x) + sk.x;
+                y[4 * c + 1] = (p0.y + p1.y) + sk.y;
+                y[4 * c + 2] = (p0.z + p1.z) + sk.z;
+                y[4 * c + 3] = (p0.w + p1.w) + sk.w;
+            }
             if (has_z) {
                 uint32_t wz[CPH * 4];
 #pragma unroll
@@ -778,32 +801,39 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
             A2[j] = pack2(av[0], av[1]);
             h[j] = pack2(0.f, 0.f);
         }
-        const float Dd = (a.D && w == 0) ? a.D[d] : 0.f;     // the skip term is added once per channel
         for (int hb = 0; hb < nhb; ++hb) {
             const int buf = hb & 1;
             if (!mbar_wait(&sm.ready[buf], (hb >> 1) & 1, status, kStScanReady)) break;
             const float *Bt = sm.bc[buf][0] + w * HS, *Ct = sm.bc[buf][1] + w * HS;
 #pragma unroll
-            for (int i = 0; i < kHB; ++i) {
-                const float dl = sm.xd[buf][0][i][lane], uu = sm.xd[buf][1][i][lane];
-                const float du = dl * uu;
-                const uint64_t dl2 = pack2(dl, dl), du2 = pack2(du, du);
-                uint64_t bp[HS / 2], cp[HS / 2];
-                lds_pairs<HS>(Bt + i * NS, bp);
-                lds_pairs<HS>(Ct + i * NS, cp);
-                uint64_t ya = pack2(Dd * uu, 0.f), yb = pack2(0.f, 0.f);
+            for (int c = 0; c < 2; ++c) {
+                const int off = sw32_offset(lane, c);
+                const float4 dlv = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.xd[buf][0]) + off);
+                const float4 duv = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.xd[buf][1]) + off);
+                const float dls[4] = {dlv.x, dlv.y, dlv.z, dlv.w}, dus[4] = {duv.x, duv.y, duv.z, duv.w};
+                float ys[4];
 #pragma unroll
-                for (int j = 0; j < HS / 2; ++j) {
-                    float x0, x1;
-                    unpack2(mul2(dl2, A2[j]), x0, x1);
-                    h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(du2, bp[j]));
-                    if (j & 1) yb = fma2(h[j], cp[j], yb);
-                    else ya = fma2(h[j], cp[j], ya);
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const int i = 4 * c + i4;
+                    const uint64_t dl2 = pack2(dls[i4], dls[i4]), du2 = pack2(dus[i4], dus[i4]);
+                    uint64_t bp[HS / 2], cp[HS / 2];
+                    lds_pairs<HS>(Bt + i * NS, bp);
+                    lds_pairs<HS>(Ct + i * NS, cp);
+                    uint64_t ya = pack2(0.f, 0.f), yb = pack2(0.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < HS / 2; ++j) {
+                        float x0, x1;
+                        unpack2(mul2(dl2, A2[j]), x0, x1);
+                        h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(du2, bp[j]));
+                        if (j & 1) yb = fma2(h[j], cp[j], yb);
+                        else ya = fma2(h[j], cp[j], ya);
+                    }
+                    float s0, s1, s2, s3;
+                    unpack2(ya, s0, s1);
+                    unpack2(yb, s2, s3);
+                    ys[i4] = (s0 + s1) + (s2 + s3);
                 }
-                float s0, s1, s2, s3;
-                unpack2(ya, s0, s1);
-                unpack2(yb, s2, s3);
-                sm.yp[buf][w][i][lane] = (s0 + s1) + (s2 + s3);
+                *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(sm.yp[buf][w]) + off) = make_float4(ys[0], ys[1], ys[2], ys[3]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.ydone[buf]);
