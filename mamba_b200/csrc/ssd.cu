@@ -370,6 +370,7 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         cudaError_t e = cudaMemsetAsync(base + lay.off_status, 0, sizeof(int), stream);
         if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: status reset: %s", cudaGetErrorString(e));
     }
+    const bool fused_states = tc && ssd_tc_stream_eligible(a);
     if (a.phases & MB200_SSD_PHASE_LOCAL) {
         const size_t cs_smem = sizeof(float) * Q * 33;
         if (cs_smem > 48 * 1024) {
@@ -378,7 +379,9 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         }
         ssd_cumsum_kernel<<<dim3(nc, a.batch, (a.nheads + 31) / 32), 256, cs_smem, stream>>>(a, dtb, dAb, nc);
         MB200_CHECK_LAUNCH("ssd chunk_cumsum");
-        if (tc) {
+        if (fused_states) {
+            if (int rc = ssd_tc_state_stream(a, lay, stream)) return rc;
+        } else if (tc) {
             if (int rc = ssd_tc_chunk_state(a, lay, stream)) return rc;
         } else {
             ssd_chunk_state_kernel<T><<<dim3(((a.headdim + 63) / 64) * ((a.dstate + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(
@@ -399,13 +402,16 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     if (a.phases & MB200_SSD_PHASE_OUTPUT) {
         mb200_ssd_args p = a;
         if (!(a.phases & MB200_SSD_PHASE_LOCAL)) p.range_decay = nullptr;
-        if (PN % 4 == 0)
+        if (fused_states) {
+            // the state-stream kernel has already left the entering states and the final state
+        } else if (PN % 4 == 0) {
             ssd_state_passing_kernel<4><<<dim3((unsigned)((PN / 4 + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
-        else
+        } else {
             ssd_state_passing_kernel<1><<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
+        }
         MB200_CHECK_LAUNCH("ssd state_passing");
         if (tc) {
-            if (int rc = ssd_tc_cb_and_scan(a, lay, stream)) return rc;
+            if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream)) return rc;
         } else {
             const int tq = (Q + 63) / 64;
             ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);

@@ -12,7 +12,8 @@ namespace mb200 {
 //                                              overwrites slot c with the state ENTERING chunk c
 //   cb      (batch, nchunks, ngroups, Q, Q)    C.B^T per chunk (lower block triangle only); fp32 for the
 //                                              general kernels, 16-bit in the same region for the tensor-core ones
-//   prev16  (batch, nchunks, nheads, P, N)     16-bit copy of the state entering each chunk (tensor-core path)
+//   prev16  (batch, nchunks, nheads, P, N)     16-bit copy of the state entering each chunk (tensor-core path);
+//                                              (.., N, P) when the fused state-stream kernel wrote it
 //   status  one int32 in the last 256 bytes    0 after a clean run; a kernel that gave up a bounded wait
 //                                              leaves its code here (the output is then invalid)
 struct SsdScratch {
@@ -40,6 +41,10 @@ inline SsdScratch ssd_scratch_layout(const mb200_ssd_args &a)
 // Tensor-core stages (ssd_tc.cu): whether the call qualifies, and the two launch groups.
 bool ssd_tc_eligible(const mb200_ssd_args &a);
 int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
-int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
+int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool states_np, cudaStream_t stream);
+// Chunk states and inter-chunk recurrence fused (one CTA per batch row and head); leaves the 16-bit entering
+// states in [n][p] order, which ssd_tc_cb_and_scan is told through states_np.
+bool ssd_tc_stream_eligible(const mb200_ssd_args &a);
+int ssd_tc_state_stream(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
 
 }  // namespace mb200

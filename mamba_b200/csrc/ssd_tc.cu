@@ -85,6 +85,21 @@ __device__ __forceinline__ uint8_t *align1024(uint8_t *p)
 {
     return reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
 }
+// Barrier over the 256 element-wise threads (named barrier 1) that also ANDs a predicate across them, so a
+// bounded wait that ran out in one warp stops every warp at the same point.
+__device__ __forceinline__ bool compute_barrier_and(bool p)
+{
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred q, o;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred o, 1, 256, q;\n\t"
+        "selp.u32 %0, 1, 0, o;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)p)
+        : "memory");
+    return r != 0;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr)
 {
     uint4 v;
@@ -263,6 +278,196 @@ __global__ void __launch_bounds__(kStateThreads) ssd_tc_chunk_state_kernel(const
     if (warp == 8) tmem_dealloc(tmem, 64);
 }
 
+// ====================================================================================== state stream
+// Chunk states and the inter-chunk recurrence in ONE pass: grid (nheads, batch), a CTA walks the chunks of its
+// (batch, head) in order, so the fp32 chunk states never leave the SM.  Per chunk c it forms
+// S_c^T[n,p] = sum_k B[k,n] (w_k x[k,p]) on the tensor core exactly as the chunk-state kernel does, keeps the
+// running state H in registers (thread = one state index n and 32 columns p), stores the state ENTERING chunk
+// c as a 16-bit [n][p] tile (the B operand of the chunk-scan kernel's C.H product, fetched there by TMA) and
+// folds H <- exp(dA_last_c) H + S_c.  After the last chunk H is the final state.
+// 320 threads: warps 0-7 weight the x rows and own the running state, warp 8 issues TMA loads, warp 9 the
+// MMAs.  Shared memory: 4 stages of half a chunk (B 2 x 16 KB + x 16 KB for 128 steps) and one 16 KB state
+// tile; TMEM: two accumulators of 64 columns, so the MMAs of chunk c overlap the fold of chunk c-1.
+#ifndef MB200_SSD_STREAM_MIN_UNITS
+#define MB200_SSD_STREAM_MIN_UNITS 74
+#endif
+constexpr int kStreamThreads = 320;
+constexpr uint32_t kStreamStage = 49152;
+constexpr uint32_t kStreamSmem = 4 * kStreamStage + 16384 + 256 + 1024;
+enum { kStStreamFull = 41, kStStreamWeighted, kStStreamEmpty, kStStreamAcc, kStStreamAccEmpty };
+
+template <typename T>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
+                           const __grid_constant__ CUtensorMap tm_Hs, const float *dtb, const float *dAb, const float *initial,
+                           float *final_states, int nchunks, int nheads, int heads_per_group, int *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *sm = align1024(smem_raw);
+    uint8_t *tile = sm + 4 * kStreamStage;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tile + 16384);
+    uint64_t *full = bars, *weighted = bars + 4, *empty = bars + 8, *acc_full = bars + 12, *acc_empty = bars + 14;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int g = h / heads_per_group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nstages = 2 * nchunks;
+    if (threadIdx.x == 256) {
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&weighted[i], 8);      // one arrival per element-wise warp
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 8);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 8) tmem_alloc(tmem_slot, 128);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ TMA loads, up to 4 stages ahead
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < nstages; ++i) {
+                const int st = i & 3;
+                if (i >= 4 && !mbar_wait(&empty[st], ((i >> 2) - 1) & 1, status, kStStreamEmpty)) break;
+                uint8_t *dst = sm + st * kStreamStage;
+                const int t0 = i * 128;
+                mbar_expect_tx(&full[st], kStreamStage);
+                tma_load_4d(dst + 32768, &tm_x, &full[st], 0, h, t0, b);
+                tma_load_4d(dst, &tm_B, &full[st], 0, g, t0, b);
+                tma_load_4d(dst + 16384, &tm_B, &full[st], 64, g, t0, b);
+                ++issued;
+            }
+            // nothing may still be landing in this CTA's shared memory when it exits
+            for (int i = issued > 4 ? issued - 4 : 0; i < issued; ++i) mbar_wait(&full[i & 3], (i >> 2) & 1, status, kStStreamFull);
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMAs
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 1, 1);
+            bool ok = true;
+            for (int c = 0; c < nchunks && ok; ++c) {
+                const uint32_t acc = tmem + (uint32_t)(c & 1) * 64;
+                if (c >= 2) ok = mbar_wait(&acc_empty[c & 1], ((c >> 1) - 1) & 1, status, kStStreamAccEmpty);
+                for (int half = 0; half < 2 && ok; ++half) {
+                    const int i = 2 * c + half, st = i & 3;
+                    ok = mbar_wait(&weighted[st], (i >> 2) & 1, status, kStStreamWeighted);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t sb = smem_u32(sm + st * kStreamStage);
+                    for (int s = 0; s < 8; ++s)
+                        mma_f16_ss(acc, smem_desc_sw128(sb + s * 2048, 16384, 1024), smem_desc_sw128(sb + 32768 + s * 2048, 16, 1024), idesc,
+                                   (half | s) != 0);
+                    mma_commit(&empty[st]);
+                }
+                if (ok) mma_commit(&acc_full[c & 1]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ element-wise warps
+        const int tid = threadIdx.x;
+        const int r = tid >> 1, cq = (tid & 1) * 4;          // my x row inside a stage and my four 16-byte chunks of it
+        const int n = (warp & 3) * 32 + lane;                // TMEM lane = state index
+        const int p0 = (warp >> 2) * 32;                     // my half of the head's columns
+        const int64_t bh = (int64_t)b * nheads + h;
+        float H[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) H[j] = initial ? initial[bh * (kP * kN) + (int64_t)(p0 + j) * kN + n] : 0.f;
+        auto scalars = [&](int c, float (&v)[5]) {
+            const float *dAc = dAb + (bh * nchunks + c) * kQ, *dtc = dtb + (bh * nchunks + c) * kQ;
+            v[0] = dAc[r]; v[1] = dtc[r]; v[2] = dAc[128 + r]; v[3] = dtc[128 + r]; v[4] = dAc[kQ - 1];
+        };
+        float nxt[5];
+        scalars(0, nxt);
+        float dec_prev = 0.f;
+        bool ok = true;
+        auto fold = [&](int c, float dec) {      // H <- dec H + S_c once the MMAs of chunk c have completed
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(&acc_full[c & 1], (c >> 1) & 1, status, kStStreamAcc));   // tcgen05.ld is warp-collective
+            if (!ok) return;
+            tc_fence_after_sync();
+            float v[32];
+            tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(c & 1) * 64 + p0, v);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[c & 1]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) H[j] = fmaf(dec, H[j], v[j]);
+        };
+        for (int c = 0; c < nchunks && ok; ++c) {
+            float cur[5];
+#pragma unroll
+            for (int q = 0; q < 5; ++q) cur[q] = nxt[q];
+            if (c + 1 < nchunks) scalars(c + 1, nxt);
+            // weight my x rows of both halves: w_k = exp(dA_last - dA_k) dt_k
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int i = 2 * c + half, st = i & 3;
+                const float w = __expf(fminf(cur[4] - cur[2 * half], 0.f)) * cur[2 * half + 1];
+                ok = ok && mbar_wait(&full[st], (i >> 2) & 1, status, kStStreamFull);
+                if (ok) {
+                    const uint32_t base = smem_u32(sm + st * kStreamStage + 32768) + r * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const uint32_t addr = base + (((cq + ch) ^ (r & 7)) << 4);
+                        uint4 v = lds128(addr);
+                        uint32_t *e = reinterpret_cast<uint32_t *>(&v);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = Pack2<T>::unpack(e[q]);
+                            e[q] = Pack2<T>::pack(f.x * w, f.y * w);
+                        }
+                        sts128(addr, v);
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(&weighted[st]);
+            }
+            if (c > 0) fold(c - 1, dec_prev);
+            dec_prev = __expf(cur[4]);
+            // the state entering chunk c leaves as a 16-bit [n][p] tile
+            if (tid == 0) tma_store_wait_read();             // the previous store has finished reading the tile
+            ok = compute_barrier_and(ok);                    // from here on every element-wise warp agrees on ok
+            if (!ok) break;
+            {
+                const uint32_t row = smem_u32(tile) + n * 128;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 o;
+                    o.x = Pack2<T>::pack(H[8 * q + 0], H[8 * q + 1]);
+                    o.y = Pack2<T>::pack(H[8 * q + 2], H[8 * q + 3]);
+                    o.z = Pack2<T>::pack(H[8 * q + 4], H[8 * q + 5]);
+                    o.w = Pack2<T>::pack(H[8 * q + 6], H[8 * q + 7]);
+                    sts128(row + ((((p0 >> 3) + q) ^ (n & 7)) << 4), o);
+                }
+            }
+            fence_proxy_async();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (tid == 0 && ok) {
+                tma_store_3d(&tm_Hs, tile, 0, 0, (int)((((int64_t)b * nchunks + c) * nheads) + h));
+                tma_store_commit();
+            }
+        }
+        if (ok) fold(nchunks - 1, dec_prev);
+        if (ok && final_states) {
+            float *F = final_states + bh * (kP * kN);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) F[(p0 + j) * kN + n] = H[j];
+        }
+        if (tid == 0) tma_store_wait_read();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) tmem_dealloc(tmem, 128);
+}
+
 // ====================================================================================== chunk scan
 // grid (nheads, nchunks * 2, batch), 288 threads: warps 0-7 element-wise + epilogue (thread = one row and one
 // 32-column half), warp 8 TMA + MMA.  A "block" is a 64-wide slice of the mask product: the CB tile [128 x 64]
@@ -303,7 +508,7 @@ __global__ void __launch_bounds__(kScanThreads, 3)
 ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_C,
                          const __grid_constant__ CUtensorMap tm_H, const __grid_constant__ CUtensorMap tm_CB,
                          const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_out, const mb200_ssd_args a,
-                         const float *dtb, const float *dAb, int nchunks, int *status)
+                         const float *dtb, const float *dAb, int nchunks, int h_np, int *status)
 {
     extern __shared__ __align__(1024) uint8_t sm[];
     constexpr uint32_t kSlot = 24576, kSlotX = 16384;   // a slot: CB tile, then 64 rows of x
@@ -390,19 +595,23 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 mbar_expect_tx(bar_c, 32768 + 16384);
                 for (int kb = 0; kb < 2; ++kb) {
                     tma_load_4d(Cs + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
-                    tma_load_3d(Hs + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
+                    if (!h_np) tma_load_3d(Hs + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
                 }
+                if (h_np) tma_load_3d(Hs, &tm_H, bar_c, 0, 0, (int)unit_h);     // one [128 n x 64 p] tile
             }
             // Y1 = C . H^T, then area A is free for blocks 1 and 2
             ok = ok && mbar_wait(bar_c, 0, status, kStBarC);
             MB200_TRACE(1);
             if (ok) {
                 tc_fence_after_sync();
-                const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 0, 0);
+                // the entering state is either [p][n] (two K-major boxes) or [n][p] (one tile, N-major B operand)
+                const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 0, h_np ? 1 : 0);
                 for (int kb = 0; kb < 2; ++kb)
                     for (int s = 0; s < 4; ++s)
                         mma_f16_ss(tmem, smem_desc_sw128(smem_u32(Cs + kb * 16384) + s * 32, 16, 1024),
-                                   smem_desc_sw128(smem_u32(Hs + kb * 8192) + s * 32, 16, 1024), idesc, (kb | s) != 0);
+                                   h_np ? smem_desc_sw128(smem_u32(Hs) + kb * 8192 + s * 2048, 16, 1024)
+                                        : smem_desc_sw128(smem_u32(Hs + kb * 8192) + s * 32, 16, 1024),
+                                   idesc, (kb | s) != 0);
             }
             mma_commit(bar_g1);
             ok = ok && mbar_wait(bar_g1, 0, status, kStBarG1);
@@ -590,7 +799,7 @@ struct TcMaps {
 };
 
 template <typename T>
-int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream_t stream)
+int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np, cudaStream_t stream)
 {
     char *base = static_cast<char *>(a.scratch);
     float *dtb = reinterpret_cast<float *>(base + lay.off_dt);
@@ -605,8 +814,9 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
     {
         const uint64_t d[4] = {(uint64_t)kP, (uint64_t)a.nheads, L, (uint64_t)a.batch};
         const uint64_t s[3] = {(uint64_t)a.x_stride[2] * 2, (uint64_t)a.x_stride[1] * 2, (uint64_t)a.x_stride[0] * 2};
-        const uint32_t bx256[4] = {64, 1, 256, 1}, bx64[4] = {64, 1, 64, 1};
-        if (!encode_16bit(&tx, fmt, a.x, 4, d, s, stage == 0 ? bx256 : bx64)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for x failed");
+        const uint32_t bx256[4] = {64, 1, 256, 1}, bx128[4] = {64, 1, 128, 1}, bx64[4] = {64, 1, 64, 1};
+        if (!encode_16bit(&tx, fmt, a.x, 4, d, s, stage == 0 ? bx256 : (stage == 2 ? bx128 : bx64)))
+            return fail(MB200_ERR_LAUNCH, "ssd: tensor map for x failed");
     }
     {
         const uint64_t d[4] = {(uint64_t)kN, (uint64_t)a.ngroups, L, (uint64_t)a.batch};
@@ -617,6 +827,18 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
         if (!encode_16bit(&tC, fmt, a.C, 4, d, sC, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for C failed");
     }
     const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = kScanSmem;
+    if (stage == 2) {
+        CUtensorMap tHs;
+        const uint64_t d[3] = {(uint64_t)kP, (uint64_t)kN, (uint64_t)a.batch * nc * a.nheads};
+        const uint64_t s[2] = {(uint64_t)kP * 2, (uint64_t)kN * kP * 2};
+        const uint32_t bx[3] = {64, 128, 1};
+        if (!encode_16bit(&tHs, fmt, prev16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for states failed");
+        cudaFuncSetAttribute(ssd_tc_state_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmem);
+        ssd_tc_state_stream_kernel<T><<<dim3(a.nheads, a.batch), kStreamThreads, kStreamSmem, stream>>>(
+            tx, tB, tHs, dtb, dAb, a.initial_states, a.final_states, nc, a.nheads, a.nheads / a.ngroups, status);
+        MB200_CHECK_LAUNCH("ssd state stream (tensor core)");
+        return MB200_OK;
+    }
     if (stage == 0) {
         cudaFuncSetAttribute(ssd_tc_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state);
         ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kStateThreads, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
@@ -624,7 +846,12 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
         MB200_CHECK_LAUNCH("ssd chunk_state (tensor core)");
         return MB200_OK;
     }
-    {
+    if (h_np) {
+        const uint64_t d[3] = {(uint64_t)kP, (uint64_t)kN, (uint64_t)a.batch * nc * a.nheads};
+        const uint64_t s[2] = {(uint64_t)kP * 2, (uint64_t)kN * kP * 2};
+        const uint32_t bx[3] = {64, 128, 1};
+        if (!encode_16bit(&tH, fmt, prev16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for states failed");
+    } else {
         const uint64_t d[3] = {(uint64_t)kN, (uint64_t)kP, (uint64_t)a.batch * nc * a.nheads};
         const uint64_t s[2] = {(uint64_t)kN * 2, (uint64_t)kN * kP * 2};
         const uint32_t bx[3] = {64, 64, 1};
@@ -651,7 +878,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, cudaStream
     ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
     MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
     cudaFuncSetAttribute(ssd_tc_chunk_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scan);
-    ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, status);
+    ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, h_np ? 1 : 0, status);
     MB200_CHECK_LAUNCH("ssd chunk_scan (tensor core)");
     return MB200_OK;
 }
@@ -672,12 +899,24 @@ bool ssd_tc_eligible(const mb200_ssd_args &a)
 
 int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
 {
-    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 0, stream) : run_tc<__half>(a, lay, 0, stream);
+    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 0, false, stream) : run_tc<__half>(a, lay, 0, false, stream);
 }
 
-int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
+int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool states_np, cudaStream_t stream)
 {
-    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 1, stream) : run_tc<__half>(a, lay, 1, stream);
+    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 1, states_np, stream) : run_tc<__half>(a, lay, 1, states_np, stream);
+}
+
+// One (batch, head) per CTA: worth it once those fill at least half of the SMs; the whole operator in one call,
+// no range summary asked for.
+bool ssd_tc_stream_eligible(const mb200_ssd_args &a)
+{
+    return a.phases == MB200_SSD_PHASE_ALL && !a.range_decay && (int64_t)a.batch * a.nheads >= MB200_SSD_STREAM_MIN_UNITS;
+}
+
+int ssd_tc_state_stream(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
+{
+    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 2, true, stream) : run_tc<__half>(a, lay, 2, true, stream);
 }
 
 }  // namespace mb200

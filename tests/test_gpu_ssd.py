@@ -101,6 +101,16 @@ def test_tensor_core_shapes(dtype, L, G, H, init, D_hdim, has_z):
              f"tc L{L} G{G} H{H}")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,L,G,H,init,has_z", [(2, 1024, 1, 40, False, True), (1, 700, 8, 80, True, False),
+                                                 (3, 256, 2, 26, True, True), (2, 100, 1, 37, False, True)])
+def test_fused_state_stream_shapes(dtype, b, L, G, H, init, has_z):
+    """Enough (batch, head) pairs (>= 74) for the kernel that fuses the chunk states with the inter-chunk
+    recurrence: several chunks, a ragged tail, a single short chunk, groups, initial states."""
+    run_both(make(140 + L, b, L, H, 64, G, 128, dtype, has_z=has_z, init=init), 256, TOL_BF16,
+             f"stream b{b} L{L} G{G} H{H}")
+
+
 def test_dt_limit_and_no_softplus():
     inp = make(11, 1, 128, 2, 16, 1, 16, torch.float32)
     inp["dt"] = inp["dt"].abs() * 0.1
