@@ -62,23 +62,39 @@ __device__ __forceinline__ int seq_at(const mb200_ssd_args &a, int b, int t)
 // ---- stage 1 ------------------------------------------------------------------------------------
 // One CTA per (chunk, batch, 32 heads): coalesced read of dt over heads, transposed in shared
 // memory, then a warp scan along the chunk per head.
+template <typename TD>
 __global__ void __launch_bounds__(256) ssd_cumsum_kernel(const mb200_ssd_args a, float *dt_out, float *dA_out, int nchunks)
 {
     extern __shared__ float sm[];   // Q x 33
     const int Q = a.chunk_size;
     const int c = blockIdx.x, b = blockIdx.y, h0 = blockIdx.z * 32;
     const int t0 = c * Q;
-    for (int e = threadIdx.x; e < Q * 32; e += 256) {
-        const int k = e / 32, hh = e % 32;
-        const int h = h0 + hh;
-        float v = 0.f;
-        if (h < a.nheads && t0 + k < a.seqlen) {
-            v = load_any(a.dt, a.dt_dtype, (int64_t)b * a.dt_stride[0] + (int64_t)(t0 + k) * a.dt_stride[1] + (int64_t)h * a.dt_stride[2]);
-            if (a.dt_bias) v += a.dt_bias[h];
-            if (a.dt_softplus) v = softplus20(v);
-            v = fminf(fmaxf(v, a.dt_min), a.dt_max);
+    // a thread keeps one head (lane) and walks the steps 8 at a time: the 8 loads are issued back to back so
+    // that their latencies overlap instead of adding up
+    const int hh = threadIdx.x & 31, h = h0 + hh;
+    const bool h_ok = h < a.nheads;
+    const float bias = (h_ok && a.dt_bias) ? a.dt_bias[h] : 0.f;
+    const TD *src = static_cast<const TD *>(a.dt) + (int64_t)b * a.dt_stride[0] + (int64_t)h * a.dt_stride[2];
+    for (int k0 = threadIdx.x >> 5; k0 < Q; k0 += 64) {
+        TD raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int k = k0 + 8 * u;
+            raw[u] = (h_ok && k < Q && t0 + k < a.seqlen) ? src[(int64_t)(t0 + k) * a.dt_stride[1]] : from_float<TD>(0.f);
         }
-        sm[k * 33 + hh] = v;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int k = k0 + 8 * u;
+            if (k < Q) {
+                float v = 0.f;
+                if (h_ok && t0 + k < a.seqlen) {
+                    v = to_float(raw[u]) + bias;
+                    if (a.dt_softplus) v = fast_softplus20(v);
+                    v = fminf(fmaxf(v, a.dt_min), a.dt_max);
+                }
+                sm[k * 33 + hh] = v;
+            }
+        }
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -374,10 +390,15 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     if (a.phases & MB200_SSD_PHASE_LOCAL) {
         const size_t cs_smem = sizeof(float) * Q * 33;
         if (cs_smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(ssd_cumsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
+            cudaError_t e = cudaFuncSetAttribute(ssd_cumsum_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(ssd_cumsum_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(ssd_cumsum_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
             if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd chunk_cumsum: shared memory opt-in: %s", cudaGetErrorString(e));
         }
-        ssd_cumsum_kernel<<<dim3(nc, a.batch, (a.nheads + 31) / 32), 256, cs_smem, stream>>>(a, dtb, dAb, nc);
+        const dim3 cs_grid(nc, a.batch, (a.nheads + 31) / 32);
+        if (a.dt_dtype == MB200_F32) ssd_cumsum_kernel<float><<<cs_grid, 256, cs_smem, stream>>>(a, dtb, dAb, nc);
+        else if (a.dt_dtype == MB200_BF16) ssd_cumsum_kernel<__nv_bfloat16><<<cs_grid, 256, cs_smem, stream>>>(a, dtb, dAb, nc);
+        else ssd_cumsum_kernel<__half><<<cs_grid, 256, cs_smem, stream>>>(a, dtb, dAb, nc);
         MB200_CHECK_LAUNCH("ssd chunk_cumsum");
         if (fused_states) {
             if (int rc = ssd_tc_state_stream(a, lay, stream)) return rc;

@@ -85,15 +85,15 @@ __device__ __forceinline__ uint8_t *align1024(uint8_t *p)
 {
     return reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
 }
-// Barrier over the 256 element-wise threads (named barrier 1) that also ANDs a predicate across them, so a
-// bounded wait that ran out in one warp stops every warp at the same point.
-__device__ __forceinline__ bool compute_barrier_and(bool p)
+// Barrier over the 512 element-wise threads of the state-stream kernel (named barrier 1) that also ANDs a
+// predicate across them, so a bounded wait that ran out in one warp stops every warp at the same point.
+__device__ __forceinline__ bool stream_barrier_and(bool p)
 {
     uint32_t r;
     asm volatile(
         "{\n\t.reg .pred q, o;\n\t"
         "setp.ne.u32 q, %1, 0;\n\t"
-        "bar.red.and.pred o, 1, 256, q;\n\t"
+        "bar.red.and.pred o, 1, 512, q;\n\t"
         "selp.u32 %0, 1, 0, o;\n\t}"
         : "=r"(r)
         : "r"((uint32_t)p)
@@ -282,16 +282,18 @@ __global__ void __launch_bounds__(kStateThreads) ssd_tc_chunk_state_kernel(const
 // Chunk states and the inter-chunk recurrence in ONE pass: grid (nheads, batch), a CTA walks the chunks of its
 // (batch, head) in order, so the fp32 chunk states never leave the SM.  Per chunk c it forms
 // S_c^T[n,p] = sum_k B[k,n] (w_k x[k,p]) on the tensor core exactly as the chunk-state kernel does, keeps the
-// running state H in registers (thread = one state index n and 32 columns p), stores the state ENTERING chunk
+// running state H in registers (thread = one state index n and 16 columns p), stores the state ENTERING chunk
 // c as a 16-bit [n][p] tile (the B operand of the chunk-scan kernel's C.H product, fetched there by TMA) and
 // folds H <- exp(dA_last_c) H + S_c.  After the last chunk H is the final state.
-// 320 threads: warps 0-7 weight the x rows and own the running state, warp 8 issues TMA loads, warp 9 the
-// MMAs.  Shared memory: 4 stages of half a chunk (B 2 x 16 KB + x 16 KB for 128 steps) and one 16 KB state
+// 576 threads: warps 0-15 weight the x rows and own the running state (16 warps because this work is a chain
+// of shared-memory and TMEM round trips that only more warps in flight can hide), warp 16 issues TMA loads,
+// warp 17 the MMAs.  Shared memory: 4 stages of half a chunk (B 2 x 16 KB + x 16 KB for 128 steps) and one 16 KB state
 // tile; TMEM: two accumulators of 64 columns, so the MMAs of chunk c overlap the fold of chunk c-1.
 #ifndef MB200_SSD_STREAM_MIN_UNITS
 #define MB200_SSD_STREAM_MIN_UNITS 74
 #endif
-constexpr int kStreamThreads = 320;
+constexpr int kStreamWarps = 16;                       // element-wise warps
+constexpr int kStreamThreads = (kStreamWarps + 2) * 32;
 constexpr uint32_t kStreamStage = 49152;
 constexpr uint32_t kStreamSmem = 4 * kStreamStage + 16384 + 256 + 1024;
 enum { kStStreamFull = 41, kStStreamWeighted, kStStreamEmpty, kStStreamAcc, kStStreamAccEmpty };
@@ -312,25 +314,25 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
     const int g = h / heads_per_group;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nstages = 2 * nchunks;
-    if (threadIdx.x == 256) {
+    if (threadIdx.x == kStreamWarps * 32) {
         for (int i = 0; i < 4; ++i) {
             mbar_init(&full[i], 1);
-            mbar_init(&weighted[i], 8);      // one arrival per element-wise warp
+            mbar_init(&weighted[i], kStreamWarps);      // one arrival per element-wise warp
             mbar_init(&empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 8);
+            mbar_init(&acc_empty[i], kStreamWarps);
         }
         mbar_fence_init();
     }
-    if (warp == 8) tmem_alloc(tmem_slot, 128);
+    if (warp == kStreamWarps) tmem_alloc(tmem_slot, 128);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 8) {
+    if (warp == kStreamWarps) {
         // ------------------------------------------------------------------ TMA loads, up to 4 stages ahead
         if (lane == 0) {
             int issued = 0;
@@ -348,7 +350,7 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
             // nothing may still be landing in this CTA's shared memory when it exits
             for (int i = issued > 4 ? issued - 4 : 0; i < issued; ++i) mbar_wait(&full[i & 3], (i >> 2) & 1, status, kStStreamFull);
         }
-    } else if (warp == 9) {
+    } else if (warp == kStreamWarps + 1) {
         // ------------------------------------------------------------------ MMAs
         if (lane == 0) {
             const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 1, 1);
@@ -373,13 +375,13 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
     } else {
         // ------------------------------------------------------------------ element-wise warps
         const int tid = threadIdx.x;
-        const int r = tid >> 1, cq = (tid & 1) * 4;          // my x row inside a stage and my four 16-byte chunks of it
+        const int r = tid >> 2, cq = (tid & 3) * 2;          // my x row inside a stage and my two 16-byte chunks of it
         const int n = (warp & 3) * 32 + lane;                // TMEM lane = state index
-        const int p0 = (warp >> 2) * 32;                     // my half of the head's columns
+        const int p0 = (warp >> 2) * 16;                     // my quarter of the head's columns
         const int64_t bh = (int64_t)b * nheads + h;
-        float H[32];
+        float H[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) H[j] = initial ? initial[bh * (kP * kN) + (int64_t)(p0 + j) * kN + n] : 0.f;
+        for (int j = 0; j < 16; ++j) H[j] = initial ? initial[bh * (kP * kN) + (int64_t)(p0 + j) * kN + n] : 0.f;
         auto scalars = [&](int c, float (&v)[5]) {
             const float *dAc = dAb + (bh * nchunks + c) * kQ, *dtc = dtb + (bh * nchunks + c) * kQ;
             v[0] = dAc[r]; v[1] = dtc[r]; v[2] = dAc[128 + r]; v[3] = dtc[128 + r]; v[4] = dAc[kQ - 1];
@@ -392,13 +394,13 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
             ok = __all_sync(0xffffffffu, ok && mbar_wait(&acc_full[c & 1], (c >> 1) & 1, status, kStStreamAcc));   // tcgen05.ld is warp-collective
             if (!ok) return;
             tc_fence_after_sync();
-            float v[32];
-            tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(c & 1) * 64 + p0, v);
+            float v[16];
+            tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(c & 1) * 64 + p0, v);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[c & 1]);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) H[j] = fmaf(dec, H[j], v[j]);
+            for (int j = 0; j < 16; ++j) H[j] = fmaf(dec, H[j], v[j]);
         };
         for (int c = 0; c < nchunks && ok; ++c) {
             float cur[5];
@@ -414,7 +416,7 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
                 if (ok) {
                     const uint32_t base = smem_u32(sm + st * kStreamStage + 32768) + r * 128;
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
+                    for (int ch = 0; ch < 2; ++ch) {
                         const uint32_t addr = base + (((cq + ch) ^ (r & 7)) << 4);
                         uint4 v = lds128(addr);
                         uint32_t *e = reinterpret_cast<uint32_t *>(&v);
@@ -434,12 +436,12 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
             dec_prev = __expf(cur[4]);
             // the state entering chunk c leaves as a 16-bit [n][p] tile
             if (tid == 0) tma_store_wait_read();             // the previous store has finished reading the tile
-            ok = compute_barrier_and(ok);                    // from here on every element-wise warp agrees on ok
+            ok = stream_barrier_and(ok);                     // from here on every element-wise warp agrees on ok
             if (!ok) break;
             {
                 const uint32_t row = smem_u32(tile) + n * 128;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
+                for (int q = 0; q < 2; ++q) {
                     uint4 o;
                     o.x = Pack2<T>::pack(H[8 * q + 0], H[8 * q + 1]);
                     o.y = Pack2<T>::pack(H[8 * q + 2], H[8 * q + 3]);
@@ -449,7 +451,7 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
                 }
             }
             fence_proxy_async();
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync 1, 512;" ::: "memory");
             if (tid == 0 && ok) {
                 tma_store_3d(&tm_Hs, tile, 0, 0, (int)((((int64_t)b * nchunks + c) * nheads) + h));
                 tma_store_commit();
@@ -459,13 +461,13 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
         if (ok && final_states) {
             float *F = final_states + bh * (kP * kN);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) F[(p0 + j) * kN + n] = H[j];
+            for (int j = 0; j < 16; ++j) F[(p0 + j) * kN + n] = H[j];
         }
         if (tid == 0) tma_store_wait_read();
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 8) tmem_dealloc(tmem, 128);
+    if (warp == kStreamWarps) tmem_dealloc(tmem, 128);
 }
 
 // ====================================================================================== chunk scan
@@ -490,6 +492,9 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 //   range holds k = m   exact: exp(min(dA_m - dA_k, 0)) dt_k [k <= m] per element
 // The mask factors are rounded to the input dtype and applied with packed 16-bit multiplies (two roundings
 // per element instead of one; far inside the 16-bit tolerance, and it halves the instruction count).
+#ifndef MB200_SCAN_L2_PREFETCH
+#define MB200_SCAN_L2_PREFETCH 1
+#endif
 constexpr int kScanThreads = 288;
 constexpr uint32_t kScanSmem = 49152 + 24576 + 1024 + 1024 + 512 + 64 + 128 + 16;   // 76496 B, base must be 1 KB aligned
 #ifdef MB200_SCAN_TRACE
@@ -592,6 +597,12 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             // the first mask block is what the element-wise warps wait for: request it first, then C and H
             if (ok) {
                 load_block(0);
+#if MB200_SCAN_L2_PREFETCH
+                // the later x rows and the gate tile cannot be requested yet (their shared memory is still in use):
+                // have them brought into L2 now, so that the later requests are L2 hits
+                for (int j = 1; j < nk; ++j) tma_prefetch_l2_4d(&tm_x, 0, h, c * kQ + j * 64, b);
+                if (a.z) tma_prefetch_l2_4d(&tm_z, 0, h, c * kQ + mb * 128, b);
+#endif
                 mbar_expect_tx(bar_c, 32768 + 16384);
                 for (int kb = 0; kb < 2; ++kb) {
                     tma_load_4d(Cs + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
