@@ -32,8 +32,8 @@ if ROOT not in sys.path:
 # dram bytes (read + write) per launch of the dominant kernel from the committed ncu capture
 # (profiles/), or None where no capture exists for that workload.
 NCU_TRAFFIC_BYTES = {
-    "c1": 656_311_808,      # scan_seq_kernel: 505.4 MB read + 150.9 MB written
-    "c2": 2_357_000_000,    # five SSD launches summed (chunk_scan alone: 881.0 MB read + 310.1 MB written)
+    "c1": 656_877_312,      # scan_stream_kernel: 506.6 MB read + 150.3 MB written
+    "c2": 1_734_500_000,    # four SSD launches summed (state stream 368.4 + 153.6 MB, chunk_scan 880.9 + 309.5 MB)
     "c4": 1_291_591_424,    # ssu_packet_kernel: 676.8 MB read + 614.7 MB written
     "c0": None, "c3": None,
 }
@@ -118,7 +118,7 @@ class Workload:
             self.dtype = "bf16"
             self.step_inputs = ("x", "dt", "z", "B", "C")
             self.alg_bytes = 3 * b * L * H * P * 2 + b * L * H * 2 + 2 * b * L * 128 * 2 + b * H * P * 128 * 4 + 3 * H * 4
-            self.launches_per_step = 5
+            self.launches_per_step = 4      # cumsum, state stream, C.B^T, chunk scan
         elif name == "c3":
             # long sequence split into contiguous chunk ranges, one per rank; the whole sequence at N=1
             from mamba_b200.seqpar import split_sequence
@@ -139,7 +139,7 @@ class Workload:
             self.dtype = "bf16"
             self.step_inputs = ("x", "dt", "B", "C")
             self.alg_bytes = 2 * Lr * H * P * 2 + Lr * H * 2 + 2 * Lr * G * N * 2 + H * P * N * 4 + 3 * H * 4
-            self.launches_per_step = 5 if world == 1 else 7
+            self.launches_per_step = 4 if world == 1 else 7
             self.world = world
         elif name == "c4":
             host = make_c4(batch or 256)
