@@ -253,3 +253,33 @@ def bench_config2_inputs(b, H, L=4096, P=64, N=128, seed=1002):
 def test_bench_config2_slice_against_oracle():
     """bf16, seqlen 4096, headdim 64, dstate 128, chunk 256, one group: 1 batch row x 4 heads."""
     run_both(bench_config2_inputs(1, 4), 256, TOL_BF16, "config 2 slice")
+
+
+def test_bench_config2_full_size_properties():
+    """Full benchmark size (batch 8, 80 heads, seqlen 4096): the fused state-stream path.  Three heads of one batch
+    row against the oracle (heads are independent given their group's B and C), run-to-run bit identity (no
+    atomics anywhere), and agreement with the two-launch path that a sequence split takes."""
+    from mamba_b200 import ops
+    inp = bench_config2_inputs(8, 80)
+    c = {k: _c(v) for k, v in inp.items()}
+    kw = dict(D=c["D"], z=c["z"], dt_bias=c["dt_bias"], dt_softplus=True, return_final_states=True)
+    out1, fin1 = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 256, **kw)
+    assert _status() == 0
+    out2, fin2 = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 256, **kw)
+    assert torch.equal(out1, out2) and torch.equal(fin1, fin2)
+    row, heads = 5, torch.tensor([0, 41, 79])
+    f = lambda t: t.float()
+    want, wfin = oracle.ssd_chunk_scan(f(inp["x"][row:row + 1, :, heads]), f(inp["dt"][row:row + 1, :, heads]), inp["A"][heads],
+                                       f(inp["B"][row:row + 1]), f(inp["C"][row:row + 1]), 256, inp["D"][heads],
+                                       f(inp["z"][row:row + 1, :, heads]), inp["dt_bias"][heads], None, dt_softplus=True)
+    hd = heads.to(DEV)
+    assert_close(out1[row:row + 1, :, hd], want, TOL_BF16, "full-size subset out")
+    assert_close(fin1[row:row + 1, hd], wfin, TOL_BF16, "full-size subset final_states")
+    # the same operator in two phases (chunk states kept in memory, separate state passing)
+    st, dec, scratch = ops.ssd_local_states(c["x"], c["dt"], c["A"], c["B"], 256, dt_bias=c["dt_bias"], dt_softplus=True)
+    out3, fin3 = ops.ssd_finish(c["x"], c["dt"], c["A"], c["B"], c["C"], 256, scratch, D=c["D"], z=c["z"], dt_bias=c["dt_bias"],
+                                incoming_state=None, dt_softplus=True, return_final_states=True)
+    assert _status() == 0
+    assert_close(out3, out1.float(), TOL_BF16, "fused vs two-launch out")
+    assert_close(fin3, fin1, TOL_BF16, "fused vs two-launch final_states")
+    assert_close(st, fin1, TOL_BF16, "range state vs final state")
