@@ -139,7 +139,7 @@ class Workload:
             self.dtype = "bf16"
             self.step_inputs = ("x", "dt", "B", "C")
             self.alg_bytes = 2 * Lr * H * P * 2 + Lr * H * 2 + 2 * Lr * G * N * 2 + H * P * N * 4 + 3 * H * 4
-            self.launches_per_step = 4 if world == 1 else 7
+            self.launches_per_step = 4 if world == 1 else 6
             self.world = world
         elif name == "c4":
             host = make_c4(batch or 256)

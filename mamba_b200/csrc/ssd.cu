@@ -386,7 +386,18 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         cudaError_t e = cudaMemsetAsync(base + lay.off_status, 0, sizeof(int), stream);
         if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: status reset: %s", cudaGetErrorString(e));
     }
+    // Chunk states + inter-chunk recurrence in one streaming launch.  In a sequence split the LOCAL phase runs it
+    // from a zero state for the range summary only, and the OUTPUT phase runs it again from the incoming state
+    // (cheaper than keeping the fp32 chunk states in memory: they are 4x the size of x).
     const bool fused_states = tc && ssd_tc_stream_eligible(a);
+    // The LOCAL phase of this problem took the streaming launch (it does not see out / z): then the scratch holds
+    // no chunk states, and an OUTPUT phase that cannot stream has to form them itself.
+    bool local_streamed = false;
+    if (!(a.phases & MB200_SSD_PHASE_LOCAL) && !fused_states) {
+        mb200_ssd_args l = a;
+        l.phases = MB200_SSD_PHASE_LOCAL;
+        local_streamed = ssd_tc_eligible(l) && ssd_tc_stream_eligible(l);
+    }
     if (a.phases & MB200_SSD_PHASE_LOCAL) {
         const size_t cs_smem = sizeof(float) * Q * 33;
         if (cs_smem > 48 * 1024) {
@@ -409,7 +420,7 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
                 a, dtb, dAb, states, nc);
             MB200_CHECK_LAUNCH("ssd chunk_state");
         }
-        if (!(a.phases & MB200_SSD_PHASE_OUTPUT) && (a.final_states || a.range_decay)) {
+        if (!fused_states && !(a.phases & MB200_SSD_PHASE_OUTPUT) && (a.final_states || a.range_decay)) {
             // range summary only: fold the local chunk states from a zero state, leave the slots as they are
             mb200_ssd_args z = a;
             z.initial_states = nullptr;
@@ -423,8 +434,20 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     if (a.phases & MB200_SSD_PHASE_OUTPUT) {
         mb200_ssd_args p = a;
         if (!(a.phases & MB200_SSD_PHASE_LOCAL)) p.range_decay = nullptr;
+        if (local_streamed) {
+            if (tc) {
+                if (int rc = ssd_tc_chunk_state(a, lay, stream)) return rc;
+            } else {
+                ssd_chunk_state_kernel<T><<<dim3(((a.headdim + 63) / 64) * ((a.dstate + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(
+                    a, dtb, dAb, states, nc);
+                MB200_CHECK_LAUNCH("ssd chunk_state");
+            }
+        }
         if (fused_states) {
-            // the state-stream kernel has already left the entering states and the final state
+            // the entering states and the final state come from the state-stream kernel: it ran in the LOCAL half of
+            // this call, or runs now from the incoming state
+            if (!(a.phases & MB200_SSD_PHASE_LOCAL))
+                if (int rc = ssd_tc_state_stream(a, lay, stream)) return rc;
         } else if (PN % 4 == 0) {
             ssd_state_passing_kernel<4><<<dim3((unsigned)((PN / 4 + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
         } else {

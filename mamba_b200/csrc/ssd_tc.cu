@@ -302,7 +302,8 @@ template <typename T>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
                            const __grid_constant__ CUtensorMap tm_Hs, const float *dtb, const float *dAb, const float *initial,
-                           float *final_states, int nchunks, int nheads, int heads_per_group, int *status)
+                           float *final_states, float *range_decay, int store_entering, int nchunks, int nheads,
+                           int heads_per_group, int *status)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = align1024(smem_raw);
@@ -388,7 +389,7 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
         };
         float nxt[5];
         scalars(0, nxt);
-        float dec_prev = 0.f;
+        float dec_prev = 0.f, dA_total = 0.f;
         bool ok = true;
         auto fold = [&](int c, float dec) {      // H <- dec H + S_c once the MMAs of chunk c have completed
             ok = __all_sync(0xffffffffu, ok && mbar_wait(&acc_full[c & 1], (c >> 1) & 1, status, kStStreamAcc));   // tcgen05.ld is warp-collective
@@ -434,11 +435,12 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
             }
             if (c > 0) fold(c - 1, dec_prev);
             dec_prev = __expf(cur[4]);
-            // the state entering chunk c leaves as a 16-bit [n][p] tile
-            if (tid == 0) tma_store_wait_read();             // the previous store has finished reading the tile
+            dA_total += cur[4];
+            // the state entering chunk c leaves as a 16-bit [n][p] tile (not when only the range summary is wanted)
+            if (tid == 0 && store_entering) tma_store_wait_read();   // the previous store has finished reading the tile
             ok = stream_barrier_and(ok);                     // from here on every element-wise warp agrees on ok
             if (!ok) break;
-            {
+            if (store_entering) {
                 const uint32_t row = smem_u32(tile) + n * 128;
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
@@ -449,12 +451,12 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
                     o.w = Pack2<T>::pack(H[8 * q + 6], H[8 * q + 7]);
                     sts128(row + ((((p0 >> 3) + q) ^ (n & 7)) << 4), o);
                 }
-            }
-            fence_proxy_async();
-            asm volatile("bar.sync 1, 512;" ::: "memory");
-            if (tid == 0 && ok) {
-                tma_store_3d(&tm_Hs, tile, 0, 0, (int)((((int64_t)b * nchunks + c) * nheads) + h));
-                tma_store_commit();
+                fence_proxy_async();
+                asm volatile("bar.sync 1, 512;" ::: "memory");
+                if (tid == 0) {
+                    tma_store_3d(&tm_Hs, tile, 0, 0, (int)((((int64_t)b * nchunks + c) * nheads) + h));
+                    tma_store_commit();
+                }
             }
         }
         if (ok) fold(nchunks - 1, dec_prev);
@@ -463,7 +465,10 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 #pragma unroll
             for (int j = 0; j < 16; ++j) F[(p0 + j) * kN + n] = H[j];
         }
-        if (tid == 0) tma_store_wait_read();
+        if (tid == 0) {
+            tma_store_wait_read();
+            if (ok && range_decay) range_decay[bh] = __expf(dA_total);
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -846,7 +851,9 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         if (!encode_16bit(&tHs, fmt, prev16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for states failed");
         cudaFuncSetAttribute(ssd_tc_state_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmem);
         ssd_tc_state_stream_kernel<T><<<dim3(a.nheads, a.batch), kStreamThreads, kStreamSmem, stream>>>(
-            tx, tB, tHs, dtb, dAb, a.initial_states, a.final_states, nc, a.nheads, a.nheads / a.ngroups, status);
+            tx, tB, tHs, dtb, dAb, (a.phases & MB200_SSD_PHASE_OUTPUT) ? a.initial_states : nullptr, a.final_states,
+            (a.phases & MB200_SSD_PHASE_LOCAL) ? a.range_decay : nullptr, (a.phases & MB200_SSD_PHASE_OUTPUT) ? 1 : 0, nc, a.nheads,
+            a.nheads / a.ngroups, status);
         MB200_CHECK_LAUNCH("ssd state stream (tensor core)");
         return MB200_OK;
     }
@@ -918,11 +925,10 @@ int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool stat
     return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 1, states_np, stream) : run_tc<__half>(a, lay, 1, states_np, stream);
 }
 
-// One (batch, head) per CTA: worth it once those fill at least half of the SMs; the whole operator in one call,
-// no range summary asked for.
+// One (batch, head) per CTA: worth it once those fill at least half of the SMs.
 bool ssd_tc_stream_eligible(const mb200_ssd_args &a)
 {
-    return a.phases == MB200_SSD_PHASE_ALL && !a.range_decay && (int64_t)a.batch * a.nheads >= MB200_SSD_STREAM_MIN_UNITS;
+    return (int64_t)a.batch * a.nheads >= MB200_SSD_STREAM_MIN_UNITS;
 }
 
 int ssd_tc_state_stream(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
