@@ -139,7 +139,7 @@ class Workload:
             self.dtype = "bf16"
             self.step_inputs = ("x", "dt", "B", "C")
             self.alg_bytes = 2 * Lr * H * P * 2 + Lr * H * 2 + 2 * Lr * G * N * 2 + H * P * N * 4 + 3 * H * 4
-            self.launches_per_step = 4 if world == 1 else 6
+            self.launches_per_step = 4 if world == 1 else 5
             self.world = world
         elif name == "c4":
             host = make_c4(batch or 256)
@@ -177,7 +177,8 @@ class Workload:
                                                     dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True)[0]
             from mamba_b200.seqpar import mamba_chunk_scan_sequence_parallel
             return mamba_chunk_scan_sequence_parallel(d["x"], d["dt"], self.d["A"], d["B"], d["C"], 256, D=self.d["D"],
-                                                      dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True)[0]
+                                                      dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True,
+                                                      handoff=os.environ.get("MB200_BENCH_HANDOFF") or None)[0]
         if self.name == "c2":
             return mb.mamba_chunk_scan_combined(d["x"], d["dt"], self.d["A"], d["B"], d["C"], 256, D=self.d["D"], z=d["z"],
                                                 dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True)[0]

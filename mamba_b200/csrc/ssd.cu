@@ -387,8 +387,8 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: status reset: %s", cudaGetErrorString(e));
     }
     // Chunk states + inter-chunk recurrence in one streaming launch.  In a sequence split the LOCAL phase runs it
-    // from a zero state for the range summary only, and the OUTPUT phase runs it again from the incoming state
-    // (cheaper than keeping the fp32 chunk states in memory: they are 4x the size of x).
+    // from a zero state (entering states of the range as if nothing came in, range summary), and the OUTPUT phase
+    // adds the incoming state's share to those entering states: H_c += prefix_decay_c * S_in.
     const bool fused_states = tc && ssd_tc_stream_eligible(a);
     // The LOCAL phase of this problem took the streaming launch (it does not see out / z): then the scratch holds
     // no chunk states, and an OUTPUT phase that cannot stream has to form them itself.
@@ -444,10 +444,10 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
             }
         }
         if (fused_states) {
-            // the entering states and the final state come from the state-stream kernel: it ran in the LOCAL half of
-            // this call, or runs now from the incoming state
+            // the entering states and the final state come from the state-stream kernel; in the OUTPUT half of a
+            // sequence split the incoming state is added to what the LOCAL half left
             if (!(a.phases & MB200_SSD_PHASE_LOCAL))
-                if (int rc = ssd_tc_state_stream(a, lay, stream)) return rc;
+                if (int rc = ssd_tc_apply_incoming(a, lay, stream)) return rc;
         } else if (PN % 4 == 0) {
             ssd_state_passing_kernel<4><<<dim3((unsigned)((PN / 4 + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
         } else {

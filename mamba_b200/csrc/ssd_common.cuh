@@ -14,10 +14,13 @@ namespace mb200 {
 //                                              general kernels, 16-bit in the same region for the tensor-core ones
 //   prev16  (batch, nchunks, nheads, P, N)     16-bit copy of the state entering each chunk (tensor-core path);
 //                                              (.., N, P) when the fused state-stream kernel wrote it
+//   aux     sequence-split hand-over of the fused state-stream path, written by the LOCAL phase for the OUTPUT
+//           phase: prefix decay (batch, nheads, nchunks), the range's end state from a zero incoming state
+//           (batch, nheads, P, N) and the range decay (batch, nheads), all fp32
 //   status  one int32 in the last 256 bytes    0 after a clean run; a kernel that gave up a bounded wait
 //                                              leaves its code here (the output is then invalid)
 struct SsdScratch {
-    size_t off_dt, off_dA, off_states, off_cb, off_prev16, off_status, total;
+    size_t off_dt, off_dA, off_states, off_cb, off_prev16, off_aux, off_aux_state, off_aux_decay, off_status, total;
     int nchunks;
 };
 
@@ -33,7 +36,10 @@ inline SsdScratch ssd_scratch_layout(const mb200_ssd_args &a)
     s.off_states = align256(s.off_dA + per);
     s.off_cb = align256(s.off_states + (size_t)a.batch * s.nchunks * a.nheads * a.headdim * a.dstate * sizeof(float));
     s.off_prev16 = align256(s.off_cb + (size_t)a.batch * s.nchunks * a.ngroups * a.chunk_size * a.chunk_size * sizeof(float));
-    s.off_status = align256(s.off_prev16 + (size_t)a.batch * s.nchunks * a.nheads * a.headdim * a.dstate * 2);
+    s.off_aux = align256(s.off_prev16 + (size_t)a.batch * s.nchunks * a.nheads * a.headdim * a.dstate * 2);
+    s.off_aux_state = align256(s.off_aux + (size_t)a.batch * a.nheads * s.nchunks * sizeof(float));
+    s.off_aux_decay = align256(s.off_aux_state + (size_t)a.batch * a.nheads * a.headdim * a.dstate * sizeof(float));
+    s.off_status = align256(s.off_aux_decay + (size_t)a.batch * a.nheads * sizeof(float));
     s.total = s.off_status + 256;
     return s;
 }
@@ -46,5 +52,8 @@ int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool stat
 // states in [n][p] order, which ssd_tc_cb_and_scan is told through states_np.
 bool ssd_tc_stream_eligible(const mb200_ssd_args &a);
 int ssd_tc_state_stream(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
+// OUTPUT phase of a sequence split on that path: adds the incoming state's share to the entering states the LOCAL
+// phase left (H_c += prefix_decay_c * S_in) and forms the range's end state.
+int ssd_tc_apply_incoming(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
 
 }  // namespace mb200

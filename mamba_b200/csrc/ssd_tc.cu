@@ -302,8 +302,8 @@ template <typename T>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
                            const __grid_constant__ CUtensorMap tm_Hs, const float *dtb, const float *dAb, const float *initial,
-                           float *final_states, float *range_decay, int store_entering, int nchunks, int nheads,
-                           int heads_per_group, int *status)
+                           float *final_states, float *range_decay, float *prefix_decay, float *state_copy, float *decay_copy,
+                           int store_entering, int nchunks, int nheads, int heads_per_group, int *status)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = align1024(smem_raw);
@@ -435,6 +435,7 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
             }
             if (c > 0) fold(c - 1, dec_prev);
             dec_prev = __expf(cur[4]);
+            if (tid == 0 && prefix_decay) prefix_decay[bh * nchunks + c] = __expf(dA_total);   // decay from the range start to chunk c
             dA_total += cur[4];
             // the state entering chunk c leaves as a 16-bit [n][p] tile (not when only the range summary is wanted)
             if (tid == 0 && store_entering) tma_store_wait_read();   // the previous store has finished reading the tile
@@ -465,9 +466,15 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 #pragma unroll
             for (int j = 0; j < 16; ++j) F[(p0 + j) * kN + n] = H[j];
         }
+        if (ok && state_copy) {
+            float *F = state_copy + bh * (kP * kN);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) F[(p0 + j) * kN + n] = H[j];
+        }
         if (tid == 0) {
             tma_store_wait_read();
             if (ok && range_decay) range_decay[bh] = __expf(dA_total);
+            if (ok && decay_copy) decay_copy[bh] = __expf(dA_total);
         }
     }
     tc_fence_before_sync();
@@ -802,6 +809,44 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     if (warp == 8) tmem_dealloc(tmem, 128);
 }
 
+// ====================================================================================== incoming state
+// Sequence split, OUTPUT half: the LOCAL half stored the entering states of the range as if nothing came in.
+// Adds prefix_decay[c] * S_in to each of them (16-bit [n][p] tiles) and forms the range's end state
+// range_decay * S_in + S_local.  grid (ceil(nchunks / kFixChunks), nheads, batch), 256 threads; the incoming
+// state of the (batch, head) is transposed once into shared memory.
+constexpr int kFixChunks = 8;
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_incoming_state_kernel(T *prev16, const float *s_in, const float *prefix_decay, const float *s_local,
+                                                                  const float *range_decay, float *final_states, int nchunks, int nheads)
+{
+    __shared__ float sin_np[kN * (kP + 1)];      // [n][p], padded
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int64_t bh = (int64_t)b * nheads + h;
+    const float *src = s_in + bh * (kP * kN);
+    for (int e = threadIdx.x; e < kP * kN; e += 256) sin_np[(e % kN) * (kP + 1) + e / kN] = src[e];    // src is [p][n]
+    if (blockIdx.x == 0 && final_states) {
+        const float d = range_decay[bh];
+        for (int e = threadIdx.x; e < kP * kN; e += 256) final_states[bh * (kP * kN) + e] = fmaf(d, src[e], s_local[bh * (kP * kN) + e]);
+    }
+    __syncthreads();
+    const int c0 = blockIdx.x * kFixChunks;
+    for (int c = c0; c < min(c0 + kFixChunks, nchunks); ++c) {
+        const float pd = prefix_decay[bh * nchunks + c];
+        T *tile = prev16 + (((int64_t)b * nchunks + c) * nheads + h) * (kP * kN);
+        for (int v = threadIdx.x; v < kP * kN / 8; v += 256) {      // 8 consecutive p of one n per step
+            const int n = v / (kP / 8), p = (v % (kP / 8)) * 8;
+            uint4 raw = *reinterpret_cast<const uint4 *>(tile + n * kP + p);
+            uint32_t *w = reinterpret_cast<uint32_t *>(&raw);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = Pack2<T>::unpack(w[q]);
+                w[q] = Pack2<T>::pack(fmaf(pd, sin_np[n * (kP + 1) + p + 2 * q], f.x), fmaf(pd, sin_np[n * (kP + 1) + p + 2 * q + 1], f.y));
+            }
+            *reinterpret_cast<uint4 *>(tile + n * kP + p) = raw;
+        }
+    }
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 bool mult8(const int64_t *s, int n)
 {
@@ -850,10 +895,16 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         const uint32_t bx[3] = {64, 128, 1};
         if (!encode_16bit(&tHs, fmt, prev16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for states failed");
         cudaFuncSetAttribute(ssd_tc_state_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmem);
+        // whole operator: from initial_states, entering states stored.  LOCAL half of a sequence split: from a zero
+        // state, entering states stored as they are without the incoming state, plus what the OUTPUT half needs to
+        // add that state's share later.
+        const bool whole = (a.phases & MB200_SSD_PHASE_OUTPUT) != 0;
+        float *aux_prefix = whole ? nullptr : reinterpret_cast<float *>(base + lay.off_aux);
+        float *aux_state = whole ? nullptr : reinterpret_cast<float *>(base + lay.off_aux_state);
+        float *aux_decay = whole ? nullptr : reinterpret_cast<float *>(base + lay.off_aux_decay);
         ssd_tc_state_stream_kernel<T><<<dim3(a.nheads, a.batch), kStreamThreads, kStreamSmem, stream>>>(
-            tx, tB, tHs, dtb, dAb, (a.phases & MB200_SSD_PHASE_OUTPUT) ? a.initial_states : nullptr, a.final_states,
-            (a.phases & MB200_SSD_PHASE_LOCAL) ? a.range_decay : nullptr, (a.phases & MB200_SSD_PHASE_OUTPUT) ? 1 : 0, nc, a.nheads,
-            a.nheads / a.ngroups, status);
+            tx, tB, tHs, dtb, dAb, whole ? a.initial_states : nullptr, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1,
+            nc, a.nheads, a.nheads / a.ngroups, status);
         MB200_CHECK_LAUNCH("ssd state stream (tensor core)");
         return MB200_OK;
     }
@@ -929,6 +980,33 @@ int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool stat
 bool ssd_tc_stream_eligible(const mb200_ssd_args &a)
 {
     return (int64_t)a.batch * a.nheads >= MB200_SSD_STREAM_MIN_UNITS;
+}
+
+template <typename T>
+int run_incoming(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
+{
+    char *base = static_cast<char *>(a.scratch);
+    const float *aux_state = reinterpret_cast<const float *>(base + lay.off_aux_state);
+    const float *aux_decay = reinterpret_cast<const float *>(base + lay.off_aux_decay);
+    const int64_t PN = (int64_t)kP * kN;
+    if (!a.initial_states) {       // nothing came in: the entering states stand, the end state is the local one
+        if (a.final_states) {
+            const cudaError_t e = cudaMemcpyAsync(a.final_states, aux_state, sizeof(float) * (size_t)a.batch * a.nheads * PN,
+                                                  cudaMemcpyDeviceToDevice, stream);
+            if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: copying the range state: %s", cudaGetErrorString(e));
+        }
+        return MB200_OK;
+    }
+    ssd_incoming_state_kernel<T><<<dim3((lay.nchunks + kFixChunks - 1) / kFixChunks, a.nheads, a.batch), 256, 0, stream>>>(
+        reinterpret_cast<T *>(base + lay.off_prev16), a.initial_states, reinterpret_cast<const float *>(base + lay.off_aux), aux_state,
+        aux_decay, a.final_states, lay.nchunks, a.nheads);
+    MB200_CHECK_LAUNCH("ssd incoming state");
+    return MB200_OK;
+}
+
+int ssd_tc_apply_incoming(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
+{
+    return a.io_dtype == MB200_BF16 ? run_incoming<__nv_bfloat16>(a, lay, stream) : run_incoming<__half>(a, lay, stream);
 }
 
 int ssd_tc_state_stream(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)

@@ -9,11 +9,17 @@ contiguous range of chunks can be summarised by ``(range_state, range_decay)`` a
              2. hand-off        recv S_in from r-1;  send  range_decay_r * S_in + range_state_r  to r+1
              3. output pass     inter-chunk recurrence from S_in, chunk outputs
 
-Step 2 is the only communication: one (batch, nheads, headdim, dstate) fp32 tensor per hop, point to
-point over the process group's backend (NCCL over NVLink between GPUs).  The received state lands in
-this rank's own memory before any kernel reads it.  Every wait in the hand-off is bounded by the
-process group's timeout; a missing predecessor surfaces as ``SequenceHandoffError`` on the waiting
-rank instead of a hang.
+Step 2 is the only communication.  Two forms, same result bit for bit:
+
+    "chain"   one (batch, nheads, headdim, dstate) fp32 tensor per hop, point to point (NCCL P2P over
+              NVLink between GPUs): world-1 hops one after the other;
+    "gather"  one all-gather of every rank's (range_state, range_decay) -- rank 0 contributes its
+              OUTGOING state, so initial_states never has to travel -- and each rank folds the
+              summaries of its predecessors itself, in rank order: one collective instead of a
+              serial chain (the default above two ranks).
+
+Received data lands in this rank's own memory before any kernel reads it.  Every wait is bounded by
+the process group's timeout; a missing peer surfaces as ``SequenceHandoffError`` instead of a hang.
 
 The compute steps are injectable so that the hand-off logic can be exercised by CPU ranks (gloo) in
 tests; the defaults are this package's CUDA operators.
@@ -64,15 +70,33 @@ def _send_state(t: torch.Tensor, dst: int, group) -> None:
         raise SequenceHandoffError(f"rank {dist.get_rank(group)}: could not hand the state to rank {dst}: {e}") from e
 
 
+def _gather_summaries(state: torch.Tensor, decay: torch.Tensor, group):
+    """Every rank's (state, decay), stacked along a new leading dimension."""
+    world = dist.get_world_size(group)
+    states = torch.empty((world,) + tuple(state.shape), dtype=state.dtype, device=state.device)
+    decays = torch.empty((world,) + tuple(decay.shape), dtype=decay.dtype, device=decay.device)
+    try:
+        if dist.get_backend(group) == "nccl":
+            dist.all_gather_into_tensor(states, state.contiguous(), group=group)
+            dist.all_gather_into_tensor(decays, decay.contiguous(), group=group)
+        else:
+            dist.all_gather(list(states.unbind(0)), state.contiguous(), group=group)
+            dist.all_gather(list(decays.unbind(0)), decay.contiguous(), group=group)
+    except Exception as e:  # timeout, peer gone, transport error
+        raise SequenceHandoffError(f"rank {dist.get_rank(group)}: gathering the range summaries failed: {e}") from e
+    return states, decays
+
+
 def mamba_chunk_scan_sequence_parallel(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
                                        dt_softplus=False, dt_limit=(0.0, float("inf")), return_final_states=False,
-                                       group=None, steps: Optional[SsdSteps] = None):
+                                       group=None, steps: Optional[SsdSteps] = None, handoff: Optional[str] = None):
     """Run this rank's slice of a sequence that is split over the ranks of `group`.
 
     x, dt, B, C, z hold THIS rank's contiguous tokens (a whole number of chunks on every rank but the
     last); A, D, dt_bias are replicated; ``initial_states`` (state before the first token of the whole
-    sequence) is only read on rank 0.  Returns this rank's ``out`` and, if asked, the state after this
-    rank's last token -- on the last rank that is the final state of the whole sequence.
+    sequence) is only read on rank 0.  ``handoff`` is "chain", "gather" or None (gather above two ranks).
+    Returns this rank's ``out`` and, if asked, the state after this rank's last token -- on the last
+    rank that is the final state of the whole sequence.
     """
     steps = steps or SsdSteps()
     rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -80,11 +104,23 @@ def mamba_chunk_scan_sequence_parallel(x, dt, A, B, C, chunk_size, D=None, z=Non
         assert x.shape[1] % chunk_size == 0, "every rank but the last must hold whole chunks"
     range_state, range_decay, scratch = steps.local(x, dt, A, B, chunk_size, dt_bias=dt_bias, dt_softplus=dt_softplus,
                                                     dt_limit=dt_limit)
-    if rank == 0:
-        incoming = None if initial_states is None else initial_states.to(range_state.dtype)
+    if handoff is None:
+        handoff = "gather" if world > 2 else "chain"
+    assert handoff in ("chain", "gather"), "handoff must be 'chain' or 'gather'"
+    first = None if (rank != 0 or initial_states is None) else initial_states.to(range_state.dtype)
+    if world == 1:
+        incoming = first
+    elif handoff == "chain":
+        incoming = first if rank == 0 else _recv_state(range_state, rank - 1, group)
+        if rank < world - 1:
+            _send_state(steps.fold(incoming, range_decay, range_state), rank + 1, group)
     else:
-        incoming = _recv_state(range_state, rank - 1, group)
-    if rank < world - 1:
-        _send_state(steps.fold(incoming, range_decay, range_state), rank + 1, group)
+        mine = steps.fold(first, range_decay, range_state) if rank == 0 else range_state
+        states, decays = _gather_summaries(mine, range_decay, group)
+        incoming = first
+        if rank > 0:
+            incoming = states[0]                       # the state rank 0 hands on
+            for r in range(1, rank):
+                incoming = steps.fold(incoming, decays[r], states[r])
     return steps.finish(x, dt, A, B, C, chunk_size, scratch, D=D, z=z, dt_bias=dt_bias, incoming_state=incoming,
                         dt_softplus=dt_softplus, dt_limit=dt_limit, return_final_states=return_final_states)

@@ -166,16 +166,22 @@ def test_prefill_state_continues_in_decode():
     assert_close(fin, fin_full, TOL_FP32, "decode state")
 
 
-def test_sequence_split_in_two_ranges():
+@pytest.mark.parametrize("shape,dtype,tol", [((1, 512, 4, 32, 2, 64, 64), torch.float32, TOL_FP32),
+                                             ((2, 1024, 40, 64, 2, 128, 256), torch.bfloat16, TOL_BF16),
+                                             ((1, 1300, 80, 64, 8, 128, 256), torch.float16, TOL_BF16)])
+def test_sequence_split_in_two_ranges(shape, dtype, tol):
     """The two-phase entry used when a sequence is split across devices: both ranges run LOCAL, the
-    first range's summary is folded and handed to the second, then both run OUTPUT.  Equal to one call."""
+    first range's summary is folded and handed to the second, then both run OUTPUT.  Equal to one call.
+    The 16-bit shapes have enough (batch, head) pairs for the fused state-stream path, where the OUTPUT half
+    adds the incoming state's share to the entering states the LOCAL half stored."""
     from mamba_b200 import ssd_finish, ssd_fold_state, ssd_local_states
-    b, L, H, P, G, N, Q = 1, 512, 4, 32, 2, 64, 64
-    inp = make(14, b, L, H, P, G, N, torch.float32, has_z=False)
+    b, L, H, P, G, N, Q = shape
+    inp = make(14, b, L, H, P, G, N, dtype, has_z=False)
     c = {k: _c(v) for k, v in inp.items()}
+    TOL_FP32_ = tol
     whole, wfin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], dt_bias=c["dt_bias"], dt_softplus=True,
                         return_final_states=True)
-    half = L // 2
+    half = (L // 2) // Q * Q
     sl = [slice(0, half), slice(half, L)]
     loc = [ssd_local_states(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], Q, dt_bias=c["dt_bias"], dt_softplus=True)
            for s in sl]
@@ -185,9 +191,9 @@ def test_sequence_split_in_two_ranges():
         o, fin = ssd_finish(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], c["C"][:, s], Q, loc[r][2], D=c["D"],
                             dt_bias=c["dt_bias"], incoming_state=incoming[r], dt_softplus=True, return_final_states=True)
         outs.append(o)
-    assert_close(torch.cat(outs, dim=1), whole, TOL_FP32, "split out")
-    assert_close(fin, wfin, TOL_FP32, "split final")
-    assert_close(ssd_fold_state(incoming[1], loc[1][1], loc[1][0]), wfin, TOL_FP32, "folded summary")
+    assert_close(torch.cat(outs, dim=1), whole, TOL_FP32_, "split out")
+    assert_close(fin, wfin, TOL_FP32_, "split final")
+    assert_close(ssd_fold_state(incoming[1], loc[1][1], loc[1][0]), wfin, TOL_FP32_, "folded summary")
 
 
 def _packed(seed, lens, H, P, G, N, dtype):

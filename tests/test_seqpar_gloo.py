@@ -60,13 +60,14 @@ def _worker(rank, world, store, mode, result_dir):
         inp = _inputs(5, b, L, H, P, G, N)
         lo, hi = split_sequence(L, Q, world, rank)
         sl = slice(lo, hi)
+        mode, _, handoff = mode.partition(":")
         if mode == "dead_predecessor" and rank == 0:
             return                                                  # leaves without handing its state on
         try:
             out, fin = mamba_chunk_scan_sequence_parallel(
                 inp["x"][:, sl], inp["dt"][:, sl], inp["A"], inp["B"][:, sl], inp["C"][:, sl], Q, D=inp["D"], z=inp["z"][:, sl],
                 dt_bias=inp["dt_bias"], initial_states=inp["init"], dt_softplus=True, return_final_states=True,
-                steps=_oracle_steps())
+                steps=_oracle_steps(), handoff=handoff or None)
             torch.save({"out": out, "fin": fin, "range": (lo, hi)}, os.path.join(result_dir, f"rank{rank}.pt"))
         except SequenceHandoffError as e:
             torch.save({"error": str(e)}, os.path.join(result_dir, f"rank{rank}.pt"))
@@ -81,10 +82,11 @@ def _run(world, mode):
         return {r: torch.load(os.path.join(tmp, f"rank{r}.pt")) for r in range(world) if os.path.exists(os.path.join(tmp, f"rank{r}.pt"))}
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_sequence_split_equals_single_rank(world):
+@pytest.mark.parametrize("world,handoff", [(2, "chain"), (3, "chain"), (2, "gather"), (3, "gather"), (3, "")])
+def test_sequence_split_equals_single_rank(world, handoff):
+    """Point-to-point chain, all-gather of the range summaries, and the default choice give the single-rank result."""
     import oracle
-    res = _run(world, "ok")
+    res = _run(world, "ok:" + handoff)
     inp = _inputs(5, 1, 448, 3, 8, 1, 16)
     want, wfin = oracle.ssd_chunk_scan(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], 64, inp["D"], inp["z"], inp["dt_bias"],
                                        inp["init"], dt_softplus=True)
@@ -96,9 +98,16 @@ def test_sequence_split_equals_single_rank(world):
 
 
 def test_missing_predecessor_is_reported_not_hung():
-    res = _run(2, "dead_predecessor")
+    res = _run(2, "dead_predecessor:chain")
     assert 0 not in res
     assert "error" in res[1] and "no state from rank 0" in res[1]["error"]
+
+
+def test_missing_rank_is_reported_by_the_gather_too():
+    res = _run(3, "dead_predecessor:gather")
+    assert 0 not in res
+    for r in (1, 2):
+        assert "error" in res[r] and "gathering the range summaries failed" in res[r]["error"]
 
 
 def test_split_sequence_covers_every_chunk_once():
