@@ -813,25 +813,42 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 // Sequence split, OUTPUT half: the LOCAL half stored the entering states of the range as if nothing came in.
 // Adds prefix_decay[c] * S_in to each of them (16-bit [n][p] tiles) and forms the range's end state
 // range_decay * S_in + S_local.  grid (ceil(nchunks / kFixChunks), nheads, batch), 256 threads; the incoming
-// state of the (batch, head) is transposed once into shared memory.
+// state of the (batch, head) is transposed once into shared memory.  Chunks whose share has decayed to nothing
+// are left alone, which for fast-decaying heads is all but the first few.
 constexpr int kFixChunks = 8;
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_incoming_state_kernel(T *prev16, const float *s_in, const float *prefix_decay, const float *s_local,
                                                                   const float *range_decay, float *final_states, int nchunks, int nheads)
 {
     __shared__ float sin_np[kN * (kP + 1)];      // [n][p], padded
+    __shared__ float wmax[8];
     const int h = blockIdx.y, b = blockIdx.z;
     const int64_t bh = (int64_t)b * nheads + h;
     const float *src = s_in + bh * (kP * kN);
-    for (int e = threadIdx.x; e < kP * kN; e += 256) sin_np[(e % kN) * (kP + 1) + e / kN] = src[e];    // src is [p][n]
+    if (blockIdx.x > 0 && prefix_decay[bh * nchunks + blockIdx.x * kFixChunks] == 0.f) return;   // decayed to zero before this CTA's chunks
+    float amax = 0.f;
+    for (int e = threadIdx.x; e < kP * kN; e += 256) {
+        const float v = src[e];
+        sin_np[(e % kN) * (kP + 1) + e / kN] = v;    // src is [p][n]
+        amax = fmaxf(amax, fabsf(v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;
     if (blockIdx.x == 0 && final_states) {
         const float d = range_decay[bh];
         for (int e = threadIdx.x; e < kP * kN; e += 256) final_states[bh * (kP * kN) + e] = fmaf(d, src[e], s_local[bh * (kP * kN) + e]);
     }
     __syncthreads();
+    float smax = wmax[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) smax = fmaxf(smax, wmax[i]);
     const int c0 = blockIdx.x * kFixChunks;
     for (int c = c0; c < min(c0 + kFixChunks, nchunks); ++c) {
         const float pd = prefix_decay[bh * nchunks + c];
+        // the prefix decay only shrinks along the range: once the whole share is below the smallest normal number
+        // nothing is left to add (infinities and NaNs in S_in still go through)
+        if (pd * smax < 1.1754944e-38f) break;
         T *tile = prev16 + (((int64_t)b * nchunks + c) * nheads + h) * (kP * kN);
         for (int v = threadIdx.x; v < kP * kN / 8; v += 256) {      // 8 consecutive p of one n per step
             const int n = v / (kP / 8), p = (v % (kP / 8)) * 8;
