@@ -484,16 +484,16 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 
 // ====================================================================================== chunk scan
 // grid (nheads, nchunks * 2, batch), 288 threads: warps 0-7 element-wise + epilogue (thread = one row and one
-// 32-column half), warp 8 TMA + MMA.  A "block" is a 64-wide slice of the mask product: the CB tile [128 x 64]
-// (16 KB) followed by the 64 rows of x it multiplies (8 KB).  Shared memory (74.7 KB, three CTAs per SM):
-//   area A (48 KB)  first C (2 x 16 KB) and H (2 x 8 KB); once Y1 = C.H^T has completed it is two block slots
-//   slot S (24 KB)  block 0, later block 3
-//   scalars         dA*log2e and the column factors (fp32), dt (bf16), barriers
-// Block placement: 0 -> S, 1 -> A.0, 2 -> A.1, 3 -> S (after block 0 has been multiplied).  The gate tile z
-// lands in the CB part of a slot whose block has been multiplied (S for the first row block, A.0 for the
-// second); the output tile is assembled in the CB part of the last-but-one block's slot and leaves through
-// one TMA store.  The row block's own x rows (for D x) are the x parts of its last two blocks, which nothing
-// overwrites.  TMEM: 128 columns (Y1, Y2).
+// 32-column half), warp 8 TMA + MMA.  Shared memory (74.7 KB, three CTAs per SM) is a ring of three 24 KB slots,
+// each a 16 KB tile followed by 8 KB: a K half of C [128 x 64] with the matching half of the entering state H, or
+// a "block" = 64-wide slice of the mask product (CB tile [128 x 64] with the 64 rows of x it multiplies).
+//   C/H half 0 -> slot 0, C/H half 1 -> slot 1, block j -> slot (2 + j) % 3
+// Both C/H halves and block 0 are requested at once; a slot is re-used as soon as the MMAs that read it have
+// completed (block 1 after Y1's first half, block 2 after its second, block 3 after block 0).  The gate tile z
+// lands in the tile part of a slot that is done with (slot 1 for the first row block, slot 0 for the second);
+// the output tile is assembled in the tile part of block 0's / block 2's slot and leaves through one TMA store.
+// The row block's own x rows (for D x) are the x parts of its last two blocks, which nothing overwrites.
+// Then scalars (dA*log2e and the column factors in fp32, dt in bf16) and barriers.  TMEM: 128 columns (Y1, Y2).
 //
 // Decay mask.  A thread owns 32 consecutive columns k of one row m per block.  Three cases:
 //   all k > m           zeros
@@ -528,26 +528,25 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                          const float *dtb, const float *dAb, int nchunks, int h_np, int *status)
 {
     extern __shared__ __align__(1024) uint8_t sm[];
-    constexpr uint32_t kSlot = 24576, kSlotX = 16384;   // a slot: CB tile, then 64 rows of x
-    uint8_t *areaA = sm;                       // C | H, then slots A.0, A.1
-    uint8_t *slotS = sm + 49152;
-    uint8_t *Cs = areaA, *Hs = areaA + 32768;
+    constexpr uint32_t kSlot = 24576, kSlotX = 16384;   // a slot: 16 KB tile (C half or CB block), then 8 KB (H half or 64 rows of x)
     float *dA2 = reinterpret_cast<float *>(sm + 73728);             // 256: dA_cumsum * log2(e)
     float *cks = dA2 + 256;                                         // 256: exp(dA_ref(k) - dA_k) dt_k, ref(k) = k | 31
     __nv_bfloat16 *dts = reinterpret_cast<__nv_bfloat16 *>(cks + 256);   // 256: dt (only the exact path reads it)
     int *mono = reinterpret_cast<int *>(sm + 73728 + 2560);         // 1 while dA_cumsum is non-increasing over the chunk
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 73728 + 2560 + 64);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
-    uint64_t *bar_c = &bars[0], *bar_g1 = &bars[1], *bar_z = &bars[2], *bar_g2 = &bars[3];
+    uint64_t *bar_chfull = &bars[0], *bar_z = &bars[2], *bar_g2 = &bars[3];     // bar_chfull[kb]: C / H half kb has landed
     uint64_t *bar_full = &bars[4], *bar_scaled = &bars[8], *bar_e = &bars[12];   // bar_e[j]: block j has been multiplied
+    uint64_t *bar_chdone = &bars[14];                                            // bar_chdone[kb]: C.H^T part kb has been multiplied
 
     const int h = blockIdx.x, c = blockIdx.y >> 1, mb = blockIdx.y & 1, b = blockIdx.z;
     const int g = h / (a.nheads / a.ngroups);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nk = (mb + 1) * 2;   // 64-wide blocks this row block needs
-    auto slot_ptr = [&](int j) -> uint8_t * { return (j == 0 || j == 3) ? slotS : areaA + (j - 1) * kSlot; };
-    uint8_t *ztile = mb ? areaA : slotS;                  // CB part of block 1's / block 0's slot
-    uint8_t *otile = mb ? areaA + kSlot : areaA;          // CB part of block 2's / block 1's slot
+    // ring of three slots: C/H half 0 -> 0, C/H half 1 -> 1, mask block j -> (2 + j) % 3
+    auto slot_ptr = [&](int j) -> uint8_t * { return sm + ((2 + j) % 3) * kSlot; };
+    uint8_t *ztile = mb ? sm : sm + kSlot;                // slot 0 after block 1 (second row block), slot 1 after C/H half 1 (first)
+    uint8_t *otile = mb ? sm + kSlot : sm + 2 * kSlot;    // tile part of block 2's / block 0's slot, multiplied long before
     // chunk scalars are requested before the set-up barrier so their latency hides behind it
     const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
     const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
@@ -560,8 +559,10 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         pre_prev = k > 0 ? dAc[k - 1] : pre_dk;
     }
     if (threadIdx.x == 256) {
-        mbar_init(bar_c, 1);
-        mbar_init(bar_g1, 1);
+        mbar_init(&bar_chfull[0], 1);
+        mbar_init(&bar_chfull[1], 1);
+        mbar_init(&bar_chdone[0], 1);
+        mbar_init(&bar_chdone[1], 1);
         mbar_init(bar_z, 1);
         mbar_init(bar_g2, 1);
         for (int i = 0; i < 4; ++i) {
@@ -606,58 +607,61 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 mbar_expect_tx(bar_z, 16384);
                 tma_load_4d(ztile, &tm_z, bar_z, 0, h, c * kQ + mb * 128, b);
             };
-            // the first mask block is what the element-wise warps wait for: request it first, then C and H
+            // Everything the three slots can hold is requested at once: both C/H halves and the first mask block.
+            // A slot is re-used as soon as the MMAs that read it have completed, so a row block needs two round
+            // trips to memory back to back instead of three.
+            auto load_ch = [&](int kb) {
+                uint8_t *dst = sm + kb * kSlot;
+                mbar_expect_tx(&bar_chfull[kb], 16384 + 8192);
+                tma_load_4d(dst, &tm_C, &bar_chfull[kb], kb * 64, g, c * kQ + mb * 128, b);
+                if (h_np) tma_load_3d(dst + kSlotX, &tm_H, &bar_chfull[kb], 0, kb * 64, (int)unit_h);   // rows n of the [n][p] state
+                else tma_load_3d(dst + kSlotX, &tm_H, &bar_chfull[kb], kb * 64, 0, (int)unit_h);        // columns n of the [p][n] state
+            };
             if (ok) {
                 load_block(0);
+                load_ch(0);
+                load_ch(1);
 #if MB200_SCAN_L2_PREFETCH
-                // the later x rows and the gate tile cannot be requested yet (their shared memory is still in use):
-                // have them brought into L2 now, so that the later requests are L2 hits
+                // the later x rows and the gate tile cannot be requested yet: have them brought into L2 now
                 for (int j = 1; j < nk; ++j) tma_prefetch_l2_4d(&tm_x, 0, h, c * kQ + j * 64, b);
                 if (a.z) tma_prefetch_l2_4d(&tm_z, 0, h, c * kQ + mb * 128, b);
 #endif
-                mbar_expect_tx(bar_c, 32768 + 16384);
-                for (int kb = 0; kb < 2; ++kb) {
-                    tma_load_4d(Cs + kb * 16384, &tm_C, bar_c, kb * 64, g, c * kQ + mb * 128, b);
-                    if (!h_np) tma_load_3d(Hs + kb * 8192, &tm_H, bar_c, kb * 64, 0, (int)unit_h);
-                }
-                if (h_np) tma_load_3d(Hs, &tm_H, bar_c, 0, 0, (int)unit_h);     // one [128 n x 64 p] tile
             }
-            // Y1 = C . H^T, then area A is free for blocks 1 and 2
-            ok = ok && mbar_wait(bar_c, 0, status, kStBarC);
-            MB200_TRACE(1);
-            if (ok) {
-                tc_fence_after_sync();
-                // the entering state is either [p][n] (two K-major boxes) or [n][p] (one tile, N-major B operand)
-                const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 0, h_np ? 1 : 0);
-                for (int kb = 0; kb < 2; ++kb)
+            // Y1 = C . H^T in two K halves
+            const uint32_t idesc1 = instr_desc_f16(128, 64, Fmt<T>::v, 0, h_np ? 1 : 0);
+            for (int kb = 0; kb < 2; ++kb) {
+                ok = ok && mbar_wait(&bar_chfull[kb], 0, status, kStBarC);
+                if (kb == 0) MB200_TRACE(1);
+                if (ok) {
+                    tc_fence_after_sync();
+                    const uint32_t cb_ = smem_u32(sm + kb * kSlot), hb_ = cb_ + kSlotX;
                     for (int s = 0; s < 4; ++s)
-                        mma_f16_ss(tmem, smem_desc_sw128(smem_u32(Cs + kb * 16384) + s * 32, 16, 1024),
-                                   h_np ? smem_desc_sw128(smem_u32(Hs) + kb * 8192 + s * 2048, 16, 1024)
-                                        : smem_desc_sw128(smem_u32(Hs + kb * 8192) + s * 32, 16, 1024),
-                                   idesc, (kb | s) != 0);
+                        mma_f16_ss(tmem, smem_desc_sw128(cb_ + s * 32, 16, 1024),
+                                   h_np ? smem_desc_sw128(hb_ + s * 2048, 16, 1024) : smem_desc_sw128(hb_ + s * 32, 16, 1024), idesc1,
+                                   (kb | s) != 0);
+                }
+                mma_commit(&bar_chdone[kb]);
             }
-            mma_commit(bar_g1);
-            ok = ok && mbar_wait(bar_g1, 0, status, kStBarG1);
+            ok = ok && mbar_wait(&bar_chdone[0], 0, status, kStBarG1);
+            if (ok) load_block(1);                       // slot 0
+            ok = ok && mbar_wait(&bar_chdone[1], 0, status, kStBarG1);
             if (ok) {
-                load_block(1);
-                if (nk > 2) load_block(2);
+                if (nk > 2) load_block(2);               // slot 1
+                else if (a.z) load_z();
             }
             MB200_TRACE(2);
             gemm2_block(0);
             MB200_TRACE(3);
-            if (nk > 2 || a.z) {
+            if (nk > 2) {
                 mma_commit(&bar_e[0]);
-                ok = ok && mbar_wait(&bar_e[0], 0, status, kStBarEmpty);    // slot S has been read
-                if (ok) {
-                    if (nk > 2) load_block(3);
-                    else load_z();
-                }
+                ok = ok && mbar_wait(&bar_e[0], 0, status, kStBarEmpty);    // slot 2 has been read
+                if (ok) load_block(3);
             }
             gemm2_block(1);
             if (nk > 2) {
                 if (a.z) {
                     mma_commit(&bar_e[1]);
-                    ok = ok && mbar_wait(&bar_e[1], 0, status, kStBarEmpty);   // block 1's CB tile has been read
+                    ok = ok && mbar_wait(&bar_e[1], 0, status, kStBarEmpty);   // slot 0 has been read
                     if (ok) load_z();
                 }
                 gemm2_block(2);
@@ -935,7 +939,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
     if (h_np) {
         const uint64_t d[3] = {(uint64_t)kP, (uint64_t)kN, (uint64_t)a.batch * nc * a.nheads};
         const uint64_t s[2] = {(uint64_t)kP * 2, (uint64_t)kN * kP * 2};
-        const uint32_t bx[3] = {64, 128, 1};
+        const uint32_t bx[3] = {64, 64, 1};      // 64 rows n of the [n][p] state: one K half of C.H^T
         if (!encode_16bit(&tH, fmt, prev16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for states failed");
     } else {
         const uint64_t d[3] = {(uint64_t)kN, (uint64_t)kP, (uint64_t)a.batch * nc * a.nheads};
