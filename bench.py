@@ -39,6 +39,16 @@ NCU_TRAFFIC_BYTES = {
 }
 
 
+# the names the GPU arm puts in config.workload; the reference arm reports under the same ones
+WORKLOAD_DESC = {
+    "c0": "mamba1_selective_scan_fwd fp32 b2 d256 L512 N16",
+    "c1": "mamba1_selective_scan_fwd bf16 b8 d5120 L2048 N16 (2.8B layer)",
+    "c2": "mamba2_ssd_chunk_scan_fwd bf16 b8 L4096 h80 P64 g1 N128 Q256 (+z, +final_states)",
+    "c3": "mamba2_ssd_chunk_scan_fwd bf16 b1 L262144 h128 P64 g8 N128 Q256 (no z), sequence split over GPUs",
+    "c4": "mamba2_selective_state_update b256 h80 P64 N128 fp32 state, bf16 activations",
+}
+
+
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -101,8 +111,7 @@ class Workload:
             host = make_c1(batch or 8) if name == "c1" else make_c0()
             self.shape = dict(batch=host["u"].shape[0], d_inner=host["u"].shape[1], seqlen=host["u"].shape[2], d_state=16)
             self.tokens = host["u"].shape[0] * host["u"].shape[2]
-            self.desc = ("mamba1_selective_scan_fwd bf16 b8 d5120 L2048 N16 (2.8B layer)" if name == "c1"
-                         else "mamba1_selective_scan_fwd fp32 b2 d256 L512 N16")
+            self.desc = WORKLOAD_DESC[name]
             self.dtype = "bf16" if name == "c1" else "f32"
             self.step_inputs = ("u", "delta", "z", "B", "C")
             esz = host["u"].element_size()
@@ -114,7 +123,7 @@ class Workload:
             b, L, H, P = host["x"].shape
             self.shape = dict(batch=b, seqlen=L, nheads=H, headdim=P, ngroups=1, d_state=128, chunk_size=256)
             self.tokens = b * L
-            self.desc = "mamba2_ssd_chunk_scan_fwd bf16 b8 L4096 h80 P64 g1 N128 Q256 (+z, +final_states)"
+            self.desc = WORKLOAD_DESC[name]
             self.dtype = "bf16"
             self.step_inputs = ("x", "dt", "z", "B", "C")
             self.alg_bytes = 3 * b * L * H * P * 2 + b * L * H * 2 + 2 * b * L * 128 * 2 + b * H * P * 128 * 4 + 3 * H * 4
@@ -135,7 +144,7 @@ class Workload:
             self.dev_only = dict(x=r(1, Lr, H, P).to(bf), dt=r(1, Lr, H).to(bf), B=r(1, Lr, G, N).to(bf), C=r(1, Lr, G, N).to(bf))
             self.shape = dict(batch=1, seqlen_total=Ltot, seqlen_this_gpu=Lr, nheads=H, headdim=P, ngroups=G, d_state=N, chunk_size=256)
             self.tokens = Lr
-            self.desc = "mamba2_ssd_chunk_scan_fwd bf16 b1 L262144 h128 P64 g8 N128 Q256 (no z), sequence split over GPUs"
+            self.desc = WORKLOAD_DESC[name]
             self.dtype = "bf16"
             self.step_inputs = ("x", "dt", "B", "C")
             self.alg_bytes = 2 * Lr * H * P * 2 + Lr * H * 2 + 2 * Lr * G * N * 2 + H * P * N * 4 + 3 * H * 4
@@ -146,7 +155,7 @@ class Workload:
             b, H, P, N = host["state"].shape
             self.shape = dict(batch=b, nheads=H, headdim=P, ngroups=1, d_state=N, consecutive_steps=True)
             self.tokens = b
-            self.desc = "mamba2_selective_state_update b256 h80 P64 N128 fp32 state, bf16 activations"
+            self.desc = WORKLOAD_DESC[name]
             self.dtype = "f32"
             self.step_inputs = ("x", "dt", "z", "B", "C")
             self.alg_bytes = 2 * b * H * P * N * 4 + 3 * b * H * P * 2 + b * H * 2 + 2 * b * N * 2 + 3 * H * 4
@@ -457,7 +466,7 @@ def main():
             "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": steps,
             "warmup": min(warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "sample_per_step": sample},
+            "config": {"workload": WORKLOAD_DESC[args.workload], "sample_per_step": sample},
             "cpu_baseline": {"value": val, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }))
