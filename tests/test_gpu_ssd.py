@@ -289,3 +289,42 @@ def test_bench_config2_full_size_properties():
     assert_close(out3, out1.float(), TOL_BF16, "fused vs two-launch out")
     assert_close(fin3, fin1, TOL_BF16, "fused vs two-launch final_states")
     assert_close(st, fin1, TOL_BF16, "range state vs final state")
+
+
+def test_bench_config3_full_size_properties():
+    """Full length of the long-sequence configuration (batch 1, 262144 steps, 128 heads, 8 groups, no gate) on one
+    GPU: two heads against the oracle over the whole sequence (output and final state), and the two-phase split
+    into two ranges against the single call."""
+    from mamba_b200 import ops
+    L, H, P, G, N, Q = 262144, 128, 64, 8, 128, 256
+    g = torch.Generator(device=DEV).manual_seed(1003)
+    r = lambda *sh: torch.randn(*sh, generator=g, device=DEV)
+    bf = torch.bfloat16
+    x, dt, B, C = r(1, L, H, P).to(bf), r(1, L, H).to(bf), r(1, L, G, N).to(bf), r(1, L, G, N).to(bf)
+    gh = torch.Generator().manual_seed(1003)
+    A = -(1 + 15 * torch.rand(H, generator=gh))
+    D = torch.randn(H, generator=gh)
+    dtv = torch.exp(torch.rand(H, generator=gh) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
+    bias = dtv + torch.log(-torch.expm1(-dtv))
+    Ad, Dd, bd = A.to(DEV), D.to(DEV), bias.to(DEV)
+    out, fin = _fn()(x, dt, Ad, B, C, Q, D=Dd, dt_bias=bd, dt_softplus=True, return_final_states=True)
+    assert _status() == 0
+    for h in (5, 127):
+        grp = h // (H // G)
+        f = lambda t: t.float().cpu()
+        want, wfin = oracle.ssd_chunk_scan(f(x[:, :, h:h + 1]), f(dt[:, :, h:h + 1]), A[h:h + 1], f(B[:, :, grp:grp + 1]),
+                                           f(C[:, :, grp:grp + 1]), Q, D[h:h + 1], None, bias[h:h + 1], None, dt_softplus=True)
+        assert_close(out[:, :, h:h + 1], want, TOL_BF16, f"head {h} out")
+        assert_close(fin[:, h:h + 1], wfin, TOL_BF16, f"head {h} final_states")
+    half = L // 2
+    loc, outs, f2 = [], [], None
+    for sl in (slice(0, half), slice(half, L)):
+        loc.append(ops.ssd_local_states(x[:, sl], dt[:, sl], Ad, B[:, sl], Q, dt_bias=bd, dt_softplus=True))
+    incoming = [None, ops.ssd_fold_state(None, loc[0][1], loc[0][0])]
+    for i, sl in enumerate((slice(0, half), slice(half, L))):
+        o, f2 = ops.ssd_finish(x[:, sl], dt[:, sl], Ad, B[:, sl], C[:, sl], Q, loc[i][2], D=Dd, dt_bias=bd,
+                               incoming_state=incoming[i], dt_softplus=True, return_final_states=True)
+        assert _status() == 0
+        outs.append(o)
+    assert_close(torch.cat(outs, dim=1), out.float(), TOL_BF16, "split out")
+    assert_close(f2, fin, TOL_BF16, "split final_states")

@@ -193,6 +193,40 @@ def test_bench_config4_consecutive_steps():
     assert_close(state, ref_state, TOL_FP32, "state after 16 steps")
 
 
+def test_bench_config4_full_size():
+    """The benchmark's own size: batch 256, 128 consecutive in-place steps.  Three batch rows are followed by the
+    oracle through all 128 steps (rows are independent), and a second run from the same start gives the same
+    bits (no atomics)."""
+    batch, steps, H, P, N = 256, 128, 80, 64, 128
+    d = bench_config4(batch, steps)
+    rows = torch.tensor([3, 128, 255])
+    A = d["A"].to(DEV)[:, None, None].expand(H, P, N)
+    bias = d["dt_bias"].to(DEV)[:, None].expand(H, P)
+    D = d["D"].to(DEV)[:, None].expand(H, P)
+    dev = {k: d[k].to(DEV) for k in ("x", "z", "dt", "B", "C")}
+
+    def run():
+        state = d["state"].to(DEV)
+        outs = []
+        for s in range(steps):
+            dt = dev["dt"][s][..., None].expand(batch, H, P)
+            outs.append(_fn()(state, dev["x"][s], dt, A, dev["B"][s], dev["C"][s], D, dev["z"][s], bias, dt_softplus=True)[rows.to(DEV)])
+        return state, torch.stack(outs)
+
+    state1, outs1 = run()
+    state2, outs2 = run()
+    assert torch.equal(state1, state2) and torch.equal(outs1, outs2)
+    ref_state = d["state"][rows].clone()
+    nb = len(rows)
+    for s in range(steps):
+        want = oracle.selective_state_update(ref_state, d["x"][s][rows].float(), d["dt"][s][rows].float()[..., None].expand(nb, H, P),
+                                             d["A"][:, None, None].expand(H, P, N), d["B"][s][rows].float(), d["C"][s][rows].float(),
+                                             d["D"][:, None].expand(H, P), d["z"][s][rows].float(),
+                                             d["dt_bias"][:, None].expand(H, P), dt_softplus=True)
+        assert_close(outs1[s], want, TOL_BF16, f"step {s} out")
+    assert_close(state1[rows.to(DEV)], ref_state, TOL_FP32, "state after 128 steps")
+
+
 def test_decode_matches_scan_recurrence():
     """T decode steps equal the Mamba-1 scan over the same T tokens (out per step and final state)."""
     from mamba_b200 import selective_scan_fn
