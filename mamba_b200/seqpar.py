@@ -71,19 +71,20 @@ def _send_state(t: torch.Tensor, dst: int, group) -> None:
 
 
 def _gather_summaries(state: torch.Tensor, decay: torch.Tensor, group):
-    """Every rank's (state, decay), stacked along a new leading dimension."""
+    """Every rank's (state, decay) as two lists indexed by rank; one collective carries both."""
     world = dist.get_world_size(group)
-    states = torch.empty((world,) + tuple(state.shape), dtype=state.dtype, device=state.device)
-    decays = torch.empty((world,) + tuple(decay.shape), dtype=decay.dtype, device=decay.device)
+    ns, nd = state.numel(), decay.numel()
+    mine = torch.cat([state.reshape(-1), decay.reshape(-1).to(state.dtype)])
+    everyone = torch.empty(world, ns + nd, dtype=state.dtype, device=state.device)
     try:
         if dist.get_backend(group) == "nccl":
-            dist.all_gather_into_tensor(states, state.contiguous(), group=group)
-            dist.all_gather_into_tensor(decays, decay.contiguous(), group=group)
+            dist.all_gather_into_tensor(everyone, mine, group=group)
         else:
-            dist.all_gather(list(states.unbind(0)), state.contiguous(), group=group)
-            dist.all_gather(list(decays.unbind(0)), decay.contiguous(), group=group)
+            dist.all_gather(list(everyone.unbind(0)), mine, group=group)
     except Exception as e:  # timeout, peer gone, transport error
         raise SequenceHandoffError(f"rank {dist.get_rank(group)}: gathering the range summaries failed: {e}") from e
+    states = [everyone[r, :ns].view(state.shape) for r in range(world)]          # views, nothing is copied
+    decays = [everyone[r, ns:].view(decay.shape).to(decay.dtype) for r in range(world)]
     return states, decays
 
 
