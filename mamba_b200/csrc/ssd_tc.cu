@@ -533,11 +533,12 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     float *cks = dA2 + 256;                                         // 256: exp(dA_ref(k) - dA_k) dt_k, ref(k) = k | 31
     __nv_bfloat16 *dts = reinterpret_cast<__nv_bfloat16 *>(cks + 256);   // 256: dt (only the exact path reads it)
     int *mono = reinterpret_cast<int *>(sm + 73728 + 2560);         // 1 while dA_cumsum is non-increasing over the chunk
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 73728 + 2560 + 64);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 73728 + 2560 + 16);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 22);
     uint64_t *bar_chfull = &bars[0], *bar_z = &bars[2], *bar_g2 = &bars[3];     // bar_chfull[kb]: C / H half kb has landed
     uint64_t *bar_full = &bars[4], *bar_scaled = &bars[8], *bar_e = &bars[12];   // bar_e[j]: block j has been multiplied
     uint64_t *bar_chdone = &bars[14];                                            // bar_chdone[kb]: C.H^T part kb has been multiplied
+    uint64_t *bar_chscaled = &bars[16];                                          // bar_chscaled[kb]: scaled C half kb is in tensor memory
 
     const int h = blockIdx.x, c = blockIdx.y >> 1, mb = blockIdx.y & 1, b = blockIdx.z;
     const int g = h / (a.nheads / a.ngroups);
@@ -563,6 +564,8 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         mbar_init(&bar_chfull[1], 1);
         mbar_init(&bar_chdone[0], 1);
         mbar_init(&bar_chdone[1], 1);
+        mbar_init(&bar_chscaled[0], 8);
+        mbar_init(&bar_chscaled[1], 8);
         mbar_init(bar_z, 1);
         mbar_init(bar_g2, 1);
         for (int i = 0; i < 4; ++i) {
@@ -593,14 +596,13 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 tma_load_4d(slot_ptr(j) + kSlotX, &tm_x, &bar_full[j], 0, h, c * kQ + j * 64, b);
             };
             const uint32_t idesc2 = instr_desc_f16(128, 64, Fmt<T>::v, 0, 1);
-            auto gemm2_block = [&](int j) {      // Y2 += (CB o L)_j . X_j once the element-wise warps release block j
+            auto gemm2_block = [&](int j) {      // Y += (CB o L)_j . X_j once the element-wise warps have put the scaled tile in TMEM
                 ok = ok && mbar_wait(&bar_scaled[j], 0, status, kStBarScaled);
                 if (ok) {
                     tc_fence_after_sync();
                     const uint32_t sb = smem_u32(slot_ptr(j));
                     for (int s = 0; s < 4; ++s)
-                        mma_f16_ss(tmem + 64, smem_desc_sw128(sb + s * 32, 16, 1024),
-                                   smem_desc_sw128(sb + kSlotX + s * 2048, 16, 1024), idesc2, (j | s) != 0);
+                        mma_f16_ts(tmem, tmem + 64 + (j & 1) * 32 + s * 8, smem_desc_sw128(sb + kSlotX + s * 2048, 16, 1024), idesc2, true);
                 }
             };
             auto load_z = [&]() {
@@ -627,16 +629,16 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 if (a.z) tma_prefetch_l2_4d(&tm_z, 0, h, c * kQ + mb * 128, b);
 #endif
             }
-            // Y1 = C . H^T in two K halves
+            // Y = (exp(dA_m) C) . H^T in two K halves; the row-scaled C half comes from tensor memory
             const uint32_t idesc1 = instr_desc_f16(128, 64, Fmt<T>::v, 0, h_np ? 1 : 0);
             for (int kb = 0; kb < 2; ++kb) {
-                ok = ok && mbar_wait(&bar_chfull[kb], 0, status, kStBarC);
+                ok = ok && mbar_wait(&bar_chscaled[kb], 0, status, kStBarC);
                 if (kb == 0) MB200_TRACE(1);
                 if (ok) {
                     tc_fence_after_sync();
-                    const uint32_t cb_ = smem_u32(sm + kb * kSlot), hb_ = cb_ + kSlotX;
+                    const uint32_t hb_ = smem_u32(sm + kb * kSlot) + kSlotX;
                     for (int s = 0; s < 4; ++s)
-                        mma_f16_ss(tmem, smem_desc_sw128(cb_ + s * 32, 16, 1024),
+                        mma_f16_ts(tmem, tmem + 64 + kb * 32 + s * 8,
                                    h_np ? smem_desc_sw128(hb_ + s * 2048, 16, 1024) : smem_desc_sw128(hb_ + s * 32, 16, 1024), idesc1,
                                    (kb | s) != 0);
                 }
@@ -659,9 +661,9 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             }
             gemm2_block(1);
             if (nk > 2) {
+                mma_commit(&bar_e[1]);                   // frees slot 0 and the second TMEM tile buffer
                 if (a.z) {
-                    mma_commit(&bar_e[1]);
-                    ok = ok && mbar_wait(&bar_e[1], 0, status, kStBarEmpty);   // slot 0 has been read
+                    ok = ok && mbar_wait(&bar_e[1], 0, status, kStBarEmpty);
                     if (ok) load_z();
                 }
                 gemm2_block(2);
@@ -690,23 +692,56 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         const float dAm = dA2[m];
         const bool factor_ok = *mono != 0;
         bool ok = (smem_u32(sm) & 1023u) == 0;
+        const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);      // my row of tensor memory
+        // The A operands of all products go to the tensor core through tensor memory: a thread reads its 32
+        // columns of the 16 KB tile from shared memory, applies its factors, and writes 16 packed words to its TMEM
+        // lane (two tile buffers of 32 columns, used alternately by the ring items).
+        // First the two K halves of C, row-scaled by exp(dA_m), so that C.H^T lands in the same accumulator.
+        {
+            const float rs = ex2(dAm);
+            const uint32_t rs2 = Pack2<T>::pack(rs, rs);
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb) {
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(&bar_chfull[kb], 0, status, kStBarC));
+                if (ok) {
+                    const uint32_t rowaddr = smem_u32(sm + kb * kSlot) + r * 128;
+                    uint32_t w[16];
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const uint4 v = lds128(rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4));
+                        w[4 * ch] = Pack2<T>::mul(v.x, rs2);
+                        w[4 * ch + 1] = Pack2<T>::mul(v.y, rs2);
+                        w[4 * ch + 2] = Pack2<T>::mul(v.z, rs2);
+                        w[4 * ch + 3] = Pack2<T>::mul(v.w, rs2);
+                    }
+                    tmem_st16(tlane + 64 + kb * 32 + kh * 16, w);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(&bar_chscaled[kb]);
+            }
+        }
         for (int j = 0; j < nk; ++j) {
             const int klo = j * 64 + kh * 32;       // first column of this thread's range
             ok = ok && mbar_wait(&bar_full[j], 0, status, kStBarFull);
+            // the tile buffer this block goes to was last read by the product two ring items earlier
+            ok = ok && mbar_wait(j < 2 ? &bar_chdone[j] : &bar_e[j - 2], 0, status, kStBarEmpty);
+            ok = __all_sync(0xffffffffu, ok);       // tcgen05.st is warp-collective
             if (threadIdx.x == 0 && j == 0) MB200_TRACE(10);
             const uint32_t rowaddr = smem_u32(slot_ptr(j)) + r * 128;
             if (ok) {
+                tc_fence_after_sync();
+                uint32_t w[16];
                 if (klo > m) {
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) sts128(rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4), make_uint4(0, 0, 0, 0));
+                    for (int i = 0; i < 16; ++i) w[i] = 0u;
                 } else if (klo + 31 <= m && factor_ok) {
                     const float rm = ex2(dAm - dA2[klo + 31]);
                     const uint64_t rm2 = pack2(rm, rm);
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) {
-                        const uint32_t addr = rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4);
-                        uint4 v = lds128(addr);
-                        uint32_t *e = reinterpret_cast<uint32_t *>(&v);
+                        const uint4 v = lds128(rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4));
+                        const uint32_t e[4] = {v.x, v.y, v.z, v.w};
                         const ulonglong2 *ck = reinterpret_cast<const ulonglong2 *>(cks + klo + ch * 8);
                         const ulonglong2 c01 = ck[0], c23 = ck[1];
                         const uint64_t cp[4] = {c01.x, c01.y, c23.x, c23.y};
@@ -714,16 +749,14 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         for (int q = 0; q < 4; ++q) {
                             float l0, l1;
                             unpack2(mul2(rm2, cp[q]), l0, l1);
-                            e[q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
+                            w[4 * ch + q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
                         }
-                        sts128(addr, v);
                     }
                 } else {
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) {
-                        const uint32_t addr = rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4);
-                        uint4 v = lds128(addr);
-                        uint32_t *e = reinterpret_cast<uint32_t *>(&v);
+                        const uint4 v = lds128(rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4));
+                        const uint32_t e[4] = {v.x, v.y, v.z, v.w};
                         const int kc = klo + ch * 8;
                         const float4 d0 = *reinterpret_cast<const float4 *>(dA2 + kc), d1 = *reinterpret_cast<const float4 *>(dA2 + kc + 4);
                         const uint4 tv = *reinterpret_cast<const uint4 *>(dts + kc);
@@ -734,15 +767,15 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                             const float2 tk = Pack2<__nv_bfloat16>::unpack(tw[q]);
                             const float l0 = (kc + 2 * q <= m) ? ex2(fminf(dAm - dk[2 * q], 0.f)) * tk.x : 0.f;
                             const float l1 = (kc + 2 * q + 1 <= m) ? ex2(fminf(dAm - dk[2 * q + 1], 0.f)) * tk.y : 0.f;
-                            e[q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
+                            w[4 * ch + q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
                         }
-                        sts128(addr, v);
                     }
                 }
+                tmem_st16(tlane + 64 + (j & 1) * 32 + kh * 16, w);
             }
-            fence_proxy_async();
+            tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_scaled[j]);
+            if (lane == 0 && ok) mbar_arrive(&bar_scaled[j]);
         }
         if (threadIdx.x == 0) MB200_TRACE(11);
         ok = ok && mbar_wait(bar_g2, 0, status, kStBarG2);
@@ -751,11 +784,9 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: the whole warp takes one path
         tc_fence_after_sync();
         if (ok) {
-            float y1[32], y2[32];
-            const uint32_t tl = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kh * 32;
-            tmem_ld32_pair(tl, tl + 64, y1, y2);
+            float acc[32];
+            tmem_ld32(tlane + kh * 32, acc);
             if (threadIdx.x == 0) MB200_TRACE(14);
-            const float scale = ex2(dAm);
             // row m of x sits in the x part of the slot that carried block m / 64
             const uint32_t xrow = smem_u32(slot_ptr(m >> 6) + kSlotX) + (m & 63) * 128;
 #pragma unroll
@@ -764,7 +795,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 const uint32_t swz = (uint32_t)(((p0 >> 3) ^ (r & 7)) << 4);
                 float y[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) y[i] = fmaf(scale, y1[q4 * 8 + i], y2[q4 * 8 + i]);
+                for (int i = 0; i < 8; ++i) y[i] = acc[q4 * 8 + i];
                 if (a.D) {
                     const uint4 xv = lds128(xrow + swz);
                     const uint32_t *xe = reinterpret_cast<const uint32_t *>(&xv);
