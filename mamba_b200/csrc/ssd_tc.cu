@@ -507,6 +507,9 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 #ifndef MB200_SCAN_L2_PREFETCH
 #define MB200_SCAN_L2_PREFETCH 1
 #endif
+// Largest decay span (in powers of two) of a 32-column range for which the diagonal range may use the factorised
+// mask: the row factor 2^span and the smallest column factor 2^-span * dt stay far inside the fp32 range.
+constexpr float kMaxDiagSpan = 80.f;
 constexpr int kScanThreads = 288;
 constexpr uint32_t kScanSmem = 49152 + 24576 + 1024 + 1024 + 512 + 64 + 128 + 16;   // 76496 B, base must be 1 KB aligned
 #ifdef MB200_SCAN_TRACE
@@ -749,6 +752,28 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         for (int q = 0; q < 4; ++q) {
                             float l0, l1;
                             unpack2(mul2(rm2, cp[q]), l0, l1);
+                            w[4 * ch + q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
+                        }
+                    }
+                } else if (factor_ok && dA2[klo] - dA2[klo + 31] <= kMaxDiagSpan) {
+                    // the range holds the diagonal but its decay span is moderate: same split with ref = last column
+                    // (the row factor is then >= 1, bounded by 2^kMaxDiagSpan), columns past the diagonal masked
+                    const float rm = ex2(dAm - dA2[klo + 31]);
+                    const uint64_t rm2 = pack2(rm, rm);
+                    const int dm = m - klo;             // columns 0..dm of the range are at or before the diagonal
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const uint4 v = lds128(rowaddr + (((kh * 4 + ch) ^ (r & 7)) << 4));
+                        const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+                        const ulonglong2 *ck = reinterpret_cast<const ulonglong2 *>(cks + klo + ch * 8);
+                        const ulonglong2 c01 = ck[0], c23 = ck[1];
+                        const uint64_t cp[4] = {c01.x, c01.y, c23.x, c23.y};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            float l0, l1;
+                            unpack2(mul2(rm2, cp[q]), l0, l1);
+                            l0 = (ch * 8 + 2 * q <= dm) ? l0 : 0.f;
+                            l1 = (ch * 8 + 2 * q + 1 <= dm) ? l1 : 0.f;
                             w[4 * ch + q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
                         }
                     }
