@@ -61,6 +61,8 @@ def test_argument_errors_without_gpu(built):
     assert rc == _lib.ERR_BAD_ARG and b"256" in _lib.lib().mb200_last_error()
     with pytest.raises(AssertionError):
         _lib.check(rc)
+    rc = _lib.lib().mb200_scan_status(0, None)
+    assert rc == _lib.ERR_BAD_ARG and b"status is NULL" in _lib.lib().mb200_last_error()
     s = _lib.SsdArgs()
     s.batch, s.seqlen, s.nheads, s.headdim, s.ngroups, s.dstate, s.chunk_size = 64, 1 << 16, 64, 64, 1, 128, 256
     s.phases = _lib.PHASE_ALL

@@ -136,6 +136,19 @@ def test_tma_fed_kernel(dtype, tol, L, N, groups, gated):
     assert_close(got_last, want_last, tol, "tma-fed last_state")
 
 
+def test_tma_fed_kernel_plain_delta():
+    """The same kernel without softplus, bias, skip and gate (delta used as given)."""
+    from mamba_b200 import ops
+    inp = make_inputs(97, 2, 4800, 200, 16, 1, torch.bfloat16, has_z=False, has_D=False)
+    want, want_last = oracle.selective_scan(inp["u"].float(), inp["delta"].float(), inp["A"], inp["B"].float(), inp["C"].float(),
+                                            None, None, None, delta_softplus=False, return_last_state=True)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    got, got_last = _fn()(c["u"], c["delta"], c["A"], c["B"], c["C"], return_last_state=True)
+    assert ops.scan_status() == 0
+    assert_close(got, want, TOL_BF16, "plain delta out")
+    assert_close(got_last, want_last, TOL_BF16, "plain delta last_state")
+
+
 def test_many_channels_unaligned_and_ungated():
     inp = make_inputs(71, 2, 4800, 77, 16, 1, torch.bfloat16, has_z=False, has_D=False)
     c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}

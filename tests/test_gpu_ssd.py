@@ -111,6 +111,22 @@ def test_fused_state_stream_shapes(dtype, b, L, G, H, init, has_z):
              f"stream b{b} L{L} G{G} H{H}")
 
 
+def test_fused_state_stream_options():
+    """The fused path with a per-(head, column) D, a dt clamp and no softplus."""
+    inp = make(171, 2, 768, 40, 64, 2, 128, torch.bfloat16, has_z=True, D_hdim=True, init=True)
+    inp["dt"] = (inp["dt"].float().abs() * 0.1).to(torch.bfloat16)
+    inp["dt_bias"] = None
+    f = lambda t: None if t is None else t.float()
+    want, wfin = oracle.ssd_chunk_scan(f(inp["x"]), f(inp["dt"]), inp["A"], f(inp["B"]), f(inp["C"]), 256, inp["D"], f(inp["z"]), None,
+                                       inp["initial_states"], dt_softplus=False, dt_limit=(0.01, 0.1))
+    c = {k: _c(v) for k, v in inp.items()}
+    got, fin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 256, D=c["D"], z=c["z"], initial_states=c["initial_states"],
+                     dt_limit=(0.01, 0.1), return_final_states=True)
+    assert _status() == 0
+    assert_close(got, want, TOL_BF16, "fused options out")
+    assert_close(fin, wfin, TOL_BF16, "fused options final")
+
+
 def test_dt_limit_and_no_softplus():
     inp = make(11, 1, 128, 2, 16, 1, 16, torch.float32)
     inp["dt"] = inp["dt"].abs() * 0.1
