@@ -127,7 +127,7 @@ class Workload:
             self.dtype = "bf16"
             self.step_inputs = ("x", "dt", "z", "B", "C")
             self.alg_bytes = 3 * b * L * H * P * 2 + b * L * H * 2 + 2 * b * L * 128 * 2 + b * H * P * 128 * 4 + 3 * H * 4
-            self.launches_per_step = 4      # cumsum, state stream, C.B^T, chunk scan
+            self.launches_per_step = 5      # cumsum, state stream (head pairs, then single heads), C.B^T, chunk scan
         elif name == "c3":
             # long sequence split into contiguous chunk ranges, one per rank; the whole sequence at N=1
             from mamba_b200.seqpar import split_sequence

@@ -287,36 +287,48 @@ __global__ void __launch_bounds__(kStateThreads) ssd_tc_chunk_state_kernel(const
 // folds H <- exp(dA_last_c) H + S_c.  After the last chunk H is the final state.
 // 576 threads: warps 0-15 weight the x rows and own the running state (16 warps because this work is a chain
 // of shared-memory and TMEM round trips that only more warps in flight can hide), warp 16 issues TMA loads,
-// warp 17 the MMAs.  Shared memory: 4 stages of half a chunk (B 2 x 16 KB + x 16 KB for 128 steps) and one 16 KB state
-// tile; TMEM: two accumulators of 64 columns, so the MMAs of chunk c overlap the fold of chunk c-1.
+// warp 17 the MMAs.  Shared memory: stages of half a chunk (B 2 x 16 KB + x 16 KB per head for 128 steps) and one
+// 16 KB state tile per head; TMEM: two accumulators of 64 columns per head, so the MMAs of chunk c overlap the fold
+// of chunk c-1.  A CTA serves one head or two heads of one group (template parameter HEADS): with two, the B tile
+// is fetched and read by the tensor core once for both (N = 128).
 #ifndef MB200_SSD_STREAM_MIN_UNITS
 #define MB200_SSD_STREAM_MIN_UNITS 74
 #endif
 constexpr int kStreamWarps = 16;                       // element-wise warps
 constexpr int kStreamThreads = (kStreamWarps + 2) * 32;
-constexpr uint32_t kStreamStage = 49152;
-constexpr uint32_t kStreamSmem = 4 * kStreamStage + 16384 + 256 + 1024;
+// HEADS heads of one group per CTA share the B tile: one stage is half a chunk of B (2 x 16 KB) and of every head's
+// x (16 KB each).  One head: 4 stages of 48 KB; two heads: 3 stages of 64 KB; plus one 16 KB state tile per head.
+template <int HEADS> struct StreamCfg {
+    static constexpr uint32_t kStage = 32768 + HEADS * 16384;
+    static constexpr int kStages = HEADS == 1 ? 4 : 3;
+    static constexpr uint32_t kSmem = kStages * kStage + HEADS * 16384 + 256 + 1024;
+};
 enum { kStStreamFull = 41, kStStreamWeighted, kStStreamEmpty, kStStreamAcc, kStStreamAccEmpty };
 
-template <typename T>
+template <typename T, int HEADS>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
                            const __grid_constant__ CUtensorMap tm_Hs, const float *dtb, const float *dAb, const float *initial,
                            float *final_states, float *range_decay, float *prefix_decay, float *state_copy, float *decay_copy,
-                           int store_entering, int nchunks, int nheads, int heads_per_group, int *status)
+                           int store_entering, int nchunks, int nheads, int heads_per_group, int unit0, int *status)
 {
+    using Cfg = StreamCfg<HEADS>;
+    constexpr int NST = Cfg::kStages;
+    constexpr uint32_t kStage = Cfg::kStage;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = align1024(smem_raw);
-    uint8_t *tile = sm + 4 * kStreamStage;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tile + 16384);
+    uint8_t *tile = sm + NST * kStage;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tile + HEADS * 16384);
     uint64_t *full = bars, *weighted = bars + 4, *empty = bars + 8, *acc_full = bars + 12, *acc_empty = bars + 14;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
-    const int h = blockIdx.x, b = blockIdx.y;
-    const int g = h / heads_per_group;
+    // work unit = HEADS consecutive heads of one batch row (all of one group); units are numbered batch-major
+    const int unit = unit0 + blockIdx.x, upb = nheads / HEADS;
+    const int h0 = (unit % upb) * HEADS, b = unit / upb;
+    const int g = h0 / heads_per_group;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nstages = 2 * nchunks;
     if (threadIdx.x == kStreamWarps * 32) {
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < NST; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&weighted[i], kStreamWarps);      // one arrival per element-wise warp
             mbar_init(&empty[i], 1);
@@ -327,47 +339,47 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
         }
         mbar_fence_init();
     }
-    if (warp == kStreamWarps) tmem_alloc(tmem_slot, 128);
+    if (warp == kStreamWarps) tmem_alloc(tmem_slot, 128 * HEADS);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
     if (warp == kStreamWarps) {
-        // ------------------------------------------------------------------ TMA loads, up to 4 stages ahead
+        // ------------------------------------------------------------------ TMA loads, up to NST stages ahead
         if (lane == 0) {
             int issued = 0;
             for (int i = 0; i < nstages; ++i) {
-                const int st = i & 3;
-                if (i >= 4 && !mbar_wait(&empty[st], ((i >> 2) - 1) & 1, status, kStStreamEmpty)) break;
-                uint8_t *dst = sm + st * kStreamStage;
+                const int st = i % NST;
+                if (i >= NST && !mbar_wait(&empty[st], ((i / NST) - 1) & 1, status, kStStreamEmpty)) break;
+                uint8_t *dst = sm + st * kStage;
                 const int t0 = i * 128;
-                mbar_expect_tx(&full[st], kStreamStage);
-                tma_load_4d(dst + 32768, &tm_x, &full[st], 0, h, t0, b);
+                mbar_expect_tx(&full[st], kStage);
+                for (int hd = 0; hd < HEADS; ++hd) tma_load_4d(dst + 32768 + hd * 16384, &tm_x, &full[st], 0, h0 + hd, t0, b);
                 tma_load_4d(dst, &tm_B, &full[st], 0, g, t0, b);
                 tma_load_4d(dst + 16384, &tm_B, &full[st], 64, g, t0, b);
                 ++issued;
             }
             // nothing may still be landing in this CTA's shared memory when it exits
-            for (int i = issued > 4 ? issued - 4 : 0; i < issued; ++i) mbar_wait(&full[i & 3], (i >> 2) & 1, status, kStStreamFull);
+            for (int i = issued > NST ? issued - NST : 0; i < issued; ++i) mbar_wait(&full[i % NST], (i / NST) & 1, status, kStStreamFull);
         }
     } else if (warp == kStreamWarps + 1) {
-        // ------------------------------------------------------------------ MMAs
+        // ------------------------------------------------------------------ MMAs: S^T[n, (head, p)] += B[k, n] xw[k, (head, p)]
         if (lane == 0) {
-            const uint32_t idesc = instr_desc_f16(128, 64, Fmt<T>::v, 1, 1);
+            const uint32_t idesc = instr_desc_f16(128, 64 * HEADS, Fmt<T>::v, 1, 1);
             bool ok = true;
             for (int c = 0; c < nchunks && ok; ++c) {
-                const uint32_t acc = tmem + (uint32_t)(c & 1) * 64;
+                const uint32_t acc = tmem + (uint32_t)(c & 1) * 64 * HEADS;
                 if (c >= 2) ok = mbar_wait(&acc_empty[c & 1], ((c >> 1) - 1) & 1, status, kStStreamAccEmpty);
                 for (int half = 0; half < 2 && ok; ++half) {
-                    const int i = 2 * c + half, st = i & 3;
-                    ok = mbar_wait(&weighted[st], (i >> 2) & 1, status, kStStreamWeighted);
+                    const int i = 2 * c + half, st = i % NST;
+                    ok = mbar_wait(&weighted[st], (i / NST) & 1, status, kStStreamWeighted);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t sb = smem_u32(sm + st * kStreamStage);
+                    const uint32_t sb = smem_u32(sm + st * kStage);
                     for (int s = 0; s < 8; ++s)
-                        mma_f16_ss(acc, smem_desc_sw128(sb + s * 2048, 16384, 1024), smem_desc_sw128(sb + 32768 + s * 2048, 16, 1024), idesc,
-                                   (half | s) != 0);
+                        mma_f16_ss(acc, smem_desc_sw128(sb + s * 2048, 16384, 1024), smem_desc_sw128(sb + 32768 + s * 2048, 16384, 1024),
+                                   idesc, (half | s) != 0);
                     mma_commit(&empty[st]);
                 }
                 if (ok) mma_commit(&acc_full[c & 1]);
@@ -376,48 +388,66 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
     } else {
         // ------------------------------------------------------------------ element-wise warps
         const int tid = threadIdx.x;
-        const int r = tid >> 2, cq = (tid & 3) * 2;          // my x row inside a stage and my two 16-byte chunks of it
+        // weighting: the 512 threads split into HEADS groups; a group's threads share out the 128 rows x 8 chunks
+        // of its head's x tile
+        constexpr int TPH = kStreamWarps * 32 / HEADS, TPR = TPH / 128, NCH = 8 / TPR;
+        const int whead = tid / TPH, wt = tid % TPH;
+        const int r = wt / TPR, cq = (wt % TPR) * NCH;       // my x row inside a stage and my first 16-byte chunk of it
         const int n = (warp & 3) * 32 + lane;                // TMEM lane = state index
-        const int p0 = (warp >> 2) * 16;                     // my quarter of the head's columns
-        const int64_t bh = (int64_t)b * nheads + h;
-        float H[16];
+        const int p0 = (warp >> 2) * 16;                     // my quarter of every head's columns
+        const int64_t bh0 = (int64_t)b * nheads + h0;
+        float H[HEADS][16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) H[j] = initial ? initial[bh * (kP * kN) + (int64_t)(p0 + j) * kN + n] : 0.f;
-        auto scalars = [&](int c, float (&v)[5]) {
-            const float *dAc = dAb + (bh * nchunks + c) * kQ, *dtc = dtb + (bh * nchunks + c) * kQ;
-            v[0] = dAc[r]; v[1] = dtc[r]; v[2] = dAc[128 + r]; v[3] = dtc[128 + r]; v[4] = dAc[kQ - 1];
+        for (int hd = 0; hd < HEADS; ++hd)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) H[hd][j] = initial ? initial[(bh0 + hd) * (kP * kN) + (int64_t)(p0 + j) * kN + n] : 0.f;
+        // per chunk: dA and dt of my two x rows (my weighting head), and every head's dA at the end of the chunk
+        auto scalars = [&](int c, float (&v)[4 + HEADS]) {
+            const float *dAc = dAb + ((bh0 + whead) * nchunks + c) * kQ, *dtc = dtb + ((bh0 + whead) * nchunks + c) * kQ;
+            v[0] = dAc[r]; v[1] = dtc[r]; v[2] = dAc[128 + r]; v[3] = dtc[128 + r];
+#pragma unroll
+            for (int hd = 0; hd < HEADS; ++hd) v[4 + hd] = dAb[((bh0 + hd) * nchunks + c) * kQ + kQ - 1];
         };
-        float nxt[5];
+        float nxt[4 + HEADS];
         scalars(0, nxt);
-        float dec_prev = 0.f, dA_total = 0.f;
+        float dec_prev[HEADS], dA_total[HEADS];
+#pragma unroll
+        for (int hd = 0; hd < HEADS; ++hd) dec_prev[hd] = 0.f, dA_total[hd] = 0.f;
         bool ok = true;
-        auto fold = [&](int c, float dec) {      // H <- dec H + S_c once the MMAs of chunk c have completed
+        auto fold = [&](int c) {      // H <- dec H + S_c once the MMAs of chunk c have completed
             ok = __all_sync(0xffffffffu, ok && mbar_wait(&acc_full[c & 1], (c >> 1) & 1, status, kStStreamAcc));   // tcgen05.ld is warp-collective
             if (!ok) return;
             tc_fence_after_sync();
-            float v[16];
-            tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(c & 1) * 64 + p0, v);
+            float v[HEADS][16];
+#pragma unroll
+            for (int hd = 0; hd < HEADS; ++hd)
+                tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(c & 1) * 64 * HEADS + hd * 64 + p0, v[hd]);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[c & 1]);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) H[j] = fmaf(dec, H[j], v[j]);
+            for (int hd = 0; hd < HEADS; ++hd)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) H[hd][j] = fmaf(dec_prev[hd], H[hd][j], v[hd][j]);
         };
         for (int c = 0; c < nchunks && ok; ++c) {
-            float cur[5];
+            float cur[4 + HEADS];
 #pragma unroll
-            for (int q = 0; q < 5; ++q) cur[q] = nxt[q];
+            for (int q = 0; q < 4 + HEADS; ++q) cur[q] = nxt[q];
             if (c + 1 < nchunks) scalars(c + 1, nxt);
+            float my_last = cur[4];
+#pragma unroll
+            for (int hd = 1; hd < HEADS; ++hd) my_last = whead == hd ? cur[4 + hd] : my_last;
             // weight my x rows of both halves: w_k = exp(dA_last - dA_k) dt_k
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                const int i = 2 * c + half, st = i & 3;
-                const float w = __expf(fminf(cur[4] - cur[2 * half], 0.f)) * cur[2 * half + 1];
-                ok = ok && mbar_wait(&full[st], (i >> 2) & 1, status, kStStreamFull);
+                const int i = 2 * c + half, st = i % NST;
+                const float w = __expf(fminf(my_last - cur[2 * half], 0.f)) * cur[2 * half + 1];
+                ok = ok && mbar_wait(&full[st], (i / NST) & 1, status, kStStreamFull);
                 if (ok) {
-                    const uint32_t base = smem_u32(sm + st * kStreamStage + 32768) + r * 128;
+                    const uint32_t base = smem_u32(sm + st * kStage + 32768 + whead * 16384) + r * 128;
 #pragma unroll
-                    for (int ch = 0; ch < 2; ++ch) {
+                    for (int ch = 0; ch < NCH; ++ch) {
                         const uint32_t addr = base + (((cq + ch) ^ (r & 7)) << 4);
                         uint4 v = lds128(addr);
                         uint32_t *e = reinterpret_cast<uint32_t *>(&v);
@@ -433,53 +463,65 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
                 __syncwarp();
                 if (lane == 0 && ok) mbar_arrive(&weighted[st]);
             }
-            if (c > 0) fold(c - 1, dec_prev);
-            dec_prev = __expf(cur[4]);
-            if (tid == 0 && prefix_decay) prefix_decay[bh * nchunks + c] = __expf(dA_total);   // decay from the range start to chunk c
-            dA_total += cur[4];
-            // the state entering chunk c leaves as a 16-bit [n][p] tile (not when only the range summary is wanted)
-            if (tid == 0 && store_entering) tma_store_wait_read();   // the previous store has finished reading the tile
+            if (c > 0) fold(c - 1);
+#pragma unroll
+            for (int hd = 0; hd < HEADS; ++hd) {
+                dec_prev[hd] = __expf(cur[4 + hd]);
+                if (tid == 0 && prefix_decay) prefix_decay[(bh0 + hd) * nchunks + c] = __expf(dA_total[hd]);   // decay from the range start to chunk c
+                dA_total[hd] += cur[4 + hd];
+            }
+            // the states entering chunk c leave as 16-bit [n][p] tiles (not when only the range summary is wanted)
+            if (tid == 0 && store_entering) tma_store_wait_read();   // the previous stores have finished reading the tiles
             ok = stream_barrier_and(ok);                     // from here on every element-wise warp agrees on ok
             if (!ok) break;
             if (store_entering) {
-                const uint32_t row = smem_u32(tile) + n * 128;
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    uint4 o;
-                    o.x = Pack2<T>::pack(H[8 * q + 0], H[8 * q + 1]);
-                    o.y = Pack2<T>::pack(H[8 * q + 2], H[8 * q + 3]);
-                    o.z = Pack2<T>::pack(H[8 * q + 4], H[8 * q + 5]);
-                    o.w = Pack2<T>::pack(H[8 * q + 6], H[8 * q + 7]);
-                    sts128(row + ((((p0 >> 3) + q) ^ (n & 7)) << 4), o);
+                for (int hd = 0; hd < HEADS; ++hd) {
+                    const uint32_t row = smem_u32(tile + hd * 16384) + n * 128;
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        uint4 o;
+                        o.x = Pack2<T>::pack(H[hd][8 * q + 0], H[hd][8 * q + 1]);
+                        o.y = Pack2<T>::pack(H[hd][8 * q + 2], H[hd][8 * q + 3]);
+                        o.z = Pack2<T>::pack(H[hd][8 * q + 4], H[hd][8 * q + 5]);
+                        o.w = Pack2<T>::pack(H[hd][8 * q + 6], H[hd][8 * q + 7]);
+                        sts128(row + ((((p0 >> 3) + q) ^ (n & 7)) << 4), o);
+                    }
                 }
                 fence_proxy_async();
                 asm volatile("bar.sync 1, 512;" ::: "memory");
                 if (tid == 0) {
-                    tma_store_3d(&tm_Hs, tile, 0, 0, (int)((((int64_t)b * nchunks + c) * nheads) + h));
+                    for (int hd = 0; hd < HEADS; ++hd)
+                        tma_store_3d(&tm_Hs, tile + hd * 16384, 0, 0, (int)((((int64_t)b * nchunks + c) * nheads) + h0 + hd));
                     tma_store_commit();
                 }
             }
         }
-        if (ok) fold(nchunks - 1, dec_prev);
-        if (ok && final_states) {
-            float *F = final_states + bh * (kP * kN);
+        if (ok) fold(nchunks - 1);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) F[(p0 + j) * kN + n] = H[j];
-        }
-        if (ok && state_copy) {
-            float *F = state_copy + bh * (kP * kN);
+        for (int hd = 0; hd < HEADS; ++hd) {
+            if (ok && final_states) {
+                float *F = final_states + (bh0 + hd) * (kP * kN);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) F[(p0 + j) * kN + n] = H[j];
+                for (int j = 0; j < 16; ++j) F[(p0 + j) * kN + n] = H[hd][j];
+            }
+            if (ok && state_copy) {
+                float *F = state_copy + (bh0 + hd) * (kP * kN);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) F[(p0 + j) * kN + n] = H[hd][j];
+            }
         }
         if (tid == 0) {
             tma_store_wait_read();
-            if (ok && range_decay) range_decay[bh] = __expf(dA_total);
-            if (ok && decay_copy) decay_copy[bh] = __expf(dA_total);
+            for (int hd = 0; hd < HEADS; ++hd) {
+                if (ok && range_decay) range_decay[bh0 + hd] = __expf(dA_total[hd]);
+                if (ok && decay_copy) decay_copy[bh0 + hd] = __expf(dA_total[hd]);
+            }
         }
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == kStreamWarps) tmem_dealloc(tmem, 128);
+    if (warp == kStreamWarps) tmem_dealloc(tmem, 128 * HEADS);
 }
 
 // ====================================================================================== chunk scan
@@ -971,7 +1013,6 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         const uint64_t s[2] = {(uint64_t)kP * 2, (uint64_t)kN * kP * 2};
         const uint32_t bx[3] = {64, 128, 1};
         if (!encode_16bit(&tHs, fmt, prev16, 3, d, s, bx)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for states failed");
-        cudaFuncSetAttribute(ssd_tc_state_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmem);
         // whole operator: from initial_states, entering states stored.  LOCAL half of a sequence split: from a zero
         // state, entering states stored as they are without the incoming state, plus what the OUTPUT half needs to
         // add that state's share later.
@@ -979,9 +1020,28 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         float *aux_prefix = whole ? nullptr : reinterpret_cast<float *>(base + lay.off_aux);
         float *aux_state = whole ? nullptr : reinterpret_cast<float *>(base + lay.off_aux_state);
         float *aux_decay = whole ? nullptr : reinterpret_cast<float *>(base + lay.off_aux_decay);
-        ssd_tc_state_stream_kernel<T><<<dim3(a.nheads, a.batch), kStreamThreads, kStreamSmem, stream>>>(
-            tx, tB, tHs, dtb, dAb, whole ? a.initial_states : nullptr, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1,
-            nc, a.nheads, a.nheads / a.ngroups, status);
+        const float *init = whole ? a.initial_states : nullptr;
+        const int hpg = a.nheads / a.ngroups;
+        // Two heads of a group per CTA share the B tile (a fifth less shared-memory and L2 traffic per head), but a
+        // CTA then runs 1.6x as long, so only whole waves of such CTAs pay; what is left over runs as pairs if that is
+        // more than half a wave and as single heads otherwise.
+        const int sms = sm_count(a.device);
+        const int64_t pairs = hpg % 2 == 0 ? (int64_t)a.batch * (a.nheads / 2) : 0;
+        int64_t paired = pairs / sms * sms;
+        if (pairs - paired > sms / 2) paired = pairs;
+        if (paired > 0) {
+            cudaFuncSetAttribute(ssd_tc_state_stream_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamCfg<2>::kSmem);
+            ssd_tc_state_stream_kernel<T, 2><<<(unsigned)paired, kStreamThreads, StreamCfg<2>::kSmem, stream>>>(
+                tx, tB, tHs, dtb, dAb, init, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1, nc, a.nheads, hpg, 0, status);
+            MB200_CHECK_LAUNCH("ssd state stream (tensor core, head pairs)");
+        }
+        const int64_t singles = (int64_t)a.batch * a.nheads - 2 * paired;
+        if (singles > 0) {
+            cudaFuncSetAttribute(ssd_tc_state_stream_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamCfg<1>::kSmem);
+            ssd_tc_state_stream_kernel<T, 1><<<(unsigned)singles, kStreamThreads, StreamCfg<1>::kSmem, stream>>>(
+                tx, tB, tHs, dtb, dAb, init, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1, nc, a.nheads, hpg,
+                (int)(2 * paired), status);
+        }
         MB200_CHECK_LAUNCH("ssd state stream (tensor core)");
         return MB200_OK;
     }
