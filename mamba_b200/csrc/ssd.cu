@@ -69,21 +69,22 @@ __global__ void __launch_bounds__(256) ssd_cumsum_kernel(const mb200_ssd_args a,
     const int Q = a.chunk_size;
     const int c = blockIdx.x, b = blockIdx.y, h0 = blockIdx.z * 32;
     const int t0 = c * Q;
-    // a thread keeps one head (lane) and walks the steps 8 at a time: the 8 loads are issued back to back so
+    // a thread keeps one head (lane) and walks the steps 32 at a time: the loads are issued back to back so
     // that their latencies overlap instead of adding up
     const int hh = threadIdx.x & 31, h = h0 + hh;
     const bool h_ok = h < a.nheads;
     const float bias = (h_ok && a.dt_bias) ? a.dt_bias[h] : 0.f;
     const TD *src = static_cast<const TD *>(a.dt) + (int64_t)b * a.dt_stride[0] + (int64_t)h * a.dt_stride[2];
-    for (int k0 = threadIdx.x >> 5; k0 < Q; k0 += 64) {
-        TD raw[8];
+    constexpr int NB = 32;          // loads in flight per thread: a whole chunk of 256 steps in one round trip
+    for (int k0 = threadIdx.x >> 5; k0 < Q; k0 += 8 * NB) {
+        TD raw[NB];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < NB; ++u) {
             const int k = k0 + 8 * u;
             raw[u] = (h_ok && k < Q && t0 + k < a.seqlen) ? src[(int64_t)(t0 + k) * a.dt_stride[1]] : from_float<TD>(0.f);
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < NB; ++u) {
             const int k = k0 + 8 * u;
             if (k < Q) {
                 float v = 0.f;
