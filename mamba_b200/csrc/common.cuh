@@ -118,6 +118,18 @@ __device__ __forceinline__ float fast_softplus20(float x)
     return fmaf(2.f * s, p, fmaxf(x, 0.f));
 }
 
+// softplus for 16-bit inputs and outputs: max(x, 0) + log2(1 + 2^(-|x| log2 e)) ln 2 with the two MUFU functions and
+// four FMA-pipe instructions.  Forming 1 + t costs up to 6e-8 absolute, i.e. a relative error of 6e-8 / softplus(x):
+// 2e-4 at x = -8, below 1e-5 from x = -5 up.  That is far inside what a 16-bit dt can express, but not good enough
+// for fp32 callers, who get fast_softplus20.  Above 20 the correction is below half an ulp, so the result equals x.
+__device__ __forceinline__ float softplus20_lowprec(float x)
+{
+    float l;
+    const float t = ex2(-fabsf(x) * kLog2e);
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(1.f + t));
+    return fmaf(l, 0.6931471805599453f, fmaxf(x, 0.f));
+}
+
 // silu(z) = h + h tanh(h), h = z/2, with the single-MUFU tanh.approx (relative error 2^-11).  For outputs
 // that are rounded to bfloat16 (8 significant bits) the approximation stays below the rounding step.
 __device__ __forceinline__ float tanh_approx(float x)

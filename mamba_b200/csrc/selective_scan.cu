@@ -679,12 +679,13 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
                 }
             }
             const int t0 = hb * kHB;
+            const bool tail = t0 + kHB > L;             // only the last hand-off can run past the end
             float dl[kHB], dlu[kHB], skip[kHB];
 #pragma unroll
             for (int i = 0; i < kHB; ++i) {
                 float v = words_get<T>(wd, i) + bias;
-                if (a.delta_softplus) v = fast_softplus20(v);
-                if (t0 + i >= L) v = 0.f;               // steps past the end are the identity (1, 0)
+                if (a.delta_softplus) v = sizeof(T) == 2 ? softplus20_lowprec(v) : fast_softplus20(v);
+                if (tail && t0 + i >= L) v = 0.f;       // steps past the end are the identity (1, 0)
                 const float uu = words_get<T>(wu, i);
                 dl[i] = v;
                 dlu[i] = v * uu;
