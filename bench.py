@@ -32,7 +32,7 @@ if ROOT not in sys.path:
 # dram bytes (read + write) per launch of the dominant kernel from the committed ncu capture
 # (profiles/), or None where no capture exists for that workload.
 NCU_TRAFFIC_BYTES = {
-    "c1": 656_877_312,      # scan_stream_kernel: 506.6 MB read + 150.3 MB written
+    "c1": 659_956_992,      # scan_stream_kernel: 509.0 MB read + 151.0 MB written
     "c2": 1_735_000_000,    # the SSD launches summed (state stream 368 + 154 MB, chunk_scan 881 + 310 MB)
     "c4": 1_291_591_424,    # ssu_packet_kernel: 676.8 MB read + 614.7 MB written
     "c0": None, "c3": None,
