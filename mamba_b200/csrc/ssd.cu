@@ -122,6 +122,9 @@ __global__ void __launch_bounds__(256) ssd_cumsum_kernel(const mb200_ssd_args a,
             carry = __shfl_sync(0xffffffffu, v, 31);
         }
     }
+    // When launched as the programmatic dependent of the C.B^T kernel this grid runs alongside it; it must not be
+    // complete before that kernel is, because later launches only wait for this one.  (Returns at once otherwise.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ---- stage 2 ------------------------------------------------------------------------------------
@@ -407,10 +410,27 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
             if (e == cudaSuccess) e = cudaFuncSetAttribute(ssd_cumsum_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
             if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd chunk_cumsum: shared memory opt-in: %s", cudaGetErrorString(e));
         }
-        const dim3 cs_grid(nc, a.batch, (a.nheads + 31) / 32);
-        if (a.dt_dtype == MB200_F32) ssd_cumsum_kernel<float><<<cs_grid, 256, cs_smem, stream>>>(a, dtb, dAb, nc);
-        else if (a.dt_dtype == MB200_BF16) ssd_cumsum_kernel<__nv_bfloat16><<<cs_grid, 256, cs_smem, stream>>>(a, dtb, dAb, nc);
-        else ssd_cumsum_kernel<__half><<<cs_grid, 256, cs_smem, stream>>>(a, dtb, dAb, nc);
+        // C.B^T needs nothing the other stages produce: when the whole operator runs on the tensor-core path it goes
+        // first and the cumsum is launched as its programmatic dependent, so the two small kernels share the GPU.
+        const bool cb_first = tc && (a.phases & MB200_SSD_PHASE_OUTPUT);
+        if (cb_first)
+            if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream, 1)) return rc;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(nc, a.batch, (a.nheads + 31) / 32);
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = cs_smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = cb_first ? 1 : 0;
+        int ncv = nc;
+        cudaError_t ce;
+        if (a.dt_dtype == MB200_F32) ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<float>, a, dtb, dAb, ncv);
+        else if (a.dt_dtype == MB200_BF16) ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<__nv_bfloat16>, a, dtb, dAb, ncv);
+        else ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<__half>, a, dtb, dAb, ncv);
+        if (ce != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd chunk_cumsum: %s", cudaGetErrorString(ce));
         MB200_CHECK_LAUNCH("ssd chunk_cumsum");
         if (fused_states) {
             if (int rc = ssd_tc_state_stream(a, lay, stream)) return rc;
@@ -456,7 +476,8 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         }
         MB200_CHECK_LAUNCH("ssd state_passing");
         if (tc) {
-            if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream)) return rc;
+            // C.B^T already ran ahead of the cumsum when this call includes the LOCAL phase
+            if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream, (a.phases & MB200_SSD_PHASE_LOCAL) ? 2 : 3)) return rc;
         } else {
             const int tq = (Q + 63) / 64;
             ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);

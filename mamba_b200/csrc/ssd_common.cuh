@@ -47,7 +47,8 @@ inline SsdScratch ssd_scratch_layout(const mb200_ssd_args &a)
 // Tensor-core stages (ssd_tc.cu): whether the call qualifies, and the two launch groups.
 bool ssd_tc_eligible(const mb200_ssd_args &a);
 int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
-int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool states_np, cudaStream_t stream);
+// parts: 1 = the C.B^T launch, 2 = the chunk-scan launch, 3 = both
+int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool states_np, cudaStream_t stream, int parts = 3);
 // Chunk states and inter-chunk recurrence fused (one CTA per batch row and head); leaves the 16-bit entering
 // states in [n][p] order, which ssd_tc_cb_and_scan is told through states_np.
 bool ssd_tc_stream_eligible(const mb200_ssd_args &a);

@@ -128,6 +128,9 @@ __global__ void __launch_bounds__(kThreadsTc) ssd_tc_cb_kernel(const __grid_cons
     const int g = blockIdx.x, c = blockIdx.y >> 1, mb = blockIdx.y & 1, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ncols = (mb + 1) * 128;
+    // a kernel launched after this one as its programmatic dependent (the cumsum, which shares no data with it) may
+    // start at once; it ends with griddepcontrol.wait, so it is not complete before this grid is
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 128) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
@@ -979,7 +982,7 @@ struct TcMaps {
 };
 
 template <typename T>
-int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np, cudaStream_t stream)
+int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np, cudaStream_t stream, int parts = 3)
 {
     char *base = static_cast<char *>(a.scratch);
     float *dtb = reinterpret_cast<float *>(base + lay.off_dt);
@@ -1080,12 +1083,16 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
             if (!encode_16bit(&tz, fmt, a.z, 4, d, sz, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for z failed");
         }
     }
-    cudaFuncSetAttribute(ssd_tc_cb_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cb);
-    ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
-    MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
-    cudaFuncSetAttribute(ssd_tc_chunk_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scan);
-    ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, h_np ? 1 : 0, status);
-    MB200_CHECK_LAUNCH("ssd chunk_scan (tensor core)");
+    if (parts & 1) {
+        cudaFuncSetAttribute(ssd_tc_cb_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cb);
+        ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
+        MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
+    }
+    if (parts & 2) {
+        cudaFuncSetAttribute(ssd_tc_chunk_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scan);
+        ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, h_np ? 1 : 0, status);
+        MB200_CHECK_LAUNCH("ssd chunk_scan (tensor core)");
+    }
     return MB200_OK;
 }
 
@@ -1108,9 +1115,10 @@ int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStrea
     return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 0, false, stream) : run_tc<__half>(a, lay, 0, false, stream);
 }
 
-int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool states_np, cudaStream_t stream)
+int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool states_np, cudaStream_t stream, int parts)
 {
-    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 1, states_np, stream) : run_tc<__half>(a, lay, 1, states_np, stream);
+    return a.io_dtype == MB200_BF16 ? run_tc<__nv_bfloat16>(a, lay, 1, states_np, stream, parts)
+                                    : run_tc<__half>(a, lay, 1, states_np, stream, parts);
 }
 
 // One (batch, head) per CTA: worth it once those fill at least half of the SMs.
