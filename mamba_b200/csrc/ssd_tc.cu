@@ -110,7 +110,6 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v)
 {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // ====================================================================================== C . B^T
 // grid (ngroups, nchunks * 2, batch); CTA = rows [mb*128, mb*128+128) of one chunk against B rows
@@ -534,11 +533,15 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 // a "block" = 64-wide slice of the mask product (CB tile [128 x 64] with the 64 rows of x it multiplies).
 //   C/H half 0 -> slot 0, C/H half 1 -> slot 1, block j -> slot (2 + j) % 3
 // Both C/H halves and block 0 are requested at once; a slot is re-used as soon as the MMAs that read it have
-// completed (block 1 after Y1's first half, block 2 after its second, block 3 after block 0).  The gate tile z
+// completed (block 1 after the first half of C.H^T, block 2 after its second, block 3 after block 0).  The gate tile z
 // lands in the tile part of a slot that is done with (slot 1 for the first row block, slot 0 for the second);
 // the output tile is assembled in the tile part of block 0's / block 2's slot and leaves through one TMA store.
 // The row block's own x rows (for D x) are the x parts of its last two blocks, which nothing overwrites.
-// Then scalars (dA*log2e and the column factors in fp32, dt in bf16) and barriers.  TMEM: 128 columns (Y1, Y2).
+// Then scalars (dA*log2e and the column factors in fp32, dt in bf16) and barriers.
+// The 16 KB tiles are never multiplied from shared memory: the element-wise threads read their 32 columns of a
+// row, apply their factors (exp(dA_m) for a C half, the decay mask for a CB tile) and write 16 packed words to
+// their lane of tensor memory; tcgen05.mma takes A from there and B (H half, x rows) from shared memory.
+// TMEM: 128 columns = one 64-column accumulator Y for all products + two 32-column A buffers used alternately.
 //
 // Decay mask.  A thread owns 32 consecutive columns k of one row m per block.  Three cases:
 //   all k > m           zeros
@@ -546,7 +549,9 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 //                       exponential per thread, the column factors are computed once per CTA.  Both exponents
 //                       are <= 0 because dA_cumsum is non-increasing (A <= 0, dt >= 0); a chunk where that does
 //                       not hold is detected and sent down the exact path.
-//   range holds k = m   exact: exp(min(dA_m - dA_k, 0)) dt_k [k <= m] per element
+//   range holds k = m   the same split with the columns past the diagonal zeroed while the range's decay span is
+//                       moderate (row factor >= 1, at most 2^kMaxDiagSpan); otherwise element by element:
+//                       exp(min(dA_m - dA_k, 0)) dt_k [k <= m]
 // The mask factors are rounded to the input dtype and applied with packed 16-bit multiplies (two roundings
 // per element instead of one; far inside the 16-bit tolerance, and it halves the instruction count).
 #ifndef MB200_SCAN_L2_PREFETCH
