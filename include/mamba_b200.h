@@ -214,6 +214,15 @@ int mb200_ssd_chunk_scan_fwd_static(const mb200_ssd_args *args, void *stream);
 int mb200_ssd_fold_state(const float *s_in, const float *range_decay, const float *s_local, float *s_out,
                          int64_t rows, int64_t row, int32_t device, void *stream);
 
+/*
+ * The same for a run of consecutive ranges in one launch (the all-gather hand-off: a rank folds the summaries of
+ * all its predecessors).  `summaries` holds one record per range, `record_stride` floats apart: rows*row floats of
+ * state followed by rows floats of decay.  Computes, in this order and with the arithmetic of
+ * mb200_ssd_fold_state,   s = state[first];  for r = first+1 .. last:  s = decay[r] * s + state[r];   s_out = s.
+ */
+int mb200_ssd_fold_ranges(const float *summaries, int64_t record_stride, int32_t first, int32_t last, float *s_out,
+                          int64_t rows, int64_t row, int32_t device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

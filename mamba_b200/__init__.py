@@ -12,6 +12,7 @@ from .ops import (  # noqa: F401
     selective_scan_fn,
     selective_state_update,
     ssd_finish,
+    ssd_fold_ranges,
     ssd_fold_state,
     ssd_local_states,
 )

@@ -74,6 +74,7 @@ _PROTOTYPES = {
     "mb200_ssd_chunk_scan_fwd": (ctypes.c_int, [ctypes.POINTER(SsdArgs), c_vp]),
     "mb200_ssd_chunk_scan_fwd_static": (ctypes.c_int, [ctypes.POINTER(SsdArgs), c_vp]),
     "mb200_ssd_fold_state": (ctypes.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_vp]),
+    "mb200_ssd_fold_ranges": (ctypes.c_int, [c_vp, c_i64, c_i32, c_i32, c_vp, c_i64, c_i64, c_i32, c_vp]),
 }
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)
 

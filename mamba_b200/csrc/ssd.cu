@@ -11,6 +11,8 @@
 // The contractions here run on the fp32 FMA pipes through a 64x64 shared-memory tile loop, which
 // keeps fp32 inputs exact; the bf16/fp16 tensor-core tiles for the benchmark shapes live in
 // ssd_tc.cu and replace stages 2, 4 and 5 when the shape qualifies.
+#include <algorithm>
+
 #include "ssd_common.cuh"
 
 namespace mb200 {
@@ -374,6 +376,20 @@ __global__ void ssd_fold_kernel(const float *s_in, const float *decay, const flo
     }
 }
 
+__global__ void ssd_fold_ranges_kernel(const float *summaries, int64_t record_stride, int first, int last, float *s_out, int64_t rows,
+                                       int64_t row)
+{
+    const int64_t total = rows * row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float s = summaries[(int64_t)first * record_stride + i];
+        for (int r = first + 1; r <= last; ++r) {
+            const float *rec = summaries + (int64_t)r * record_stride;
+            s = fmaf(rec[total + i / row], s, rec[i]);
+        }
+        s_out[i] = s;
+    }
+}
+
 template <typename T>
 int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
 {
@@ -596,5 +612,20 @@ extern "C" int mb200_ssd_fold_state(const float *s_in, const float *range_decay,
     const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
     ssd_fold_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(s_in, range_decay, s_local, s_out, rows, row);
     MB200_CHECK_LAUNCH("ssd_fold_state");
+    return MB200_OK;
+}
+
+extern "C" int mb200_ssd_fold_ranges(const float *summaries, int64_t record_stride, int32_t first, int32_t last, float *s_out,
+                                     int64_t rows, int64_t row, int32_t device, void *stream)
+{
+    using namespace mb200;
+    MB200_CHECK_ARG(summaries && s_out && rows >= 0 && row > 0 && first >= 0 && last >= first && record_stride >= rows * row + rows,
+                    "ssd_fold_ranges: bad argument");
+    if (rows == 0) return MB200_OK;
+    if (int rc = enter_device(device)) return rc;
+    const int64_t total = rows * row;
+    const int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 8);
+    ssd_fold_ranges_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(summaries, record_stride, first, last, s_out, rows, row);
+    MB200_CHECK_LAUNCH("ssd_fold_ranges");
     return MB200_OK;
 }

@@ -385,3 +385,17 @@ def ssd_fold_state(incoming_state, range_decay, range_state):
                                          L.ptr(out), rows, row, range_state.device.index,
                                          L.stream_ptr(range_state.device)))
     return out
+
+
+def ssd_fold_ranges(summaries, first, last, state_shape):
+    """Folds the range summaries ``first..last`` (rows of ``summaries``: a flattened state followed by its
+    (batch, nheads) decays, as the all-gather hand-off lays them out) into the state after range ``last``,
+    in one launch: ``s = state[first]; s = decay[r] * s + state[r]`` for r = first+1 .. last."""
+    L.require_cuda(summaries)
+    assert summaries.dim() == 2 and summaries.dtype == torch.float32 and summaries.stride(1) == 1
+    out = torch.empty(state_shape, device=summaries.device, dtype=torch.float32)
+    rows = int(state_shape[0]) * int(state_shape[1])
+    row = out.numel() // max(rows, 1)
+    L.check(L.lib().mb200_ssd_fold_ranges(L.ptr(summaries), summaries.stride(0), int(first), int(last), L.ptr(out), rows, row,
+                                          summaries.device.index, L.stream_ptr(summaries.device)))
+    return out

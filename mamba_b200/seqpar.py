@@ -39,10 +39,12 @@ class SequenceHandoffError(RuntimeError):
 
 @dataclass
 class SsdSteps:
-    """The three compute steps of a rank; defaults are the CUDA operators of this package."""
+    """The compute steps of a rank; defaults are the CUDA operators of this package.  ``fold_ranges`` (optional)
+    folds several gathered summaries in one call; without it ``fold`` is applied range by range."""
     local: Callable = ops.ssd_local_states
     fold: Callable = ops.ssd_fold_state
     finish: Callable = ops.ssd_finish
+    fold_ranges: Optional[Callable] = ops.ssd_fold_ranges
 
 
 def split_sequence(seqlen: int, chunk_size: int, world: int, rank: int):
@@ -85,7 +87,7 @@ def _gather_summaries(state: torch.Tensor, decay: torch.Tensor, group):
         raise SequenceHandoffError(f"rank {dist.get_rank(group)}: gathering the range summaries failed: {e}") from e
     states = [everyone[r, :ns].view(state.shape) for r in range(world)]          # views, nothing is copied
     decays = [everyone[r, ns:].view(decay.shape).to(decay.dtype) for r in range(world)]
-    return states, decays
+    return states, decays, everyone
 
 
 def mamba_chunk_scan_sequence_parallel(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
@@ -117,10 +119,14 @@ def mamba_chunk_scan_sequence_parallel(x, dt, A, B, C, chunk_size, D=None, z=Non
             _send_state(steps.fold(incoming, range_decay, range_state), rank + 1, group)
     else:
         mine = steps.fold(first, range_decay, range_state) if rank == 0 else range_state
-        states, decays = _gather_summaries(mine, range_decay, group)
+        states, decays, everyone = _gather_summaries(mine, range_decay, group)
         incoming = first
-        if rank > 0:
+        if rank == 1:
             incoming = states[0]                       # the state rank 0 hands on
+        elif rank > 1 and steps.fold_ranges is not None and everyone.is_cuda and everyone.dtype == torch.float32:
+            incoming = steps.fold_ranges(everyone, 0, rank - 1, tuple(range_state.shape))    # one launch
+        elif rank > 1:
+            incoming = states[0]
             for r in range(1, rank):
                 incoming = steps.fold(incoming, decays[r], states[r])
     return steps.finish(x, dt, A, B, C, chunk_size, scratch, D=D, z=z, dt_bias=dt_bias, incoming_state=incoming,

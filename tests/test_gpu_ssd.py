@@ -344,3 +344,19 @@ def test_bench_config3_full_size_properties():
         outs.append(o)
     assert_close(torch.cat(outs, dim=1), out.float(), TOL_BF16, "split out")
     assert_close(f2, fin, TOL_BF16, "split final_states")
+
+
+def test_fold_ranges_equals_range_by_range_folds():
+    """One launch over several gathered summaries gives the bits of folding them one at a time."""
+    from mamba_b200 import ssd_fold_ranges, ssd_fold_state
+    g = torch.Generator().manual_seed(5)
+    world, b, h, p, n = 5, 2, 3, 8, 16
+    states = torch.randn(world, b, h, p, n, generator=g)
+    decays = torch.rand(world, b, h, generator=g)
+    rec = torch.cat([states.reshape(world, -1), decays.reshape(world, -1)], dim=1).to(DEV)
+    for last in (0, 1, 4):
+        want = states[0].to(DEV)
+        for r in range(1, last + 1):
+            want = ssd_fold_state(want, decays[r].to(DEV), states[r].to(DEV))
+        got = ssd_fold_ranges(rec, 0, last, (b, h, p, n))
+        assert torch.equal(got, want)
