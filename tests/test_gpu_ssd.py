@@ -127,6 +127,25 @@ def test_fused_state_stream_options():
     assert_close(fin, wfin, TOL_BF16, "fused options final")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_tensor_core_steep_decay(dtype):
+    """dt*|A| of several units per step: the decay over a 32-step range exceeds what the factorised mask may
+    span, so the element-by-element mask path of the tensor-core chunk scan runs (and rows far apart decay to 0)."""
+    inp = make(181, 2, 512, 4, 64, 1, 128, dtype, has_z=True)
+    g = torch.Generator().manual_seed(182)
+    inp["dt"] = (0.3 + 0.7 * torch.rand(2, 512, 4, generator=g)).to(dtype)
+    inp["A"] = -(8 + 8 * torch.rand(4, generator=g))
+    inp["dt_bias"] = None
+    f = lambda t: None if t is None else t.float()
+    want, wfin = oracle.ssd_chunk_scan(f(inp["x"]), f(inp["dt"]), inp["A"], f(inp["B"]), f(inp["C"]), 256, inp["D"], f(inp["z"]), None,
+                                       None, dt_softplus=False)
+    c = {k: _c(v) for k, v in inp.items()}
+    got, fin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], 256, D=c["D"], z=c["z"], return_final_states=True)
+    assert _status() == 0
+    assert_close(got, want, TOL_BF16, "steep out")
+    assert_close(fin, wfin, TOL_BF16, "steep final")
+
+
 def test_dt_limit_and_no_softplus():
     inp = make(11, 1, 128, 2, 16, 1, 16, torch.float32)
     inp["dt"] = inp["dt"].abs() * 0.1
