@@ -130,7 +130,7 @@ int mb200_selective_state_update(const mb200_ssu_args *args, void *stream);
  * D : (nheads) fp32, or (nheads, headdim) fp32 contiguous when D_has_hdim.
  * seq_idx : optional int32 (batch, seqlen) contiguous, non-decreasing sequence ids starting at 0 for packed
  *   sequences: positions with different ids do not interact (ssd_chunk_state.py:246-251, ssd_state_passing.py:76-79,
- *   ssd_bmm.py:84-88, ssd_chunk_scan.py:97-113).  Calls with seq_idx or cu_seqlens run the general stage kernels.
+ *   ssd_bmm.py:84-88, ssd_chunk_scan.py:97-113).
  * cu_seqlens / num_seqs / varlen_states : optional (batch must be 1): int32 (num_seqs + 1) cumulative sequence
  *   lengths and an fp32 (num_seqs, nheads, headdim, dstate) output receiving the state after the last token of
  *   every packed sequence (chunk_state_varlen, ssd_chunk_state.py:1018-1044, kernel :639-715).
@@ -203,6 +203,12 @@ int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream);
  */
 #define MB200_SSD_STATIC_SCRATCH_BYTES (32u << 20)
 int mb200_ssd_chunk_scan_fwd_static(const mb200_ssd_args *args, void *stream);
+
+/* Diagnostic for the call above, no counterpart in the reference: copies the status word that the last
+ * mb200_ssd_chunk_scan_fwd_static call with these sizes left in the built-in buffer to *status (0 = every kernel ran
+ * to completion).  Synchronises with the device; for tests and post-mortems, not for the hot path.  Callers of
+ * mb200_ssd_chunk_scan_fwd read the word from their own scratch buffer (its last 256 bytes) instead. */
+int mb200_ssd_static_status(const mb200_ssd_args *args, int *status);
 
 /*
  * Folds an incoming state through a device's local range when a sequence is split across devices:

@@ -73,6 +73,7 @@ _PROTOTYPES = {
     "mb200_ssd_scratch_bytes": (ctypes.c_int, [ctypes.POINTER(SsdArgs), ctypes.POINTER(ctypes.c_size_t)]),
     "mb200_ssd_chunk_scan_fwd": (ctypes.c_int, [ctypes.POINTER(SsdArgs), c_vp]),
     "mb200_ssd_chunk_scan_fwd_static": (ctypes.c_int, [ctypes.POINTER(SsdArgs), c_vp]),
+    "mb200_ssd_static_status": (ctypes.c_int, [ctypes.POINTER(SsdArgs), ctypes.POINTER(c_i32)]),
     "mb200_ssd_fold_state": (ctypes.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_vp]),
     "mb200_ssd_fold_ranges": (ctypes.c_int, [c_vp, c_i64, c_i32, c_i32, c_vp, c_i64, c_i64, c_i32, c_vp]),
 }

@@ -38,10 +38,18 @@ class _SelectiveScanCuda:
         n_chunks = (seqlen + _CHUNK - 1) // _CHUNK
         x = torch.zeros(batch, dim, n_chunks, 2 * dstate, device=u.device, dtype=torch.float32)
         last = torch.empty(batch, dim, dstate, device=u.device, dtype=torch.float32)
+        # converted copies are bound to names so that they outlive the launch, and their own strides are passed
+        A = A.float()
+        D32 = None if D_ is None else D_.float().contiguous()
+        bias32 = None if delta_bias_ is None else delta_bias_.float().contiguous()
+        if not B_var:
+            B = B.float()
+        if not C_var:
+            C = C.float()
         a = L.ScanArgs()
-        a.u, a.delta, a.A, a.B, a.C = L.ptr(u), L.ptr(delta), L.ptr(A.float()), L.ptr(B), L.ptr(C)
-        a.D = L.ptr(None if D_ is None else D_.float().contiguous())
-        a.delta_bias = L.ptr(None if delta_bias_ is None else delta_bias_.float().contiguous())
+        a.u, a.delta, a.A, a.B, a.C = L.ptr(u), L.ptr(delta), L.ptr(A), L.ptr(B), L.ptr(C)
+        a.D = L.ptr(D32)
+        a.delta_bias = L.ptr(bias32)
         a.z = L.ptr(z_)
         # with a gate the extension returns the ungated result as `out` and the gated one as `out_z`
         a.out, a.out_pregate = (L.ptr(out_z), L.ptr(out)) if z_ is not None else (L.ptr(out), None)

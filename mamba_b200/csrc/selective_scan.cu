@@ -299,19 +299,12 @@ scan_fwd_kernel(const mb200_scan_args a, const int cpw, const int nblocks, const
 // the block's steps and write them to the other buffer afterwards, so one CTA barrier per block
 // suffices.
 constexpr int kSeqBytes = 32;   // bytes of one u row a lane moves per block (two 16-byte packets)
-#ifndef MB200_SEQ_AHEAD
-#define MB200_SEQ_AHEAD 2
-#endif
-constexpr int kSeqAhead = MB200_SEQ_AHEAD;   // how many blocks ahead the L1 prefetch runs
-#ifndef MB200_QUAD_WARPS
-#define MB200_QUAD_WARPS 4
-#endif
+constexpr int kSeqAhead = 2;    // how many blocks ahead the L1 prefetch runs
+constexpr int kQuadWarps = 4;   // warps per CTA of the four-lanes-per-channel kernel
 // CTAs per SM the register allocation must allow: the 1280 four-warp CTAs of the 2.8B-layer shape must
 // all be resident at once (8.65 per SM); 9 per SM means 56 registers per lane.  With 64 registers only 8
 // fit, the last 96 CTAs form a second wave and the step takes 0.84 ms instead of 0.69 ms.
-#ifndef MB200_QUAD_MINB
-#define MB200_QUAD_MINB 9
-#endif
+constexpr int kQuadMinBlocks = 9;
 
 template <typename T>
 __device__ __forceinline__ void seq_prefetch(const T *row, int t0, int L)
@@ -373,7 +366,7 @@ __device__ __forceinline__ void lds_pairs(const float *p, uint64_t (&v)[HS / 2])
 }
 
 template <typename T, int NS, int W>
-__global__ void __launch_bounds__(32 * W, MB200_QUAD_MINB) scan_quad_kernel(const mb200_scan_args a, const int vec_flags)
+__global__ void __launch_bounds__(32 * W, kQuadMinBlocks) scan_quad_kernel(const mb200_scan_args a, const int vec_flags)
 {
     constexpr int LPC = 4;                             // lanes per channel
     constexpr int TB = kSeqBytes / sizeof(T);          // steps per block: 16 (16-bit) or 8 (fp32)
@@ -556,9 +549,6 @@ __global__ void __launch_bounds__(32 * W, MB200_QUAD_MINB) scan_quad_kernel(cons
 // (state -> scalar, 8 steps of partial outputs in place), all buffers double.  The scalar warp runs
 // one hand-off ahead, and the TMA tiles two tiles ahead, of the recurrence.  Every wait is bounded;
 // on expiry the kernel records a code in g_scan_status, stops, and drains its outstanding copies.
-#ifndef MB200_SCAN_STREAM
-#define MB200_SCAN_STREAM 1
-#endif
 __device__ int g_scan_status;
 enum { kStScanFull = 31, kStScanZ, kStScanReady, kStScanYdone, kStScanAlign };
 
@@ -930,19 +920,17 @@ int launch_scan(const mb200_scan_args &a, cudaStream_t stream)
         bc_vec = bc_vec && (reinterpret_cast<uintptr_t>(a.C) % bc_align == 0) && a.C_stride[0] % 4 == 0 &&
                  a.C_stride[1] % 4 == 0 && a.C_stride[2] % 4 == 0;
     const int vec_flags = (io_vec ? 1 : 0) | (bc_vec ? 2 : 0);
-#if MB200_SCAN_STREAM
     if (stream_eligible<T>(a)) {
         const int rc = launch_stream<T>(a, stream);
         if (rc <= 0) return rc;
     }
-#endif
     // Enough independent channels to give every SM a few warps: four lanes per channel, time sequential.
     if (N <= 16 && a.B_variable && a.C_variable && (int64_t)a.batch * a.dim >= 2LL * 32 * 148) {
         // the B/C tile is fetched in 16-byte packets here
         const bool bc16 = bc_vec && aligned16(a.B) && aligned16(a.C) && a.B_stride[0] % VEC == 0 && a.B_stride[1] % VEC == 0 &&
                           a.B_stride[2] % VEC == 0 && a.C_stride[0] % VEC == 0 && a.C_stride[1] % VEC == 0 && a.C_stride[2] % VEC == 0;
         const int flags = (io_vec ? 1 : 0) | (bc16 ? 2 : 0);
-        constexpr int QW = MB200_QUAD_WARPS;
+        constexpr int QW = kQuadWarps;
         dim3 grid(a.ngroups * ((per_group + 8 * QW - 1) / (8 * QW)), a.batch);
         if (N <= 8) scan_quad_kernel<T, 8, QW><<<grid, 32 * QW, 0, stream>>>(a, flags);
         else scan_quad_kernel<T, 16, QW><<<grid, 32 * QW, 0, stream>>>(a, flags);

@@ -366,6 +366,12 @@ __global__ void __launch_bounds__(256) ssd_varlen_state_kernel(const mb200_ssd_a
     *dst = acc;
 }
 
+__global__ void ssd_fill_kernel(float *dst, float v, int64_t n)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = v;
+}
+
 __global__ void ssd_fold_kernel(const float *s_in, const float *decay, const float *s_local, float *s_out, int64_t rows,
                                 int64_t row)
 {
@@ -400,8 +406,14 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     float *cb = reinterpret_cast<float *>(base + lay.off_cb);
     const int nc = lay.nchunks, Q = a.chunk_size;
     const int64_t PN = (int64_t)a.headdim * a.dstate;
-    const bool tc = ssd_tc_eligible(a);
-    void *prev16 = tc ? static_cast<void *>(base + lay.off_prev16) : nullptr;
+    // Path choice.  The LOCAL stages (cumsum, chunk states, recurrence) read x, B and dt; the OUTPUT stages add C,
+    // z and out.  A whole-operator call takes the tensor-core path only when both halves can; in a sequence split
+    // each half decides from what IT reads, so an OUTPUT call can tell how the earlier LOCAL call ran even though
+    // that call never saw C, z or out.
+    const bool has_local = (a.phases & MB200_SSD_PHASE_LOCAL) != 0, has_out = (a.phases & MB200_SSD_PHASE_OUTPUT) != 0;
+    const bool tc_out = ssd_tc_local_eligible(a) && ssd_tc_output_eligible(a);     // OUTPUT stages on tensor cores
+    const bool tc_loc = (has_local && has_out) ? tc_out : ssd_tc_local_eligible(a);  // LOCAL stages on tensor cores
+    void *prev16 = tc_out ? static_cast<void *>(base + lay.off_prev16) : nullptr;
     {
         cudaError_t e = cudaMemsetAsync(base + lay.off_status, 0, sizeof(int), stream);
         if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: status reset: %s", cudaGetErrorString(e));
@@ -409,15 +421,10 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     // Chunk states + inter-chunk recurrence in one streaming launch.  In a sequence split the LOCAL phase runs it
     // from a zero state (entering states of the range as if nothing came in, range summary), and the OUTPUT phase
     // adds the incoming state's share to those entering states: H_c += prefix_decay_c * S_in.
-    const bool fused_states = tc && ssd_tc_stream_eligible(a);
-    // The LOCAL phase of this problem took the streaming launch (it does not see out / z): then the scratch holds
-    // no chunk states, and an OUTPUT phase that cannot stream has to form them itself.
-    bool local_streamed = false;
-    if (!(a.phases & MB200_SSD_PHASE_LOCAL) && !fused_states) {
-        mb200_ssd_args l = a;
-        l.phases = MB200_SSD_PHASE_LOCAL;
-        local_streamed = ssd_tc_eligible(l) && ssd_tc_stream_eligible(l);
-    }
+    const bool fused_states = tc_loc && ssd_tc_stream_eligible(a);
+    // The LOCAL half took the streaming launch but this OUTPUT half cannot use its 16-bit entering states: the
+    // scratch holds no fp32 chunk states, so they are formed here before the recurrence.
+    const bool local_streamed = !has_local && fused_states && !tc_out;
     if (a.phases & MB200_SSD_PHASE_LOCAL) {
         const size_t cs_smem = sizeof(float) * Q * 33;
         if (cs_smem > 48 * 1024) {
@@ -428,7 +435,7 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         }
         // C.B^T needs nothing the other stages produce: when the whole operator runs on the tensor-core path it goes
         // first and the cumsum is launched as its programmatic dependent, so the two small kernels share the GPU.
-        const bool cb_first = tc && (a.phases & MB200_SSD_PHASE_OUTPUT);
+        const bool cb_first = tc_out && has_out;
         if (cb_first)
             if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream, 1)) return rc;
         cudaLaunchConfig_t cfg = {};
@@ -450,7 +457,7 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         MB200_CHECK_LAUNCH("ssd chunk_cumsum");
         if (fused_states) {
             if (int rc = ssd_tc_state_stream(a, lay, stream)) return rc;
-        } else if (tc) {
+        } else if (tc_loc) {
             if (int rc = ssd_tc_chunk_state(a, lay, stream)) return rc;
         } else {
             ssd_chunk_state_kernel<T><<<dim3(((a.headdim + 63) / 64) * ((a.dstate + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(
@@ -471,16 +478,9 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     if (a.phases & MB200_SSD_PHASE_OUTPUT) {
         mb200_ssd_args p = a;
         if (!(a.phases & MB200_SSD_PHASE_LOCAL)) p.range_decay = nullptr;
-        if (local_streamed) {
-            if (tc) {
-                if (int rc = ssd_tc_chunk_state(a, lay, stream)) return rc;
-            } else {
-                ssd_chunk_state_kernel<T><<<dim3(((a.headdim + 63) / 64) * ((a.dstate + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(
-                    a, dtb, dAb, states, nc);
-                MB200_CHECK_LAUNCH("ssd chunk_state");
-            }
-        }
-        if (fused_states) {
+        if (local_streamed)      // x and B qualified for the tensor-core chunk-state kernel (that is why LOCAL streamed)
+            if (int rc = ssd_tc_chunk_state(a, lay, stream)) return rc;
+        if (fused_states && tc_out) {
             // the entering states and the final state come from the state-stream kernel; in the OUTPUT half of a
             // sequence split the incoming state is added to what the LOCAL half left
             if (!(a.phases & MB200_SSD_PHASE_LOCAL))
@@ -491,9 +491,9 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
             ssd_state_passing_kernel<1><<<dim3((unsigned)((PN + 255) / 256), a.nheads, a.batch), 256, 0, stream>>>(p, dAb, states, nc, true, prev16);
         }
         MB200_CHECK_LAUNCH("ssd state_passing");
-        if (tc) {
+        if (tc_out) {
             // C.B^T already ran ahead of the cumsum when this call includes the LOCAL phase
-            if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream, (a.phases & MB200_SSD_PHASE_LOCAL) ? 2 : 3)) return rc;
+            if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream, has_local ? 2 : 3)) return rc;
         } else {
             const int tq = (Q + 63) / 64;
             ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);
@@ -546,17 +546,28 @@ extern "C" int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream
     MB200_CHECK_ARG(!a.cu_seqlens || (a.num_seqs >= 0 && a.num_seqs <= 65535), "ssd: num_seqs must be in [0, 65535]");
     MB200_CHECK_ARG(!(a.seq_idx || a.cu_seqlens) || a.phases == MB200_SSD_PHASE_ALL, "ssd: packed sequences cannot be combined with a sequence split");
     if (a.batch == 0) return MB200_OK;   // nothing to do; empty tensors carry NULL pointers
-    MB200_CHECK_ARG(a.x && a.dt && a.A && a.B && a.C, "ssd: a required tensor is NULL");
+    MB200_CHECK_ARG(a.seqlen == 0 || (a.x && a.dt && a.A && a.B && a.C), "ssd: a required tensor is NULL");
     if (int rc = enter_device(a.device)) return rc;
     MB200_CHECK_ARG(a.batch * (int64_t)((a.seqlen + a.chunk_size - 1) / a.chunk_size) <= 65535 && a.nheads <= 65535 && a.batch <= 65535,
                     "ssd: batch*nchunks and nheads must be <= 65535");
     const SsdScratch lay = ssd_scratch_layout(a);
     if (a.seqlen == 0) {
+        const size_t n = sizeof(float) * (size_t)a.batch * a.nheads * a.headdim * a.dstate;
         if (a.final_states && (a.phases & MB200_SSD_PHASE_OUTPUT)) {
-            const size_t n = sizeof(float) * (size_t)a.batch * a.nheads * a.headdim * a.dstate;
             cudaError_t e = a.initial_states ? cudaMemcpyAsync(a.final_states, a.initial_states, n, cudaMemcpyDeviceToDevice, stream)
                                              : cudaMemsetAsync(a.final_states, 0, n, stream);
             if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: final state copy: %s", cudaGetErrorString(e));
+        } else if (a.phases == MB200_SSD_PHASE_LOCAL) {
+            // an empty range of a sequence split is summarised by the identity: state 0, decay 1
+            if (a.final_states) {
+                const cudaError_t e = cudaMemsetAsync(a.final_states, 0, n, stream);
+                if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: empty range state: %s", cudaGetErrorString(e));
+            }
+            if (a.range_decay) {
+                const int64_t rows = (int64_t)a.batch * a.nheads;
+                ssd_fill_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, stream>>>(a.range_decay, 1.f, rows);
+                MB200_CHECK_LAUNCH("ssd: empty range decay");
+            }
         }
         return MB200_OK;
     }
@@ -599,6 +610,20 @@ extern "C" int mb200_ssd_chunk_scan_fwd_static(const mb200_ssd_args *args, void 
     a.scratch = ptr;
     a.scratch_bytes = MB200_SSD_STATIC_SCRATCH_BYTES;
     return mb200_ssd_chunk_scan_fwd(&a, stream);
+}
+
+extern "C" int mb200_ssd_static_status(const mb200_ssd_args *args, int *status)
+{
+    using namespace mb200;
+    if (!args || !status) return fail(MB200_ERR_BAD_ARG, "ssd_static_status: NULL argument");
+    if (int rc = check_ssd(*args)) return rc;
+    const SsdScratch lay = ssd_scratch_layout(*args);
+    if (lay.total > MB200_SSD_STATIC_SCRATCH_BYTES) return fail(MB200_ERR_BAD_ARG, "ssd_static_status: this problem does not fit the built-in buffer");
+    if (int rc = enter_device(args->device)) return rc;
+    // synchronises with the device: a diagnostic, not part of the hot path
+    const cudaError_t e = cudaMemcpyFromSymbol(status, g_ssd_static_scratch, sizeof(int), lay.off_status);
+    if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd_static_status: %s", cudaGetErrorString(e));
+    return MB200_OK;
 }
 
 extern "C" int mb200_ssd_fold_state(const float *s_in, const float *range_decay, const float *s_local, float *s_out,

@@ -44,8 +44,11 @@ inline SsdScratch ssd_scratch_layout(const mb200_ssd_args &a)
     return s;
 }
 
-// Tensor-core stages (ssd_tc.cu): whether the call qualifies, and the two launch groups.
-bool ssd_tc_eligible(const mb200_ssd_args &a);
+// Tensor-core stages (ssd_tc.cu): whether the call qualifies, and the two launch groups.  The LOCAL stages read
+// x, B and dt only; the OUTPUT stages add C, z and out.  Each predicate looks at nothing else, so the two halves
+// of a sequence split agree on how the LOCAL half ran although they are handed different C / z / out.
+bool ssd_tc_local_eligible(const mb200_ssd_args &a);
+bool ssd_tc_output_eligible(const mb200_ssd_args &a);
 int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
 // parts: 1 = the C.B^T launch, 2 = the chunk-scan launch, 3 = both
 int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool states_np, cudaStream_t stream, int parts = 3);

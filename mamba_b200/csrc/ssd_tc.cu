@@ -34,12 +34,6 @@ static bool encode_16bit(CUtensorMap *map, int fmt, const void *base, int rank, 
     return encode_tiled(map, fmt == 1 ? MB200_BF16 : MB200_F16, base, rank, dims, strides_bytes, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-#ifdef MB200_SCAN_TRACE
-// Experiment aid: nanosecond stamps of the producer lane (slots 0-7) and of compute thread 0 (slots 8-15)
-// for the first 4096 CTAs of the chunk-scan kernel, read back by the experiment harness.
-__device__ unsigned long long g_scan_trace[4096 * 16];
-#endif
-
 namespace {
 
 using namespace tc;
@@ -293,9 +287,7 @@ __global__ void __launch_bounds__(kStateThreads) ssd_tc_chunk_state_kernel(const
 // 16 KB state tile per head; TMEM: two accumulators of 64 columns per head, so the MMAs of chunk c overlap the fold
 // of chunk c-1.  A CTA serves one head or two heads of one group (template parameter HEADS): with two, the B tile
 // is fetched and read by the tensor core once for both (N = 128).
-#ifndef MB200_SSD_STREAM_MIN_UNITS
-#define MB200_SSD_STREAM_MIN_UNITS 74
-#endif
+constexpr int kStreamMinUnits = 74;                    // (batch, head) units from which one CTA per unit pays: half the SMs
 constexpr int kStreamWarps = 16;                       // element-wise warps
 constexpr int kStreamThreads = (kStreamWarps + 2) * 32;
 // HEADS heads of one group per CTA share the B tile: one stage is half a chunk of B (2 x 16 KB) and of every head's
@@ -554,23 +546,11 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
 //                       exp(min(dA_m - dA_k, 0)) dt_k [k <= m]
 // The mask factors are rounded to the input dtype and applied with packed 16-bit multiplies (two roundings
 // per element instead of one; far inside the 16-bit tolerance, and it halves the instruction count).
-#ifndef MB200_SCAN_L2_PREFETCH
-#define MB200_SCAN_L2_PREFETCH 1
-#endif
 // Largest decay span (in powers of two) of a 32-column range for which the diagonal range may use the factorised
 // mask: the row factor 2^span and the smallest column factor 2^-span * dt stay far inside the fp32 range.
 constexpr float kMaxDiagSpan = 80.f;
 constexpr int kScanThreads = 288;
 constexpr uint32_t kScanSmem = 49152 + 24576 + 1024 + 1024 + 512 + 64 + 128 + 16;   // 76496 B, base must be 1 KB aligned
-#ifdef MB200_SCAN_TRACE
-#define MB200_TRACE(slot)                                                                                         \
-    do {                                                                                                          \
-        const unsigned cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                     \
-        if (cta_ < 4096) g_scan_trace[cta_ * 16 + (slot)] = global_ns();                                          \
-    } while (0)
-#else
-#define MB200_TRACE(slot) do { } while (0)
-#endif
 __device__ __forceinline__ void scan_compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <typename T>
@@ -642,7 +622,6 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     if (warp == 8) {
         if (lane == 0) {
             bool ok = (smem_u32(sm) & 1023u) == 0;
-            MB200_TRACE(0);
             auto load_block = [&](int j) {
                 mbar_expect_tx(&bar_full[j], 16384 + 8192);
                 tma_load_3d(slot_ptr(j), &tm_CB, &bar_full[j], j * 64, mb * 128, (int)unit_g);
@@ -676,17 +655,14 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 load_block(0);
                 load_ch(0);
                 load_ch(1);
-#if MB200_SCAN_L2_PREFETCH
                 // the later x rows and the gate tile cannot be requested yet: have them brought into L2 now
                 for (int j = 1; j < nk; ++j) tma_prefetch_l2_4d(&tm_x, 0, h, c * kQ + j * 64, b);
                 if (a.z) tma_prefetch_l2_4d(&tm_z, 0, h, c * kQ + mb * 128, b);
-#endif
             }
             // Y = (exp(dA_m) C) . H^T in two K halves; the row-scaled C half comes from tensor memory
             const uint32_t idesc1 = instr_desc_f16(128, 64, Fmt<T>::v, 0, h_np ? 1 : 0);
             for (int kb = 0; kb < 2; ++kb) {
                 ok = ok && mbar_wait(&bar_chscaled[kb], 0, status, kStBarC);
-                if (kb == 0) MB200_TRACE(1);
                 if (ok) {
                     tc_fence_after_sync();
                     const uint32_t hb_ = smem_u32(sm + kb * kSlot) + kSlotX;
@@ -704,9 +680,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 if (nk > 2) load_block(2);               // slot 1
                 else if (a.z) load_z();
             }
-            MB200_TRACE(2);
             gemm2_block(0);
-            MB200_TRACE(3);
             if (nk > 2) {
                 mma_commit(&bar_e[0]);
                 ok = ok && mbar_wait(&bar_e[0], 0, status, kStBarEmpty);    // slot 2 has been read
@@ -723,10 +697,8 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 gemm2_block(3);
             }
             mma_commit(bar_g2);
-            MB200_TRACE(4);
         }
     } else {
-        if (threadIdx.x == 0) MB200_TRACE(8);
         const int r = threadIdx.x & 127;    // row inside the block = TMEM lane
         const int kh = threadIdx.x >> 7;    // which 32-column half of every 64-wide block
         const int m = mb * 128 + r;         // row inside the chunk
@@ -741,7 +713,6 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         const bool live = t < a.seqlen;     // rows past the end of the sequence compute garbage that the tile store clips
         const float Dh = (a.D && !a.D_has_hdim) ? a.D[h] : 0.f;
         scan_compute_sync();
-        if (threadIdx.x == 0) MB200_TRACE(9);
         const float dAm = dA2[m];
         const bool factor_ok = *mono != 0;
         bool ok = (smem_u32(sm) & 1023u) == 0;
@@ -780,7 +751,6 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             // the tile buffer this block goes to was last read by the product two ring items earlier
             ok = ok && mbar_wait(j < 2 ? &bar_chdone[j] : &bar_e[j - 2], 0, status, kStBarEmpty);
             ok = __all_sync(0xffffffffu, ok);       // tcgen05.st is warp-collective
-            if (threadIdx.x == 0 && j == 0) MB200_TRACE(10);
             const uint32_t rowaddr = smem_u32(slot_ptr(j)) + r * 128;
             if (ok) {
                 tc_fence_after_sync();
@@ -846,22 +816,22 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         }
                     }
                 }
+                // tcgen05.st is warp-collective (.sync.aligned): it must stay here, after the per-lane mask branches
+                // above have reconverged -- the lanes of a warp that holds the diagonal take different branches
+                __syncwarp();
                 tmem_st16(tlane + 64 + (j & 1) * 32 + kh * 16, w);
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0 && ok) mbar_arrive(&bar_scaled[j]);
         }
-        if (threadIdx.x == 0) MB200_TRACE(11);
         ok = ok && mbar_wait(bar_g2, 0, status, kStBarG2);
-        if (threadIdx.x == 0) MB200_TRACE(12);
         if (a.z) ok = ok && mbar_wait(bar_z, 0, status, kStBarX);
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-collective: the whole warp takes one path
         tc_fence_after_sync();
         if (ok) {
             float acc[32];
             tmem_ld32(tlane + kh * 32, acc);
-            if (threadIdx.x == 0) MB200_TRACE(14);
             // row m of x sits in the x part of the slot that carried block m / 64
             const uint32_t xrow = smem_u32(slot_ptr(m >> 6) + kSlotX) + (m & 63) * 128;
 #pragma unroll
@@ -913,7 +883,6 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             tma_store_commit_and_wait_read();
         }
     }
-    if (threadIdx.x == 0) MB200_TRACE(13);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 8) tmem_dealloc(tmem, 128);
@@ -1012,7 +981,8 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         const uint64_t sC[3] = {(uint64_t)a.C_stride[2] * 2, (uint64_t)a.C_stride[1] * 2, (uint64_t)a.C_stride[0] * 2};
         const uint32_t bx256[4] = {64, 1, 256, 1}, bx128[4] = {64, 1, 128, 1};
         if (!encode_16bit(&tB, fmt, a.B, 4, d, sB, stage == 0 ? bx256 : bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for B failed");
-        if (!encode_16bit(&tC, fmt, a.C, 4, d, sC, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for C failed");
+        // only the C.B^T and chunk-scan launches read C (the LOCAL half of a sequence split may not even be given one)
+        if (stage == 1 && !encode_16bit(&tC, fmt, a.C, 4, d, sC, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for C failed");
     }
     const size_t smem_state = 98304 + 256 + 1024, smem_cb = 98304 + 256 + 1024, smem_scan = kScanSmem;
     if (stage == 2) {
@@ -1103,16 +1073,21 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
 
 }  // namespace
 
-bool ssd_tc_eligible(const mb200_ssd_args &a)
+bool ssd_tc_local_eligible(const mb200_ssd_args &a)
 {
     if (a.io_dtype != MB200_BF16 && a.io_dtype != MB200_F16) return false;
     if (a.headdim != kP || a.dstate != kN || a.chunk_size != kQ || a.seq_idx || a.cu_seqlens) return false;
-    if (!aligned16(a.x) || !aligned16(a.B) || !aligned16(a.C)) return false;
-    if (!mult8(a.x_stride, 3) || !mult8(a.B_stride, 3) || !mult8(a.C_stride, 3)) return false;
-    if ((a.phases & MB200_SSD_PHASE_OUTPUT) && (!aligned16(a.out) || !mult8(a.out_stride, 3))) return false;
-    if (a.z && (!aligned16(a.z) || !mult8(a.z_stride, 3))) return false;
+    if (!aligned16(a.x) || !aligned16(a.B) || !mult8(a.x_stride, 3) || !mult8(a.B_stride, 3)) return false;
     if ((int64_t)a.batch * ((a.seqlen + kQ - 1) / kQ) * a.nheads > INT32_MAX) return false;
     return encode_fn() != nullptr;
+}
+
+bool ssd_tc_output_eligible(const mb200_ssd_args &a)
+{
+    if (!aligned16(a.C) || !mult8(a.C_stride, 3)) return false;
+    if (!a.out || !aligned16(a.out) || !mult8(a.out_stride, 3)) return false;
+    if (a.z && (!aligned16(a.z) || !mult8(a.z_stride, 3))) return false;
+    return true;
 }
 
 int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
@@ -1129,7 +1104,7 @@ int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool stat
 // One (batch, head) per CTA: worth it once those fill at least half of the SMs.
 bool ssd_tc_stream_eligible(const mb200_ssd_args &a)
 {
-    return (int64_t)a.batch * a.nheads >= MB200_SSD_STREAM_MIN_UNITS;
+    return (int64_t)a.batch * a.nheads >= kStreamMinUnits;
 }
 
 template <typename T>
@@ -1166,10 +1141,3 @@ int ssd_tc_state_stream(const mb200_ssd_args &a, const SsdScratch &lay, cudaStre
 
 }  // namespace mb200
 
-#ifdef MB200_SCAN_TRACE
-// Experiment aid (only in trace builds): copies the chunk-scan time stamps to the host.
-extern "C" int mb200_debug_scan_trace(unsigned long long *host_dst)
-{
-    return cudaMemcpyFromSymbol(host_dst, mb200::g_scan_trace, sizeof(mb200::g_scan_trace)) == cudaSuccess ? 0 : -1;
-}
-#endif

@@ -12,18 +12,9 @@ namespace mb200 {
 
 namespace {
 
-// Tunables (overridable at compile time for experiments).
-#ifndef MB200_SSU_THREADS
-#define MB200_SSU_THREADS 64
-#endif
-#ifndef MB200_SSU_ROWS_IN_FLIGHT
-#define MB200_SSU_ROWS_IN_FLIGHT 4
-#endif
-#ifndef MB200_SSU_MIN_ROW_TILE
-#define MB200_SSU_MIN_ROW_TILE 64
-#endif
-constexpr int kThreads = MB200_SSU_THREADS;
-constexpr int kRowsInFlight = MB200_SSU_ROWS_IN_FLIGHT;
+constexpr int kThreads = 64;         // many small CTAs hide the per-(batch, head) set-up latency best
+constexpr int kRowsInFlight = 4;     // state rows a lane group loads before it touches any of them
+constexpr int kMinRowTile = 64;      // state rows per CTA at least (amortises the B / C / dt set-up)
 
 // out rows of a padding entry (state_batch_indices < 0) are defined to be zero.
 __device__ void zero_rows(const mb200_ssu_args &a, int b, int h, int p0, int rows)
@@ -197,7 +188,7 @@ int launch_packet(const mb200_ssu_args &a, bool tied, cudaStream_t stream)
 {
     constexpr int GROUPS = kThreads / LPR;
     int row_tile = GROUPS * kRowsInFlight;
-    if (row_tile < MB200_SSU_MIN_ROW_TILE) row_tile = MB200_SSU_MIN_ROW_TILE;
+    if (row_tile < kMinRowTile) row_tile = kMinRowTile;
     if (row_tile > a.dim) row_tile = a.dim;
     dim3 grid((a.dim + row_tile - 1) / row_tile, a.batch, a.nheads);
     if (tied)

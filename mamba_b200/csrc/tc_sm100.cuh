@@ -41,7 +41,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 // hardware-chosen time, so the bound is wall time (kWaitLimitNs on the global nanosecond timer), not
 // a poll count.  On expiry the wait records `code` in *status (first failure wins) and returns
 // false.  Callers carry on without touching the data, so the kernel still reaches its TMEM release.
-constexpr unsigned long long kWaitLimitNs = 50ull * 1000 * 1000;
+// The limit is generous (2 s): a healthy CTA can be held off its SM for tens of milliseconds when the GPU is
+// time-sliced between processes or a debugger is attached, and an expiry invalidates the call's output.
+constexpr unsigned long long kWaitLimitNs = 2000ull * 1000 * 1000;
 __device__ __forceinline__ unsigned long long global_ns()
 {
     unsigned long long t;

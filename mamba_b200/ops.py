@@ -11,6 +11,7 @@ and the current stream; all arithmetic happens in the library's CUDA kernels.
 """
 import ctypes
 import math
+import os
 
 import torch
 
@@ -212,7 +213,14 @@ def _ssd_args(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx
     return a
 
 
-_last_ssd_scratch = None
+# What ssd_status() needs of the most recent SSD call: the 256-byte tail of its scratch buffer -- the buffer itself
+# while it is small, a copy of the tail made on the stream when holding the buffer would pin a lot of memory until
+# the next call -- or the argument struct of a call that used the library's built-in buffer.
+_PIN_SCRATCH_BELOW = 64 << 20
+_last_ssd_status = None
+_last_ssd_static_args = None
+# MB200_CHECK_STATUS=1: every SSD call synchronises and raises if a kernel abandoned a bounded wait (debugging aid).
+_CHECK_STATUS = os.environ.get("MB200_CHECK_STATUS", "0") not in ("", "0")
 
 
 def scan_status(device=None):
@@ -232,9 +240,17 @@ def ssd_status():
     0 means every kernel ran to completion.  A non-zero value means a kernel abandoned one of its
     bounded waits (its code is the value) and the outputs of that call must not be used.  Meant for
     tests and debugging; the operators themselves never synchronise."""
-    if _last_ssd_scratch is None:
+    if _last_ssd_static_args is not None:
+        st = ctypes.c_int32(0)
+        L.check(L.lib().mb200_ssd_static_status(ctypes.byref(_last_ssd_static_args), ctypes.byref(st)))
+        return int(st.value)
+    if _last_ssd_status is None:
         return 0
-    return int(_last_ssd_scratch[-256:-252].view(torch.int32).item())
+    return int(_last_ssd_status[:4].view(torch.int32).item())
+
+
+def seqlen_of(x):
+    return x.shape[1]
 
 
 def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_idx, dt_softplus, dt_limit,
@@ -283,8 +299,20 @@ def _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, initial_states, seq_i
         L.set_strides(a.z_stride, z, 3)
     entry = L.lib().mb200_ssd_chunk_scan_fwd_static if builtin_scratch else L.lib().mb200_ssd_chunk_scan_fwd
     L.check(entry(ctypes.byref(a), L.stream_ptr(x.device)))
-    global _last_ssd_scratch
-    _last_ssd_scratch = scratch
+    global _last_ssd_status, _last_ssd_static_args
+    if builtin_scratch:
+        _last_ssd_status, _last_ssd_static_args = None, a        # no device tensor is created on this path
+    else:
+        _last_ssd_static_args = None
+        if seqlen_of(x) == 0:
+            _last_ssd_status = None
+        else:
+            tail = scratch[-256:]
+            _last_ssd_status = tail if scratch.numel() <= _PIN_SCRATCH_BELOW else tail.clone()
+    if _CHECK_STATUS:
+        st = ssd_status()
+        if st:
+            raise RuntimeError(f"mamba_b200: an SSD kernel abandoned a bounded wait (status {st}); the outputs are invalid")
     return out, scratch
 
 
@@ -300,8 +328,10 @@ def mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bia
     ``return_varlen_states`` (batch must then be 1).
     Returns ``out``, ``(out, final_states)``, ``(out, varlen_states)`` or ``(out, final_states, varlen_states)``
     like the reference; final_states fp32 (batch, nheads, headdim, dstate), varlen_states fp32
-    (num_sequences, nheads, headdim, dstate).  Inter-chunk states are kept in fp32 whatever ``state_dtype``
-    asks for.
+    (num_sequences, nheads, headdim, dstate).  ``state_dtype`` is accepted for signature compatibility and not
+    used: the running inter-chunk state is fp32 on chip; the copy of it that the chunk-output stage multiplies by C
+    is rounded to the input dtype on the tensor-core path (as the reference's default does) and stays fp32 on the
+    general path.
     """
     if not return_varlen_states:
         cu_seqlens = None
@@ -380,10 +410,11 @@ def ssd_fold_state(incoming_state, range_decay, range_state):
     out = torch.empty_like(range_state)
     rows = range_decay.numel()
     row = range_state.numel() // max(rows, 1)
-    s_in = None if incoming_state is None else incoming_state.contiguous()
-    L.check(L.lib().mb200_ssd_fold_state(L.ptr(s_in), L.ptr(range_decay.contiguous()), L.ptr(range_state.contiguous()),
-                                         L.ptr(out), rows, row, range_state.device.index,
-                                         L.stream_ptr(range_state.device)))
+    # the converted tensors stay bound to names until the launch has been enqueued
+    s_in = None if incoming_state is None else _fp32(incoming_state).contiguous()
+    decay, local = _fp32(range_decay).contiguous(), _fp32(range_state).contiguous()
+    L.check(L.lib().mb200_ssd_fold_state(L.ptr(s_in), L.ptr(decay), L.ptr(local), L.ptr(out), rows, row,
+                                         range_state.device.index, L.stream_ptr(range_state.device)))
     return out
 
 

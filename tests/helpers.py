@@ -34,11 +34,26 @@ def norm_err(a, b):
     return ((a - b).abs().max() / b.abs().max().clamp_min(1.0)).item()
 
 
+def rel_err(a, b, floor_frac=1e-2):
+    """Largest element-wise relative error |a-b| / |b| over the elements whose magnitude is at least
+    `floor_frac` of the output range (below that a relative error measures rounding of near-cancelled sums)."""
+    a, b = a.detach().float().cpu(), b.detach().float().cpu()
+    keep = b.abs() >= floor_frac * b.abs().max().clamp_min(1e-30)
+    if not keep.any():
+        return 0.0
+    return ((a - b).abs()[keep] / b.abs()[keep]).max().item()
+
+
+# (what, normalised max error, element-wise relative error) of every comparison made, for the end-of-run report
+ERROR_LOG = []
+
+
 def assert_close(a, b, tol, what=""):
     a, b = a.detach().float().cpu(), b.detach().float().cpu()
     assert a.shape == b.shape, f"{what}: shape {tuple(a.shape)} vs {tuple(b.shape)}"
     assert torch.isfinite(a).all(), f"{what}: non-finite values"
     e = norm_err(a, b)
+    ERROR_LOG.append((what, e, rel_err(a, b)))
     assert e <= tol, f"{what}: normalised max error {e:.3e} > {tol:.1e}"
     # element-wise form with rtol = atol = tol scaled by the output range
     scale = b.abs().max().clamp_min(1.0)

@@ -252,6 +252,22 @@ def test_extension_module_stand_in(many):
         selective_scan_cuda.bwd()
 
 
+def test_extension_module_stand_in_converts_parameter_dtypes():
+    """D and delta_bias in bf16 and a non-contiguous A: the stand-in converts them, and every converted copy must
+    still be alive (and described by its own strides) when the kernel runs."""
+    from mamba_b200.compat import selective_scan_cuda
+    inp = make_inputs(82, 2, 64, 200, 16, 1, torch.float32)
+    c = {k: v.to(DEV) for k, v in inp.items()}
+    D16, bias16 = c["D"].bfloat16(), c["delta_bias"].bfloat16()
+    A_t = c["A"].t().contiguous().t()                  # (dim, dstate) with strides (1, dim)
+    assert not A_t.is_contiguous()
+    out, x, out_z = selective_scan_cuda.fwd(c["u"], c["delta"], A_t, c["B"], c["C"], D16, c["z"], bias16, True)
+    want_z, want_last = oracle.selective_scan(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], D16.float().cpu(), inp["z"],
+                                              bias16.float().cpu(), delta_softplus=True, return_last_state=True)
+    assert_close(out_z, want_z, TOL_FP32, "gated out_z (converted D / bias)")
+    assert_close(x[:, :, -1, 1::2], want_last, TOL_FP32, "last state slice (converted D / bias)")
+
+
 def test_empty_batch():
     out = _fn()(torch.zeros(0, 4, 16, device=DEV), torch.zeros(0, 4, 16, device=DEV), torch.zeros(4, 8, device=DEV),
                 torch.zeros(0, 1, 8, 16, device=DEV), torch.zeros(0, 1, 8, 16, device=DEV))

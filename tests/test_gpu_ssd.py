@@ -231,6 +231,54 @@ def test_sequence_split_in_two_ranges(shape, dtype, tol):
     assert_close(ssd_fold_state(incoming[1], loc[1][1], loc[1][0]), wfin, TOL_FP32_, "folded summary")
 
 
+def test_sequence_split_when_only_the_output_half_is_misaligned():
+    """The LOCAL half sees x, B and dt only and takes the streaming tensor-core launch; the OUTPUT half is handed a
+    gate whose rows start 2 bytes off a 16-byte boundary, which the tensor-core chunk scan cannot take.  The OUTPUT
+    half must notice that LOCAL left no fp32 chunk states and form them itself.  Equal to the single call."""
+    from mamba_b200 import ssd_finish, ssd_fold_state, ssd_local_states
+    b, L, H, P, G, N, Q = 2, 1024, 40, 64, 2, 128, 256          # 80 (batch, head) units: the streaming launch
+    inp = make(21, b, L, H, P, G, N, torch.bfloat16)
+    c = {k: _c(v) for k, v in inp.items()}
+    zbuf = torch.zeros(b, L, H, P + 8, device=DEV, dtype=torch.bfloat16)
+    zbuf[..., 1:P + 1] = c["z"]
+    z_off = zbuf[..., 1:P + 1]                                  # unit last stride, strides multiples of 8, base 2 bytes off
+    assert z_off.data_ptr() % 16 == 2
+    whole, wfin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], z=c["z"], dt_bias=c["dt_bias"], dt_softplus=True,
+                        return_final_states=True)
+    assert _status() == 0
+    half = L // 2
+    sl = [slice(0, half), slice(half, L)]
+    loc = [ssd_local_states(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], Q, dt_bias=c["dt_bias"], dt_softplus=True) for s in sl]
+    incoming = [None, ssd_fold_state(None, loc[0][1], loc[0][0])]
+    outs, fin = [], None
+    for r, s in enumerate(sl):
+        o, fin = ssd_finish(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], c["C"][:, s], Q, loc[r][2], D=c["D"], z=z_off[:, s],
+                            dt_bias=c["dt_bias"], incoming_state=incoming[r], dt_softplus=True, return_final_states=True)
+        assert _status() == 0
+        outs.append(o)
+    assert_close(torch.cat(outs, dim=1), whole, TOL_BF16, "split out (misaligned gate)")
+    assert_close(fin, wfin, TOL_BF16, "split final (misaligned gate)")
+    # the whole operator with the same gate takes the general kernels throughout and agrees too
+    got, gfin = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], z=z_off, dt_bias=c["dt_bias"], dt_softplus=True,
+                      return_final_states=True)
+    assert_close(got, whole, TOL_BF16, "single call (misaligned gate)")
+    assert_close(gfin, wfin, TOL_BF16, "single call final (misaligned gate)")
+
+
+def test_empty_range_of_a_sequence_split_is_the_identity():
+    """A LOCAL call on zero tokens (a rank that owns no chunk) returns state 0 and decay 1; the OUTPUT call hands
+    the incoming state on as the final state."""
+    from mamba_b200 import ssd_finish, ssd_local_states
+    b, H, P, G, N, Q = 2, 3, 64, 1, 128, 256
+    inp = make(22, b, 0, H, P, G, N, torch.bfloat16, has_z=False, init=True)
+    c = {k: _c(v) for k, v in inp.items()}
+    state, decay, scratch = ssd_local_states(c["x"], c["dt"], c["A"], c["B"], Q, dt_bias=c["dt_bias"], dt_softplus=True)
+    assert torch.equal(state, torch.zeros_like(state)) and torch.equal(decay, torch.ones_like(decay))
+    out, fin = ssd_finish(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, scratch, D=c["D"], dt_bias=c["dt_bias"],
+                          incoming_state=c["initial_states"], dt_softplus=True, return_final_states=True)
+    assert out.shape == (b, 0, H, P) and torch.equal(fin, c["initial_states"])
+
+
 def _packed(seed, lens, H, P, G, N, dtype):
     total = sum(lens)
     inp = make(seed, 1, total, H, P, G, N, dtype)

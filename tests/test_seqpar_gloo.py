@@ -32,6 +32,8 @@ def _oracle_steps():
     from mamba_b200.seqpar import SsdSteps
 
     def local(x, dt, A, B, Q, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf"))):
+        if x.shape[1] == 0:      # an empty range is summarised by the identity, as the library does
+            return torch.zeros(x.shape[0], x.shape[2], x.shape[3], B.shape[3]), torch.ones(x.shape[0], x.shape[2]), None
         _, state = oracle.ssd_chunk_scan(x, dt, A, B, B, Q, dt_bias=dt_bias, dt_softplus=dt_softplus, dt_limit=dt_limit)
         d = dt.float() + (0 if dt_bias is None else dt_bias)
         d = F.softplus(d) if dt_softplus else d
@@ -43,6 +45,9 @@ def _oracle_steps():
 
     def finish(x, dt, A, B, C, Q, scratch, D=None, z=None, dt_bias=None, incoming_state=None, dt_softplus=False,
                dt_limit=(0.0, float("inf")), return_final_states=False):
+        if x.shape[1] == 0:
+            fin = incoming_state if incoming_state is not None else torch.zeros(x.shape[0], x.shape[2], x.shape[3], B.shape[3])
+            return (x.float(), fin) if return_final_states else x.float()
         out, fin = oracle.ssd_chunk_scan(x, dt, A, B, C, Q, D, z, dt_bias, incoming_state, dt_softplus=dt_softplus,
                                          dt_limit=dt_limit)
         return (out, fin) if return_final_states else out
@@ -57,10 +62,12 @@ def _worker(rank, world, store, mode, result_dir):
                             timeout=datetime.timedelta(seconds=8))
     try:
         b, L, H, P, G, N, Q = 1, 448, 3, 8, 1, 16, 64
+        mode, _, handoff = mode.partition(":")
+        if mode == "short":      # fewer chunks than ranks: the last ranks own nothing
+            L = 128
         inp = _inputs(5, b, L, H, P, G, N)
         lo, hi = split_sequence(L, Q, world, rank)
         sl = slice(lo, hi)
-        mode, _, handoff = mode.partition(":")
         if mode == "dead_predecessor" and rank == 0:
             return                                                  # leaves without handing its state on
         try:
@@ -95,6 +102,22 @@ def test_sequence_split_equals_single_rank(world, handoff):
     assert [res[r]["range"] for r in range(world)][0][0] == 0 and res[world - 1]["range"][1] == 448
     assert (got - want).abs().max() <= 1e-5 * want.abs().max()
     assert (res[world - 1]["fin"] - wfin).abs().max() <= 1e-5 * wfin.abs().max().clamp_min(1)
+
+
+@pytest.mark.parametrize("handoff", ["chain", "gather"])
+def test_more_ranks_than_chunks(handoff):
+    """Ranks that own no chunk pass the state through unchanged: the last rank still returns the final state."""
+    import oracle
+    world = 4
+    res = _run(world, "short:" + handoff)
+    inp = _inputs(5, 1, 128, 3, 8, 1, 16)
+    want, wfin = oracle.ssd_chunk_scan(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], 64, inp["D"], inp["z"], inp["dt_bias"],
+                                       inp["init"], dt_softplus=True)
+    assert [res[r]["range"] for r in range(world)] == [(0, 64), (64, 128), (128, 128), (128, 128)]
+    got = torch.cat([res[r]["out"] for r in range(world)], dim=1)
+    assert (got - want).abs().max() <= 1e-5 * want.abs().max()
+    for r in (1, 2, 3):
+        assert (res[r]["fin"] - wfin).abs().max() <= 1e-5 * wfin.abs().max().clamp_min(1)
 
 
 def test_missing_predecessor_is_reported_not_hung():

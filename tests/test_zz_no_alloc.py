@@ -1,15 +1,15 @@
 """The SSD entry point that allocates nothing (mb200_ssd_chunk_scan_fwd_static).
 
-Collected last on purpose (the file name sorts after every other test file): if it fails under
-``pytest -x`` every other test has already run.  It must pass both on its own in a fresh process and
-after the rest of the suite, because the buffer it uses lives in the library image and keeps whatever
-the previous call left in it.
+The buffer it uses lives in the library image and keeps whatever the previous call left in it, so these
+tests must pass both on their own in a fresh process and after every other test of the suite has used
+the library (this file is collected last).
 """
 import math
 
 import pytest
 import torch
 
+import oracle
 from helpers import TOL_BF16, TOL_FP32, assert_close
 
 pytestmark = pytest.mark.gpu
@@ -32,8 +32,8 @@ def _inputs(seed, b, L, H, P, G, N, dtype):
 ])
 def test_static_scratch_matches_caller_scratch_twice(dtype, tol, shape):
     """Two calls in a row through the no-allocation entry point, each on different data, each compared
-    with the ordinary entry point (which gets fresh caller-owned scratch)."""
-    from mamba_b200 import mamba_chunk_scan_combined, mamba_chunk_scan_combined_noalloc
+    with the ordinary entry point (which gets fresh caller-owned scratch) and with the CPU oracle."""
+    from mamba_b200 import mamba_chunk_scan_combined, mamba_chunk_scan_combined_noalloc, ops
     b, L, H, P, G, N, Q = shape
     for rep in range(2):
         c = _inputs(900 + rep, b, L, H, P, G, N, dtype)
@@ -50,8 +50,14 @@ def test_static_scratch_matches_caller_scratch_twice(dtype, tol, shape):
         assert allocations() == before, "the no-allocation path asked the allocator for device memory"
         torch.cuda.synchronize()
         assert got is out
+        assert ops.ssd_status() == 0, "a kernel of the no-allocation call abandoned a bounded wait"
         assert_close(out, want, tol, f"static scratch out (call {rep})")
         assert_close(fin, want_fin, tol, f"static scratch final_states (call {rep})")
+        f = lambda t: t.float().cpu()
+        o_out, o_fin = oracle.ssd_chunk_scan(f(c["x"]), f(c["dt"]), f(c["A"]), f(c["B"]), f(c["C"]), Q, f(c["D"]), f(c["z"]),
+                                             f(c["dt_bias"]), initial_states=f(c["init"]), dt_softplus=True)
+        assert_close(out, o_out, tol, f"static scratch out vs oracle (call {rep})")
+        assert_close(fin, o_fin, tol, f"static scratch final_states vs oracle (call {rep})")
 
 
 def test_problem_larger_than_the_buffer_is_refused():
