@@ -1,18 +1,24 @@
 #!/usr/bin/env python
 """Benchmark of the scan hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c0] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--only c0|c1|c2|c3|c4]
 
-Default workload (the one the headline metric is quoted on): the Mamba-1 selective scan at the
-2.8B-layer shape -- batch 8, d_inner 5120, seqlen 2048, d_state 16, bf16 activations, one B/C group
-(synthetic seeded inputs).  One "step" is one forward pass over that batch.  With N > 1 (launched by
-torchrun, one rank per GPU) every rank runs the same per-GPU batch on its own data (no collective on
-the data path; weak scaling) and the slowest rank sets the time.
+One JSON line.  The headline (`metric`, `value`, `roofline`, `e2e`, `cpu_baseline`) is the Mamba-1 selective
+scan at the 2.8B-layer shape (batch 8, d_inner 5120, seqlen 2048, d_state 16, bf16); `workloads` carries the
+other configurations of the path with the same fields:
 
-Prints ONE JSON line: tokens/s with inputs resident in HBM (`value`), the same through the public
-API with pinned host buffers and the copies timed (`e2e`), the roofline of the dominant kernel
-against the measured HBM peak, and the CPU baseline (the PyTorch-on-CPU restatement of the
-reference's definition) timed on this host.
+    c2  Mamba-2 SSD chunked scan        batch 8, seqlen 4096, 80 heads x 64, 1 group, d_state 128, chunk 256, gated
+    c3  Mamba-2 SSD, long sequence      batch 1, seqlen 262144, 128 heads x 64, 8 groups, d_state 128, no gate
+    c4  Mamba-2 decode state update     batch 256, 80 heads x 64, d_state 128, fp32 state, consecutive in-place steps
+
+With N > 1 (torchrun, one rank per GPU) every workload is the SAME fixed problem, divided: c1 by batch rows,
+c2 by heads, c4 by batch rows (independent units, no collective on the data path) and c3 by contiguous chunk
+ranges of the sequence with the range states exchanged by NCCL.  `value` is whole-problem tokens per second,
+timed on the device as the maximum over ranks ("scaling": "strong").
+
+Timing: W warm-up steps, then R blocks of exactly K steps, each block bracketed by a barrier and a device
+synchronisation and timed with CUDA events on the launching stream; the MEDIAN block sets the reported time.
+R is chosen so that the timed blocks cover at least 0.3 s (5 <= R <= 400), long enough for the clock sampler.
 """
 import argparse
 import json
@@ -29,33 +35,45 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# dram bytes (read + write) per launch of the dominant kernel from the committed ncu capture
-# (profiles/), or None where no capture exists for that workload.
-NCU_TRAFFIC_BYTES = {
-    "c1": 659_956_992,      # scan_stream_kernel: 509.0 MB read + 151.0 MB written
-    "c2": 1_735_000_000,    # the SSD launches summed (state stream 368 + 154 MB, chunk_scan 881 + 310 MB)
-    "c4": 1_291_591_424,    # ssu_packet_kernel: 676.8 MB read + 614.7 MB written
-    "c0": None, "c3": None,
+METRIC, UNIT = "scan_fwd_tokens_per_s", "tokens/s"
+
+# DRAM bytes (read + write) per launch group of a full single-GPU step, from the committed ncu captures
+NCU_TRAFFIC = {
+    "c1": (659_956_992, "profiles/scan_stream_kernel__config1.md"),
+    "c2": (1_735_000_000, "profiles/ssd_chunk_scan_forward__config2.md + profiles/ssd_state_stream_kernel__config2.md"),
+    "c4": (1_291_591_424, "profiles/ssu_packet_kernel__config4.md"),
 }
 
-
-# the names the GPU arm puts in config.workload; the reference arm reports under the same ones
 WORKLOAD_DESC = {
     "c0": "mamba1_selective_scan_fwd fp32 b2 d256 L512 N16",
     "c1": "mamba1_selective_scan_fwd bf16 b8 d5120 L2048 N16 (2.8B layer)",
     "c2": "mamba2_ssd_chunk_scan_fwd bf16 b8 L4096 h80 P64 g1 N128 Q256 (+z, +final_states)",
-    "c3": "mamba2_ssd_chunk_scan_fwd bf16 b1 L262144 h128 P64 g8 N128 Q256 (no z), sequence split over GPUs",
-    "c4": "mamba2_selective_state_update b256 h80 P64 N128 fp32 state, bf16 activations",
+    "c3": "mamba2_ssd_chunk_scan_fwd bf16 b1 L262144 h128 P64 g8 N128 Q256 (no z, +final_states)",
+    "c4": "mamba2_selective_state_update b256 h80 P64 g1 N128, fp32 state, bf16 activations, consecutive steps",
+}
+PARTITION = {
+    "c0": "replicas only (correctness configuration)",
+    "c1": "batch rows divided over the GPUs, no collective",
+    "c2": "heads divided over the GPUs (B and C replicated), no collective",
+    "c3": "contiguous chunk ranges of the sequence per GPU; range states exchanged by NCCL (all-gather + local fold)",
+    "c4": "batch rows divided over the GPUs, each owning its slice of the state; no collective",
 }
 
 
-def measured_peak_gbs():
+def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return float(p["hbm_gbs"]), float(p.get("bf16_tflops_sustained", p.get("bf16_tflops", 0.0))), "measured"
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 0.0)), "measured"
     return 6650.0, 1590.0, "fallback"
+
+
+def split_even(total, world, rank):
+    """Contiguous share [lo, hi) of `total` units for `rank`."""
+    per, extra = divmod(total, world)
+    lo = rank * per + min(rank, extra)
+    return lo, lo + per + (1 if rank < extra else 0)
 
 
 # ----------------------------------------------------------------------------------------- inputs
@@ -64,12 +82,20 @@ def softplus_inv_dt(n, g):
     return dt + torch.log(-torch.expm1(-dt))
 
 
-def make_c1(batch, dim=5120, L=2048, N=16, seed=1001, dtype=torch.bfloat16):
+def make_c1_rows(rows, dim=5120, L=2048, N=16, seed=1001, dtype=torch.bfloat16):
+    """Host tensors of the given batch rows of config 1 (a row's data depends only on its index)."""
     g = torch.Generator().manual_seed(seed)
     r = lambda *s: torch.randn(*s, generator=g)
-    return dict(u=r(batch, dim, L).to(dtype), delta=r(batch, dim, L).to(dtype), z=r(batch, dim, L).to(dtype),
-                A=-torch.exp(r(dim, N)), B=r(batch, 1, N, L).to(dtype), C=r(batch, 1, N, L).to(dtype), D=r(dim),
-                delta_bias=softplus_inv_dt(dim, g))
+    par = dict(A=-torch.exp(r(dim, N)), D=r(dim), delta_bias=softplus_inv_dt(dim, g))
+    cols = {k: [] for k in ("u", "delta", "z", "B", "C")}
+    for row in rows:
+        gr = torch.Generator().manual_seed(seed * 1000 + row)
+        rr = lambda *s: torch.randn(*s, generator=gr)
+        for k, shape in (("u", (1, dim, L)), ("delta", (1, dim, L)), ("z", (1, dim, L)), ("B", (1, 1, N, L)), ("C", (1, 1, N, L))):
+            cols[k].append(rr(*shape).to(dtype))
+    empty = {"u": (0, dim, L), "delta": (0, dim, L), "z": (0, dim, L), "B": (0, 1, N, L), "C": (0, 1, N, L)}
+    par.update({k: (torch.cat(v) if v else torch.zeros(empty[k], dtype=dtype)) for k, v in cols.items()})
+    return par
 
 
 def make_c0(batch=2, dim=256, L=512, N=16, seed=1000):
@@ -79,190 +105,229 @@ def make_c0(batch=2, dim=256, L=512, N=16, seed=1000):
                 B=r(batch, 1, N, L), C=r(batch, 1, N, L), D=r(dim), delta_bias=-4 + 2 * torch.rand(dim, generator=g))
 
 
-def make_c2(batch, H=80, L=4096, P=64, N=128, seed=1002):
+def ssd_params(H, seed):
     g = torch.Generator().manual_seed(seed)
-    r = lambda *s: torch.randn(*s, generator=g)
-    bf = torch.bfloat16
-    return dict(x=r(batch, L, H, P).to(bf), dt=r(batch, L, H).to(bf), A=-(1 + 15 * torch.rand(H, generator=g)),
-                B=r(batch, L, 1, N).to(bf), C=r(batch, L, 1, N).to(bf), D=r(H), z=r(batch, L, H, P).to(bf),
-                dt_bias=softplus_inv_dt(H, g))
-
-
-def make_c4(batch, H=80, P=64, N=128, seed=1004, pool=4):
-    """`pool` distinct token inputs are rotated through the steps; the state is updated in place."""
-    g = torch.Generator().manual_seed(seed)
-    r = lambda *s: torch.randn(*s, generator=g)
-    bf = torch.bfloat16
-    return dict(state=0.1 * r(batch, H, P, N), x=r(pool, batch, H, P).to(bf), z=r(pool, batch, H, P).to(bf),
-                dt=r(pool, batch, H).to(bf), B=r(pool, batch, 1, N).to(bf), C=r(pool, batch, 1, N).to(bf),
-                A=-(1 + 15 * torch.rand(H, generator=g)), D=r(H), dt_bias=softplus_inv_dt(H, g))
+    return dict(A=-(1 + 15 * torch.rand(H, generator=g)), D=torch.randn(H, generator=g), dt_bias=softplus_inv_dt(H, g))
 
 
 class Workload:
-    """One benchmark configuration: device step, host-buffer step, CPU-baseline sample, byte counts."""
+    """One configuration, this rank's share of it: device step, byte counts, CPU-baseline sample."""
 
-    def __init__(self, name, dev, batch=None):
-        """`batch` shrinks the per-GPU batch (profiling captures only; the JSON line then says so)."""
-        self.name, self.dev = name, dev
-        self.reduced = batch is not None
+    def __init__(self, name, dev, rank=0, world=1, batch=None):
+        """`batch` shrinks the batch (profiling captures of a small case only; the JSON line then says so)."""
         import mamba_b200 as mb
-        self.mb = mb
+        self.mb, self.name, self.dev, self.rank, self.world = mb, name, dev, rank, world
+        self.reduced = batch is not None
+        self.desc, self.partition = WORKLOAD_DESC[name], PARTITION[name]
+        self.step_no = 0
+        self.flops = None
+        bf = torch.bfloat16
         if name in ("c1", "c0"):
-            host = make_c1(batch or 8) if name == "c1" else make_c0()
-            self.shape = dict(batch=host["u"].shape[0], d_inner=host["u"].shape[1], seqlen=host["u"].shape[2], d_state=16)
-            self.tokens = host["u"].shape[0] * host["u"].shape[2]
-            self.desc = WORKLOAD_DESC[name]
-            self.dtype = "bf16" if name == "c1" else "f32"
-            self.step_inputs = ("u", "delta", "z", "B", "C")
-            esz = host["u"].element_size()
+            if name == "c1":
+                nb = batch or 8
+                lo, hi = split_even(nb, world, rank)
+                host = make_c1_rows(range(lo, hi))
+                self.global_tokens = nb * 2048
+            else:
+                host = make_c0()
+                self.global_tokens = 2 * 512
             b, d, L = host["u"].shape
+            esz = host["u"].element_size()
+            self.shape = dict(batch=b, d_inner=d, seqlen=L, d_state=16)
+            self.dtype = "bf16" if name == "c1" else "f32"
             self.alg_bytes = 4 * b * d * L * esz + 2 * b * 16 * L * esz + d * 16 * 4 + 2 * d * 4 + b * d * 16 * 4
-            self.launches_per_step = 1
+            self.launches_per_step = 1 if b > 0 else 0
+            self.kernels = "scan_stream_kernel"
+            self.host = host
+            self.d = {k: v.to(dev) for k, v in host.items()}
         elif name == "c2":
-            host = make_c2(batch or 8)
-            b, L, H, P = host["x"].shape
-            self.shape = dict(batch=b, seqlen=L, nheads=H, headdim=P, ngroups=1, d_state=128, chunk_size=256)
-            self.tokens = b * L
-            self.desc = WORKLOAD_DESC[name]
+            nb, L, Hall, P, N = batch or 8, 4096, 80, 64, 128
+            lo, hi = split_even(Hall, world, rank)
+            H = hi - lo
+            g = torch.Generator(device=dev).manual_seed(1002)
+            r = lambda *s: torch.randn(*s, generator=g, device=dev)
+            par = ssd_params(Hall, 1002)
+            # B and C belong to the one group and are the same on every rank; x, dt, z are this rank's heads
+            Bc, Cc = r(nb, L, 1, N).to(bf), r(nb, L, 1, N).to(bf)
+            g.manual_seed(100200 + rank)
+            self.d = dict(x=r(nb, L, H, P).to(bf), dt=r(nb, L, H).to(bf), z=r(nb, L, H, P).to(bf), B=Bc, C=Cc,
+                          **{k: v[lo:hi].to(dev) for k, v in par.items()})
+            self.shape = dict(batch=nb, seqlen=L, nheads=H, headdim=P, ngroups=1, d_state=N, chunk_size=256)
+            self.global_tokens = nb * L
             self.dtype = "bf16"
-            self.step_inputs = ("x", "dt", "z", "B", "C")
-            self.alg_bytes = 3 * b * L * H * P * 2 + b * L * H * 2 + 2 * b * L * 128 * 2 + b * H * P * 128 * 4 + 3 * H * 4
-            self.launches_per_step = 5      # cumsum, state stream (head pairs, then single heads), C.B^T, chunk scan
+            self.alg_bytes = 3 * nb * L * H * P * 2 + nb * L * H * 2 + 2 * nb * L * N * 2 + nb * H * P * N * 4 + 3 * H * 4
+            self.flops = nb * L * (2 * 256 * N + H * (2 * P * N + 2 * 256 * P + 2 * N * P))   # C.B^T, chunk state, intra-chunk (dense), C.state
+            self.launches_per_step = 5 if H > 0 else 0
+            self.kernels = "ssd_tc_cb, ssd_cumsum, ssd_tc_state_stream (pairs, singles), ssd_tc_chunk_scan"
         elif name == "c3":
-            # long sequence split into contiguous chunk ranges, one per rank; the whole sequence at N=1
             from mamba_b200.seqpar import split_sequence
-            world = int(os.environ.get("WORLD_SIZE", "1"))
-            rank = int(os.environ.get("RANK", "0"))
-            Ltot, H, P, G, N = 262144, 128, 64, 8, 128
+            Ltot, H, P, G, N = (batch or 1) * 262144, 128, 64, 8, 128
+            if self.reduced:
+                Ltot = 262144 // 8
             lo, hi = split_sequence(Ltot, 256, world, rank)
             Lr = hi - lo
             g = torch.Generator(device=dev).manual_seed(1003 + rank)
-            r = lambda *sh: torch.randn(*sh, generator=g, device=dev)
-            bf = torch.bfloat16
-            gh = torch.Generator().manual_seed(1003)
-            host = dict(A=-(1 + 15 * torch.rand(H, generator=gh)), D=torch.randn(H, generator=gh), dt_bias=softplus_inv_dt(H, gh))
-            self.dev_only = dict(x=r(1, Lr, H, P).to(bf), dt=r(1, Lr, H).to(bf), B=r(1, Lr, G, N).to(bf), C=r(1, Lr, G, N).to(bf))
+            r = lambda *s: torch.randn(*s, generator=g, device=dev)
+            self.d = dict(x=r(1, Lr, H, P).to(bf), dt=r(1, Lr, H).to(bf), B=r(1, Lr, G, N).to(bf), C=r(1, Lr, G, N).to(bf),
+                          **{k: v.to(dev) for k, v in ssd_params(H, 1003).items()})
             self.shape = dict(batch=1, seqlen_total=Ltot, seqlen_this_gpu=Lr, nheads=H, headdim=P, ngroups=G, d_state=N, chunk_size=256)
-            self.tokens = Lr
-            self.desc = WORKLOAD_DESC[name]
+            self.global_tokens = Ltot
             self.dtype = "bf16"
-            self.step_inputs = ("x", "dt", "B", "C")
             self.alg_bytes = 2 * Lr * H * P * 2 + Lr * H * 2 + 2 * Lr * G * N * 2 + H * P * N * 4 + 3 * H * 4
-            self.launches_per_step = 4 if world == 1 else 5
-            self.world = world
+            self.flops = Lr * (G * 2 * 256 * N + H * (2 * P * N + 2 * 256 * P + 2 * N * P))
+            self.launches_per_step = 4 if world == 1 else 7
+            self.kernels = ("ssd_tc_cb, ssd_cumsum, ssd_tc_state_stream, ssd_tc_chunk_scan" if world == 1 else
+                            "ssd_cumsum, ssd_tc_state_stream, ssd_fold_ranges, ssd_incoming_state, ssd_tc_cb, ssd_tc_chunk_scan (+ NCCL all-gather)")
         elif name == "c4":
-            host = make_c4(batch or 256)
-            b, H, P, N = host["state"].shape
-            self.shape = dict(batch=b, nheads=H, headdim=P, ngroups=1, d_state=N, consecutive_steps=True)
-            self.tokens = b
-            self.desc = WORKLOAD_DESC[name]
-            self.dtype = "f32"
-            self.step_inputs = ("x", "dt", "z", "B", "C")
-            self.alg_bytes = 2 * b * H * P * N * 4 + 3 * b * H * P * 2 + b * H * 2 + 2 * b * N * 2 + 3 * H * 4
-            self.launches_per_step = 1
-        else:
-            raise SystemExit(f"unknown workload {name}")
-        self.host = host
-        self.d = {k: v.to(dev) for k, v in host.items()}
-        if name == "c3":
-            self.d.update(self.dev_only)
-        self.step_no = 0
-        if name == "c4":
-            H, P, N = self.shape["nheads"], self.shape["headdim"], self.shape["d_state"]
+            nb_all, H, P, N, pool = batch or 256, 80, 64, 128, 4
+            lo, hi = split_even(nb_all, world, rank)
+            nb = hi - lo
+            g = torch.Generator(device=dev).manual_seed(1004 + rank)
+            r = lambda *s: torch.randn(*s, generator=g, device=dev)
+            par = ssd_params(H, 1004)
+            # `pool` distinct token inputs are rotated through the steps; the state is updated in place
+            self.d = dict(state=0.1 * r(nb, H, P, N), x=r(pool, nb, H, P).to(bf), z=r(pool, nb, H, P).to(bf), dt=r(pool, nb, H).to(bf),
+                          B=r(pool, nb, 1, N).to(bf), C=r(pool, nb, 1, N).to(bf), **{k: v.to(dev) for k, v in par.items()})
             self.A3 = self.d["A"][:, None, None].expand(H, P, N)
             self.D2 = self.d["D"][:, None].expand(H, P)
             self.bias2 = self.d["dt_bias"][:, None].expand(H, P)
+            self.shape = dict(batch=nb, nheads=H, headdim=P, ngroups=1, d_state=N, consecutive_steps=True)
+            self.global_tokens = nb_all
+            self.dtype = "f32"
+            self.alg_bytes = 2 * nb * H * P * N * 4 + 3 * nb * H * P * 2 + nb * H * 2 + 2 * nb * N * 2 + 3 * H * 4
+            self.launches_per_step = 1 if nb > 0 else 0
+            self.kernels = "ssu_packet_kernel"
+        else:
+            raise SystemExit(f"unknown workload {name}")
 
-    # -- one pass with inputs already in HBM -------------------------------------------------
+    # -- one pass with this rank's inputs already in HBM ---------------------------------------
     def step(self, src=None):
-        d = self.d if src is None else src
-        mb = self.mb
+        d, mb = (self.d if src is None else src), self.mb
         if self.name in ("c1", "c0"):
             return mb.selective_scan_fn(d["u"], d["delta"], self.d["A"], d["B"], d["C"], self.d["D"], d["z"],
                                         self.d["delta_bias"], delta_softplus=True, return_last_state=True)[0]
-        if self.name == "c3":
-            if self.world == 1:
-                return mb.mamba_chunk_scan_combined(d["x"], d["dt"], self.d["A"], d["B"], d["C"], 256, D=self.d["D"],
-                                                    dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True)[0]
-            from mamba_b200.seqpar import mamba_chunk_scan_sequence_parallel
-            return mamba_chunk_scan_sequence_parallel(d["x"], d["dt"], self.d["A"], d["B"], d["C"], 256, D=self.d["D"],
-                                                      dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True,
-                                                      handoff=os.environ.get("MB200_BENCH_HANDOFF") or None)[0]
         if self.name == "c2":
-            return mb.mamba_chunk_scan_combined(d["x"], d["dt"], self.d["A"], d["B"], d["C"], 256, D=self.d["D"], z=d["z"],
-                                                dt_bias=self.d["dt_bias"], dt_softplus=True, return_final_states=True)[0]
-        i = self.step_no % self.d["x"].shape[0] if src is None else 0
+            return mb.mamba_chunk_scan_combined(d["x"], d["dt"], d["A"], d["B"], d["C"], 256, D=d["D"], z=d["z"],
+                                                dt_bias=d["dt_bias"], dt_softplus=True, return_final_states=True)[0]
+        if self.name == "c3":
+            return self.c3_step()[0]
+        i = self.step_no % d["x"].shape[0]
         self.step_no += 1
-        pick = (lambda k: d[k][i]) if src is None else (lambda k: d[k])
         b, H, P = self.shape["batch"], self.shape["nheads"], self.shape["headdim"]
-        return mb.selective_state_update(self.d["state"], pick("x"), pick("dt")[..., None].expand(b, H, P), self.A3,
-                                         pick("B"), pick("C"), self.D2, pick("z"), self.bias2, dt_softplus=True)
+        return mb.selective_state_update(d["state"], d["x"][i], d["dt"][i][..., None].expand(b, H, P), self.A3, d["B"][i], d["C"][i],
+                                         self.D2, d["z"][i], self.bias2, dt_softplus=True)
 
-    # -- host buffers for the end-to-end leg ---------------------------------------------------
+    def c3_step(self, phases=None):
+        d, mb = self.d, self.mb
+        if self.world == 1:
+            return mb.mamba_chunk_scan_combined(d["x"], d["dt"], d["A"], d["B"], d["C"], 256, D=d["D"], dt_bias=d["dt_bias"],
+                                                dt_softplus=True, return_final_states=True)
+        from mamba_b200.seqpar import mamba_chunk_scan_sequence_parallel
+        return mamba_chunk_scan_sequence_parallel(d["x"], d["dt"], d["A"], d["B"], d["C"], 256, D=d["D"], dt_bias=d["dt_bias"],
+                                                  dt_softplus=True, return_final_states=True, phases=phases)
+
+    # -- c3 at N > 1: the split result against a one-GPU run of the same heads (outside the timed region) ----
+    def c3_parity(self, heads=(5, 127)):
+        """Normalised max error of `heads` of the N-GPU output (and of the final state) against ONE call of the
+        operator over the whole sequence for those heads on rank 0."""
+        import torch.distributed as dist
+        d, dev, world = self.d, self.dev, self.world
+        out, fin = self.c3_step()
+        hs = list(heads)
+        gs = [h // (128 // 8) for h in hs]
+        L = self.shape["seqlen_this_gpu"]
+        lens = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
+        dist.all_gather(lens, torch.tensor([L], dtype=torch.int64, device=dev))
+        if len({int(v.item()) for v in lens}) != 1:
+            return {"skipped": "ranges of unequal length"}
+        parts = dict(x=d["x"][:, :, hs], dt=d["dt"][:, :, hs], B=d["B"][:, :, gs], C=d["C"][:, :, gs], out=out[:, :, hs])
+        full = {}
+        for k, v in parts.items():
+            v = v.contiguous()
+            buf = torch.empty((world,) + tuple(v.shape), dtype=v.dtype, device=dev)
+            dist.all_gather_into_tensor(buf, v)
+            full[k] = torch.cat(list(buf.unbind(0)), dim=1)          # ranks own consecutive ranges
+        fin_last = fin[:, hs].contiguous()
+        dist.broadcast(fin_last, src=world - 1)
+        res = None
+        if self.rank == 0:
+            want, wfin = self.mb.mamba_chunk_scan_combined(full["x"], full["dt"], d["A"][hs], full["B"], full["C"], 256, D=d["D"][hs],
+                                                           dt_bias=d["dt_bias"][hs], dt_softplus=True, return_final_states=True)
+            torch.cuda.synchronize()
+            err = lambda a, b: ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1.0)).item()
+            res = {"heads": hs, "out_norm_err": err(full["out"], want), "final_state_norm_err": err(fin_last, wfin),
+                   "against": "one call over the whole sequence for these heads on rank 0", "tolerance": 2e-2}
+        return res
+
+    # -- pinned host buffers for the end-to-end leg (headline workload) -------------------------
     def pinned_inputs(self):
-        out = {}
-        for k in self.step_inputs:
-            if self.name == "c3":
-                t = self.d[k].cpu()
-            else:
-                t = self.host[k] if self.name != "c4" else self.host[k][0]
-            out[k] = t.contiguous().pin_memory()
-        return out
+        return {k: self.host[k].contiguous().pin_memory() for k in ("u", "delta", "z", "B", "C")}
 
 
 # ----------------------------------------------------------------------------------------- CPU baseline
-def cpu_sample(name, h):
-    """A bounded sample of workload `name` (host tensors `h`) for the PyTorch-on-CPU restatement.
-    Returns (callable, tokens the call processes, description of the sample)."""
-    from oracle import torch_port as tp
-    if name in ("c1", "c0"):
-        nb = 1
-        sl = {k: (h[k][:nb] if k in ("u", "delta", "z", "B", "C") else h[k]) for k in h}
-        fn = lambda: tp.selective_scan(sl["u"], sl["delta"], sl["A"], sl["B"], sl["C"], sl["D"], sl["z"],
-                                       sl["delta_bias"], delta_softplus=True, return_last_state=True)
-        return fn, nb * h["u"].shape[2], f"{nb} of {h['u'].shape[0]} batch rows, all channels, full seqlen"
-    if name == "c3":
-        f = lambda t: t.float()
-        fn = lambda: tp.ssd_chunk_scan(f(h["x"]), f(h["dt"]), h["A"], f(h["B"]), f(h["C"]), 256, h["D"], None, h["dt_bias"],
-                                       dt_softplus=True)
-        L, nh = h["x"].shape[1], h["x"].shape[2]
-        return fn, L * nh / 128, f"first {L} of 262144 tokens x {nh} of 128 heads (one B/C group), fp32-widened inputs"
-    if name == "c2":
-        nh = 16
-        f = lambda t: t.float()
-        sl = dict(x=f(h["x"][:1, :, :nh]), dt=f(h["dt"][:1, :, :nh]), A=h["A"][:nh], B=f(h["B"][:1]), C=f(h["C"][:1]),
-                  D=h["D"][:nh], z=f(h["z"][:1, :, :nh]), dt_bias=h["dt_bias"][:nh])
-        fn = lambda: tp.ssd_chunk_scan(sl["x"], sl["dt"], sl["A"], sl["B"], sl["C"], 256, sl["D"], sl["z"], sl["dt_bias"],
-                                       dt_softplus=True)
-        frac = nh / h["x"].shape[2]
-        return fn, h["x"].shape[1] * frac, f"1 of 8 batch rows x {nh} of 80 heads, full seqlen, fp32-widened inputs"
-    nb = 32
-    _, H, P, N = h["state"].shape
-    state = h["state"][:nb].clone()
-    fn = lambda: tp.selective_state_update(state, h["x"][0, :nb], h["dt"][0, :nb, :, None].expand(nb, H, P),
-                                           h["A"][:, None, None].expand(H, P, N), h["B"][0, :nb], h["C"][0, :nb],
-                                           h["D"][:, None].expand(H, P), h["z"][0, :nb],
-                                           h["dt_bias"][:, None].expand(H, P), dt_softplus=True)
-    return fn, nb, f"{nb} of 256 batch rows, one step"
-
-
-def make_c3_sample(L=4096, H=16, P=64, N=128, seed=1003):
-    g = torch.Generator().manual_seed(seed)
-    r = lambda *s: torch.randn(*s, generator=g)
+def cpu_inputs(name):
+    """Host tensors of the bounded sample of `name` the CPU baseline runs, and what that sample is."""
     bf = torch.bfloat16
-    return dict(x=r(1, L, H, P).to(bf), dt=r(1, L, H).to(bf), A=-(1 + 15 * torch.rand(H, generator=g)), B=r(1, L, 1, N).to(bf),
-                C=r(1, L, 1, N).to(bf), D=r(H), dt_bias=softplus_inv_dt(H, g))
+    if name in ("c1", "c0"):
+        h = make_c1_rows([0]) if name == "c1" else make_c0()
+        nb = h["u"].shape[0]
+        total = 8 if name == "c1" else nb
+        return h, nb * h["u"].shape[2], f"{nb} of {total} batch rows, all channels, full seqlen"
+    g = torch.Generator().manual_seed(2000)
+    r = lambda *s: torch.randn(*s, generator=g)
+    if name in ("c2", "c3"):
+        L, nh = 4096, 16
+        h = dict(x=r(1, L, nh, 64).to(bf), dt=r(1, L, nh).to(bf), B=r(1, L, 1, 128).to(bf), C=r(1, L, 1, 128).to(bf),
+                 z=r(1, L, nh, 64).to(bf) if name == "c2" else None, **ssd_params(nh, 2000))
+        if name == "c2":
+            return h, L * nh / 80, f"1 of 8 batch rows x {nh} of 80 heads, full seqlen, fp32-widened inputs"
+        return h, L * nh / 128, f"first {L} of 262144 tokens x {nh} of 128 heads (one B/C group), fp32-widened inputs"
+    nb, H, P, N = 32, 80, 64, 128
+    h = dict(state=0.1 * r(nb, H, P, N), x=r(nb, H, P).to(bf), z=r(nb, H, P).to(bf), dt=r(nb, H).to(bf), B=r(nb, 1, N).to(bf),
+             C=r(nb, 1, N).to(bf), **ssd_params(H, 2000))
+    return h, nb, f"{nb} of 256 batch rows, one step"
 
 
-HOST_INPUTS = {"c3": make_c3_sample, "c0": lambda: make_c0(), "c1": lambda: make_c1(8), "c2": lambda: make_c2(8), "c4": lambda: make_c4(256)}
+def cpu_callable(name, h):
+    """The CPU form of workload `name` on sample `h`: the reference's own function when oracle/_ref holds it
+    (kind "reference"), else the PyTorch-on-CPU restatement (kind "port")."""
+    from oracle import make_ref
+    from oracle import torch_port as tp
+    ref = make_ref.load()
+    kind = "reference" if ref else "port"
+    f = lambda t: None if t is None else t.float()
+    if name in ("c1", "c0"):
+        fn = ref["selective_scan"] if ref else tp.selective_scan
+        return (lambda: fn(h["u"], h["delta"], h["A"], h["B"], h["C"], h["D"], h["z"], h["delta_bias"], delta_softplus=True,
+                           return_last_state=True)), kind
+    if name in ("c2", "c3"):
+        x, dt, B, C, z = f(h["x"]), f(h["dt"]), f(h["B"]), f(h["C"]), f(h["z"])
+        if ref:
+            return (lambda: ref["ssd_chunk_scan"](x, dt, h["A"], B, C, 256, D=h["D"], z=z, dt_bias=h["dt_bias"], dt_softplus=True)), kind
+        return (lambda: tp.ssd_chunk_scan(x, dt, h["A"], B, C, 256, h["D"], z, h["dt_bias"], dt_softplus=True)), kind
+    nb, H, P, N = h["state"].shape
+    state = h["state"].clone()
+    fn = ref["selective_state_update"] if ref else tp.selective_state_update
+    return (lambda: fn(state, h["x"], h["dt"][..., None].expand(nb, H, P), h["A"][:, None, None].expand(H, P, N), h["B"], h["C"],
+                       h["D"][:, None].expand(H, P), h["z"], h["dt_bias"][:, None].expand(H, P), dt_softplus=True)), kind
+
+
+def time_cpu(name, budget_s):
+    torch.set_num_threads(os.cpu_count())
+    h, tokens, sample = cpu_inputs(name)
+    fn, kind = cpu_callable(name, h)
+    fn()  # warm-up (allocator, thread pool)
+    reps, t0 = 0, time.perf_counter()
+    while reps < 1 or (time.perf_counter() - t0 < budget_s and reps < 8):
+        fn()
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": tokens / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind, "sample": sample, "reps": reps}
 
 
 # ----------------------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU while the timed region runs.
-
-    NVML is polled directly (a query costs well under a millisecond, so even a 20 ms timed region
-    yields several samples); if the NVML binding is missing, `nvidia-smi` is polled instead."""
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (NVML; nvidia-smi as a fallback)."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -326,60 +391,72 @@ class ClockSampler:
                 "samples": len(sm), "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
-# ----------------------------------------------------------------------------------------- legs
-def time_device(w, steps, warmup, dist, clock_index):
-    for _ in range(warmup):
-        w.step()
+# ----------------------------------------------------------------------------------------- timing
+def all_max(values, dist, dev):
+    if not dist:
+        return list(values)
+    t = torch.tensor(list(values), device=dev, dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return t.tolist()
+
+
+def fence(dist):
     torch.cuda.synchronize()
     if dist:
         torch.distributed.barrier()
         torch.cuda.synchronize()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
-    with ClockSampler(clock_index) as clk:       # samples are taken only while the timed steps run
-        ev[0].record()
-        for i in range(steps):
-            w.step()
-            ev[i + 1].record()
-        torch.cuda.synchronize()
-    if dist:
-        torch.distributed.barrier()
-        torch.cuda.synchronize()
-    return ev[0].elapsed_time(ev[steps]) / 1e3, clk.summary()
+
+
+def time_blocks(w, steps, warmup, dist, clock_index, target_s=0.3):
+    """Median (over R blocks) of the device time of exactly `steps` steps, maximum over ranks per block."""
+    for _ in range(warmup):
+        w.step()
+    fence(dist)
+    # a first block sizes R; it is a warm-up too and is not reported
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        w.step()
+    e1.record()
+    torch.cuda.synchronize()
+    est = all_max([e0.elapsed_time(e1) / 1e3], dist, w.dev)[0]
+    R = int(min(400, max(5, math.ceil(target_s / max(est, 1e-6)))))
+    times = []
+    with ClockSampler(clock_index) as clk:
+        for _ in range(R):
+            fence(dist)
+            e0.record()
+            for _ in range(steps):
+                w.step()
+            e1.record()
+            fence(dist)
+            times.append(e0.elapsed_time(e1) / 1e3)
+    times = sorted(all_max(times, dist, w.dev))
+    return times[len(times) // 2], {"blocks": R, "block_s_min": times[0], "block_s_max": times[-1]}, clk.summary()
 
 
 def time_e2e(w, steps, warmup, dist):
-    """Same pass through the public API from pinned host buffers: H2D of the step's inputs, the
-    kernels, D2H of the step's output, all inside the timed region.
-
-    Batched workloads are fed one batch row at a time on three streams (copy-in, compute, copy-out), so
-    the two PCIe directions and the kernels overlap; every byte of the step's inputs still crosses the
-    bus inside the timed region, every step."""
+    """The headline pass through the public API from pinned host buffers: H2D of the step's inputs, the
+    kernel, D2H of the step's output, all inside the timed region, every step.  Fed one batch row at a time on
+    three streams (copy-in, compute, copy-out), so the two PCIe directions and the kernels overlap."""
     pinned = w.pinned_inputs()
+    nb = pinned["u"].shape[0]
     dev_in = {k: torch.empty_like(v, device=w.dev) for k, v in pinned.items()}
     h2d = sum(v.numel() * v.element_size() for v in pinned.values())
-    probe = w.step({k: v.to(w.dev) for k, v in pinned.items()})
-    res_host = torch.empty(probe.shape, dtype=probe.dtype).pin_memory()
+    res_host = torch.empty(pinned["u"].shape, dtype=pinned["u"].dtype).pin_memory()
     d2h = res_host.numel() * res_host.element_size()
-    del probe
-    nb = next(iter(pinned.values())).shape[0]
-    sliceable = w.name in ("c0", "c1", "c2") and nb > 1 and all(v.shape[0] == nb for v in pinned.values())
     cur = torch.cuda.current_stream(w.dev)
     s_in, s_cmp, s_out = (torch.cuda.Stream(w.dev) for _ in range(3))
     done_prev = [None] * nb
 
-    def one_simple():
-        for k, v in pinned.items():
-            dev_in[k].copy_(v, non_blocking=True)
-        res_host.copy_(w.step(dev_in), non_blocking=True)
-
-    def one_pipelined():
+    def one():
         for st in (s_in, s_cmp, s_out):
             st.wait_stream(cur)
         for i in range(nb):
             sl = slice(i, i + 1)
             with torch.cuda.stream(s_in):
                 if done_prev[i] is not None:
-                    s_in.wait_event(done_prev[i])          # the previous step's kernels have consumed this row
+                    s_in.wait_event(done_prev[i])          # the previous step's kernel has consumed this row
                 for k, v in pinned.items():
                     dev_in[k][sl].copy_(v[sl], non_blocking=True)
                 ready = s_in.record_event()
@@ -394,84 +471,111 @@ def time_e2e(w, steps, warmup, dist):
         cur.wait_stream(s_out)
         cur.wait_stream(s_cmp)
 
-    one = one_pipelined if sliceable else one_simple
     for _ in range(max(1, min(warmup, 3))):
         one()
-    torch.cuda.synchronize()
-    if dist:
-        torch.distributed.barrier()
+    fence(dist)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
         one()
     e1.record()
-    torch.cuda.synchronize()
-    if dist:
-        torch.distributed.barrier()
+    fence(dist)
     return e0.elapsed_time(e1) / 1e3, h2d, d2h
 
 
-def time_cpu(w, budget_s=20.0, min_reps=1):
+def measure(name, dev, rank, world, local, steps, warmup, batch, cpu_budget):
+    """Times one workload; returns (this workload's JSON fields, the Workload)."""
+    dist = world > 1
+    peak_gbs, peak_tf, peak_src = measured_peaks()
+    w = Workload(name, dev, rank, world, batch)
+    t_blk, blocks, clocks = time_blocks(w, steps, warmup, dist, local)
+    per_step = t_blk / steps
+    achieved = w.alg_bytes / per_step / 1e9
+    traffic = NCU_TRAFFIC.get(name) if (world == 1 and not w.reduced) else None
+    out = {
+        "workload": w.desc + (" [REDUCED SIZE: profiling run, not a benchmark result]" if w.reduced else ""),
+        "value": w.global_tokens * steps / t_blk, "unit": UNIT, "ms_per_step": per_step * 1e3, "dtype": w.dtype,
+        "this_gpu": w.shape, "partition": w.partition, "kernels": w.kernels,
+        "gpu_launches": w.launches_per_step * steps, "timing": blocks,
+        "l2_policy": "inputs_exceed_l2" if w.alg_bytes > 2 * 126e6 else "inputs_fit_l2_not_flushed",
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+                     "traffic": traffic[0] if traffic else None, "traffic_source": traffic[1] if traffic else None,
+                     "peak_source": peak_src, "algorithmic_bytes_per_launch": w.alg_bytes,
+                     "per": "this GPU's share of the problem, slowest rank's time"},
+        "clocks": clocks,
+    }
+    if w.flops:
+        tf = w.flops / per_step / 1e12
+        out["roofline"]["tensor"] = {"flops_per_launch": w.flops, "achieved_tflops": tf, "peak_tflops": peak_tf,
+                                     "frac": tf / peak_tf if peak_tf else None,
+                                     "hbm_time_ms": w.alg_bytes / peak_gbs / 1e6, "tensor_time_ms": w.flops / peak_tf / 1e9 if peak_tf else None}
+    if name == "c3" and dist:
+        out["parity"] = w.c3_parity()
+        phases = {}
+        for _ in range(3):
+            w.c3_step(phases=phases)
+        torch.cuda.synchronize()
+        if phases:
+            out["phases_ms"] = {k: round(v, 4) for k, v in phases.items()}
+    if rank == 0 and world == 1 and cpu_budget > 0 and not w.reduced:
+        out["cpu_baseline"] = time_cpu(name, cpu_budget)
+    return out, w
+
+
+def reference_arm(args, rank):
+    """The reference's own CPU implementation of the headline workload on this host's cores (rank 0 only)."""
+    if rank != 0:
+        return 0
+    name = args.only or "c1"
     torch.set_num_threads(os.cpu_count())
-    fn, tokens, sample = cpu_sample(w.name, w.host)
-    fn()  # warm-up (allocator, thread pool)
-    reps, t0 = 0, time.perf_counter()
-    while reps < min_reps or (time.perf_counter() - t0 < budget_s / 2 and reps < 8):
+    h, tokens, sample = cpu_inputs(name)
+    fn, kind = cpu_callable(name, h)
+    budget, t_start = 150.0, time.perf_counter()
+    warm = 0
+    for _ in range(max(1, args.warmup)):
         fn()
-        reps += 1
-    dt = (time.perf_counter() - t0) / reps
-    return tokens / dt, sample, torch.get_num_threads()
-
-
-def max_over_ranks(x, dist, dev):
-    if not dist:
-        return x
-    t = torch.tensor([x], device=dev, dtype=torch.float64)
-    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    return t.item()
+        warm += 1
+        if time.perf_counter() - t_start > budget / 5:
+            break
+    steps, t0 = 0, time.perf_counter()
+    while steps < args.steps and (steps == 0 or time.perf_counter() - t_start < budget):
+        fn()
+        steps += 1
+    dt = (time.perf_counter() - t0) / steps
+    val = tokens / dt
+    note = (f"each step is the bounded sample below, not the whole batch; {steps} of the {args.steps} requested steps and "
+            f"{warm} of the {args.warmup} requested warm-ups fit the wall-clock budget of {budget:.0f} s")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD_DESC[name], "sample_per_step": sample, "note": note},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+    return 0
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c1", choices=["c0", "c1", "c2", "c3", "c4"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default=None, choices=["c0", "c1", "c2", "c3", "c4"],
+                    help="measure this one workload as the headline and skip the others")
+    ap.add_argument("--workload", dest="only", choices=["c0", "c1", "c2", "c3", "c4"], help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--batch", type=int, default=None,
-                    help="shrink the per-GPU batch (for ncu captures of a small case; not a benchmark result)")
+                    help="shrink the problem (for ncu captures of a small case; not a benchmark result)")
     args = ap.parse_args()
     warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    metric, unit = "scan_fwd_tokens_per_s", "tokens/s"
 
     if args.impl == "reference":
-        # The reference's own CPU form of the path (PyTorch restatement), on this host's cores.
-        if rank != 0:
-            return 0
-        torch.set_num_threads(os.cpu_count())
-        fn, tokens, sample = cpu_sample(args.workload, HOST_INPUTS[args.workload]())
-        for _ in range(min(warmup, 1)):
-            fn()
-        steps = min(args.steps, 3)
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            fn()
-        dt = (time.perf_counter() - t0) / steps
-        val = tokens / dt
-        print(json.dumps({
-            "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": steps,
-            "warmup": min(warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD_DESC[args.workload], "sample_per_step": sample},
-            "cpu_baseline": {"value": val, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
-            "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        }))
-        return 0
-
+        return reference_arm(args, rank)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: mamba_b200 has no CPU path")
     dist = world > 1
@@ -479,36 +583,35 @@ def main():
     dev = torch.device("cuda", local)
     if dist:
         torch.distributed.init_process_group("nccl", device_id=dev)
-    w = Workload(args.workload, dev, args.batch)
 
-    t_dev, clocks = time_device(w, args.steps, warmup, dist, local)
-    t_dev = max_over_ranks(t_dev, dist, dev)
-    t_e2e, h2d, d2h = time_e2e(w, max(3, min(args.steps, 10)), warmup, dist)
-    e2e_steps = max(3, min(args.steps, 10))
-    t_e2e = max_over_ranks(t_e2e, dist, dev)
-
-    peak_gbs, _, peak_src = measured_peak_gbs()
-    per_launch_s = t_dev / args.steps
-    achieved = w.alg_bytes / per_launch_s / 1e9
+    head_name = args.only or "c1"
+    cpu_budget = 0 if args.no_cpu_baseline else 8.0
+    head, w = measure(head_name, dev, rank, world, local, args.steps, warmup, args.batch, cpu_budget)
     line = {
-        "metric": metric, "value": world * w.tokens * args.steps / t_dev, "unit": unit, "n_gpus": world,
-        "steps": args.steps, "warmup": warmup, "ms_per_step": per_launch_s * 1e3, "higher_is_better": True,
-        "scaling": "strong" if args.workload == "c3" else "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": w.desc + (" [REDUCED BATCH: profiling run, not a benchmark result]" if w.reduced else ""),
-                   "per_gpu": w.shape,
-                   "partition": ("contiguous chunk ranges per GPU, range states handed rank to rank by NCCL P2P"
-                                 if args.workload == "c3" else "batch rows per GPU, no collective"),
-                   "l2_policy": "inputs_exceed_l2" if w.alg_bytes > 2 * 126e6 else "inputs_fit_l2_not_flushed"},
-        "e2e": {"value": world * w.tokens * e2e_steps / t_e2e, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": w.launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
-                     "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": peak_src,
-                     "algorithmic_bytes_per_launch": w.alg_bytes},
-        "clocks": clocks,
+        "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong" if head_name != "c0" else "weak",
+        "vs_baseline": None, "dtype": head["dtype"], "data": "synthetic",
+        "config": {"workload": head["workload"], "this_gpu": head["this_gpu"], "partition": head["partition"],
+                   "l2_policy": head["l2_policy"], "timing": dict(head["timing"], rule="median of `blocks` blocks of `steps` steps, max over ranks per block")},
+        "gpu_launches": head["gpu_launches"], "kernels": head["kernels"], "roofline": head["roofline"], "clocks": head["clocks"],
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "c3":
-        v, sample, cores = time_cpu(w)
-        line["cpu_baseline"] = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample}
+    if head_name in ("c1", "c0") and not args.no_e2e and w.shape["batch"] > 0:
+        e2e_steps = max(3, min(args.steps, 10))
+        t_e2e, h2d, d2h = time_e2e(w, e2e_steps, warmup, dist)
+        t_e2e = all_max([t_e2e], dist, dev)[0]
+        line["e2e"] = {"value": w.global_tokens * e2e_steps / t_e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "steps": e2e_steps, "bytes": "this GPU's share per step"}
+    if "cpu_baseline" in head:
+        line["cpu_baseline"] = head["cpu_baseline"]
+    del w
+    torch.cuda.empty_cache()
+    if not args.only:
+        line["workloads"] = {}
+        for name in ("c2", "c3", "c4"):
+            res, wl = measure(name, dev, rank, world, local, args.steps, warmup, None, cpu_budget * 0.75)
+            line["workloads"][name] = res
+            del wl
+            torch.cuda.empty_cache()
     if dist:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()

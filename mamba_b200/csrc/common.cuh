@@ -16,6 +16,9 @@ int fail(int code, const char *fmt, ...);
 // Makes `device` current; checks that it is an sm_100 part.  Returns MB200_OK or an error code.
 int enter_device(int device);
 int sm_count(int device);
+// Raises the dynamic shared-memory limit of `kernel` on `device` (which must be current) to at least `bytes`; the
+// runtime is asked once per (kernel, device) and size increase, later calls only consult a small table.
+cudaError_t ensure_dynamic_smem(const void *kernel, int bytes, int device);
 
 #define MB200_CHECK_ARG(cond, ...)                                     \
     do {                                                               \
@@ -156,6 +159,18 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
 {
     uint64_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
 __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b)

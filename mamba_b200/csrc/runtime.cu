@@ -2,6 +2,8 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -49,6 +51,24 @@ int enter_device(int device)
 }
 
 int sm_count(int device) { return g_sm_count[device]; }
+
+cudaError_t ensure_dynamic_smem(const void *kernel, int bytes, int device)
+{
+    struct Entry { const void *kernel; int device, bytes; };
+    static std::mutex mu;
+    static std::vector<Entry> table;
+    std::lock_guard<std::mutex> lock(mu);
+    for (Entry &e : table)
+        if (e.kernel == kernel && e.device == device) {
+            if (e.bytes >= bytes) return cudaSuccess;
+            const cudaError_t rc = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+            if (rc == cudaSuccess) e.bytes = bytes;
+            return rc;
+        }
+    const cudaError_t rc = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (rc == cudaSuccess) table.push_back({kernel, device, bytes});
+    return rc;
+}
 
 bool debug_sync()
 {

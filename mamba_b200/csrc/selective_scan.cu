@@ -938,7 +938,7 @@ int launch_scan(const mb200_scan_args &a, cudaStream_t stream)
     }
     const size_t smem = sizeof(float) * (2 * kStateBlock * kTile + 2 * (size_t)chans * npad);
     static_assert(2 * kStateBlock * kTile * sizeof(float) + 2 * kWarps * 2 * 256 * sizeof(float) <= 227 * 1024, "smem budget");
-    cudaError_t e = cudaFuncSetAttribute(scan_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(&scan_fwd_kernel<T>), (int)smem, a.device);
     if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "selective_scan: shared memory opt-in (%zu B): %s", smem, cudaGetErrorString(e));
     const int tiles_per_group = (per_group + chans - 1) / chans;
     dim3 grid(a.ngroups * tiles_per_group, a.batch);

@@ -428,9 +428,9 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     if (a.phases & MB200_SSD_PHASE_LOCAL) {
         const size_t cs_smem = sizeof(float) * Q * 33;
         if (cs_smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(ssd_cumsum_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(ssd_cumsum_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(ssd_cumsum_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cs_smem);
+            cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_cumsum_kernel<float>), (int)cs_smem, a.device);
+            if (e == cudaSuccess) e = ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_cumsum_kernel<__nv_bfloat16>), (int)cs_smem, a.device);
+            if (e == cudaSuccess) e = ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_cumsum_kernel<__half>), (int)cs_smem, a.device);
             if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd chunk_cumsum: shared memory opt-in: %s", cudaGetErrorString(e));
         }
         // C.B^T needs nothing the other stages produce: when the whole operator runs on the tensor-core path it goes
@@ -541,7 +541,7 @@ extern "C" int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream
     const mb200_ssd_args &a = *args;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (int rc = check_ssd(a)) return rc;
-    MB200_CHECK_ARG(!(a.phases & MB200_SSD_PHASE_OUTPUT) || a.out, "ssd: out is NULL");
+    MB200_CHECK_ARG(!(a.phases & MB200_SSD_PHASE_OUTPUT) || a.out || a.seqlen == 0 || a.batch == 0, "ssd: out is NULL");
     MB200_CHECK_ARG(!a.cu_seqlens || a.batch == 1, "passing cu_seqlens to get the varlen states is only supported if batch dimension is 1");
     MB200_CHECK_ARG(!a.cu_seqlens || (a.num_seqs >= 0 && a.num_seqs <= 65535), "ssd: num_seqs must be in [0, 65535]");
     MB200_CHECK_ARG(!(a.seq_idx || a.cu_seqlens) || a.phases == MB200_SSD_PHASE_ALL, "ssd: packed sequences cannot be combined with a sequence split");

@@ -1008,14 +1008,14 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         int64_t paired = pairs / sms * sms;
         if (pairs - paired > sms / 2) paired = pairs;
         if (paired > 0) {
-            cudaFuncSetAttribute(ssd_tc_state_stream_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamCfg<2>::kSmem);
+            ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_state_stream_kernel<T, 2>), (int)StreamCfg<2>::kSmem, a.device);
             ssd_tc_state_stream_kernel<T, 2><<<(unsigned)paired, kStreamThreads, StreamCfg<2>::kSmem, stream>>>(
                 tx, tB, tHs, dtb, dAb, init, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1, nc, a.nheads, hpg, 0, status);
             MB200_CHECK_LAUNCH("ssd state stream (tensor core, head pairs)");
         }
         const int64_t singles = (int64_t)a.batch * a.nheads - 2 * paired;
         if (singles > 0) {
-            cudaFuncSetAttribute(ssd_tc_state_stream_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamCfg<1>::kSmem);
+            ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_state_stream_kernel<T, 1>), (int)StreamCfg<1>::kSmem, a.device);
             ssd_tc_state_stream_kernel<T, 1><<<(unsigned)singles, kStreamThreads, StreamCfg<1>::kSmem, stream>>>(
                 tx, tB, tHs, dtb, dAb, init, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1, nc, a.nheads, hpg,
                 (int)(2 * paired), status);
@@ -1024,7 +1024,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         return MB200_OK;
     }
     if (stage == 0) {
-        cudaFuncSetAttribute(ssd_tc_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_state);
+        ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_chunk_state_kernel<T>), (int)smem_state, a.device);
         ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kStateThreads, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
                                                                                                    a.nheads / a.ngroups, status);
         MB200_CHECK_LAUNCH("ssd chunk_state (tensor core)");
@@ -1059,12 +1059,12 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         }
     }
     if (parts & 1) {
-        cudaFuncSetAttribute(ssd_tc_cb_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cb);
+        ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_cb_kernel<T>), (int)smem_cb, a.device);
         ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
         MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
     }
     if (parts & 2) {
-        cudaFuncSetAttribute(ssd_tc_chunk_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scan);
+        ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_chunk_scan_kernel<T>), (int)smem_scan, a.device);
         ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, h_np ? 1 : 0, status);
         MB200_CHECK_LAUNCH("ssd chunk_scan (tensor core)");
     }

@@ -24,6 +24,7 @@ the process group's timeout; a missing peer surfaces as ``SequenceHandoffError``
 The compute steps are injectable so that the hand-off logic can be exercised by CPU ranks (gloo) in
 tests; the defaults are this package's CUDA operators.
 """
+import time
 from dataclasses import dataclass
 from typing import Callable, Optional
 
@@ -90,23 +91,53 @@ def _gather_summaries(state: torch.Tensor, decay: torch.Tensor, group):
     return states, decays, everyone
 
 
+class _PhaseClock:
+    """Device time stamps between the phases of one call (CUDA events on the current stream) plus the host time the
+    call spent enqueueing; fills a caller-supplied dict with milliseconds when the call ends (synchronises)."""
+
+    def __init__(self, sink, cuda):
+        self.sink, self.cuda, self.marks = sink, cuda and sink is not None, []
+        self.t_host = time.perf_counter()
+        self.mark("start")
+
+    def mark(self, name):
+        if self.cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((name, ev))
+
+    def finish(self):
+        if self.sink is None:
+            return
+        self.sink["host_enqueue"] = (time.perf_counter() - self.t_host) * 1e3
+        if self.cuda:
+            torch.cuda.synchronize()
+            for (_, a), (name, b) in zip(self.marks, self.marks[1:]):
+                self.sink[name] = a.elapsed_time(b)
+            self.sink["total_device"] = self.marks[0][1].elapsed_time(self.marks[-1][1])
+
+
 def mamba_chunk_scan_sequence_parallel(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bias=None, initial_states=None,
                                        dt_softplus=False, dt_limit=(0.0, float("inf")), return_final_states=False,
-                                       group=None, steps: Optional[SsdSteps] = None, handoff: Optional[str] = None):
+                                       group=None, steps: Optional[SsdSteps] = None, handoff: Optional[str] = None,
+                                       phases: Optional[dict] = None):
     """Run this rank's slice of a sequence that is split over the ranks of `group`.
 
     x, dt, B, C, z hold THIS rank's contiguous tokens (a whole number of chunks on every rank but the
     last); A, D, dt_bias are replicated; ``initial_states`` (state before the first token of the whole
     sequence) is only read on rank 0.  ``handoff`` is "chain", "gather" or None (gather above two ranks).
     Returns this rank's ``out`` and, if asked, the state after this rank's last token -- on the last
-    rank that is the final state of the whole sequence.
+    rank that is the final state of the whole sequence.  ``phases`` (a dict) receives the device time of every
+    phase of this call in milliseconds and the host time spent enqueueing it; asking for it synchronises.
     """
     steps = steps or SsdSteps()
     rank, world = dist.get_rank(group), dist.get_world_size(group)
+    clock = _PhaseClock(phases, x.is_cuda)
     if rank < world - 1:
         assert x.shape[1] % chunk_size == 0, "every rank but the last must hold whole chunks"
     range_state, range_decay, scratch = steps.local(x, dt, A, B, chunk_size, dt_bias=dt_bias, dt_softplus=dt_softplus,
                                                     dt_limit=dt_limit)
+    clock.mark("local")
     if handoff is None:
         handoff = "gather" if world > 2 else "chain"
     assert handoff in ("chain", "gather"), "handoff must be 'chain' or 'gather'"
@@ -129,5 +160,9 @@ def mamba_chunk_scan_sequence_parallel(x, dt, A, B, C, chunk_size, D=None, z=Non
             incoming = states[0]
             for r in range(1, rank):
                 incoming = steps.fold(incoming, decays[r], states[r])
-    return steps.finish(x, dt, A, B, C, chunk_size, scratch, D=D, z=z, dt_bias=dt_bias, incoming_state=incoming,
-                        dt_softplus=dt_softplus, dt_limit=dt_limit, return_final_states=return_final_states)
+    clock.mark("handoff")
+    res = steps.finish(x, dt, A, B, C, chunk_size, scratch, D=D, z=z, dt_bias=dt_bias, incoming_state=incoming,
+                       dt_softplus=dt_softplus, dt_limit=dt_limit, return_final_states=return_final_states)
+    clock.mark("output")
+    clock.finish()
+    return res
