@@ -145,11 +145,15 @@ int mb200_selective_state_update(const mb200_ssu_args *args, void *stream);
  *   the state at the end of the local range into final_states plus the product of the chunk decays
  *   into range_decay), exchanges states, then MB200_SSD_PHASE_OUTPUT with initial_states set to the
  *   incoming state (inter-chunk recurrence and chunk outputs; scratch must be untouched in between).
+ *   C.B^T needs nothing from the exchange: a LOCAL call with MB200_SSD_PHASE_CB added (and C given) computes it as
+ *   well, ahead of the exchange, and the OUTPUT call is then told so with MB200_SSD_PHASE_CB_READY.
  * range_decay : optional (batch, nheads) fp32, written in the LOCAL phase.
  */
-#define MB200_SSD_PHASE_LOCAL  1
-#define MB200_SSD_PHASE_OUTPUT 2
-#define MB200_SSD_PHASE_ALL    3
+#define MB200_SSD_PHASE_LOCAL    1
+#define MB200_SSD_PHASE_OUTPUT   2
+#define MB200_SSD_PHASE_ALL      3
+#define MB200_SSD_PHASE_CB       4   /* with LOCAL alone: also form C.B^T in the scratch                    */
+#define MB200_SSD_PHASE_CB_READY 8   /* with OUTPUT alone: the scratch already holds C.B^T of these inputs */
 
 typedef struct mb200_ssd_args {
     const void *x, *dt;
@@ -228,6 +232,74 @@ int mb200_ssd_fold_state(const float *s_in, const float *range_decay, const floa
  */
 int mb200_ssd_fold_ranges(const float *summaries, int64_t record_stride, int32_t first, int32_t last, float *s_out,
                           int64_t rows, int64_t row, int32_t device, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * The element-wise steps either side of the scan inside the Mamba mixers.
+ *
+ * Causal depthwise conv1d, optionally followed by SiLU.  Replaces causal_conv1d_fn of the causal-conv1d package
+ * (a dependency the reference does not vendor) as the mixers call it -- mamba_ssm/modules/mamba2.py:236-242,
+ * mamba_ssm/modules/mamba_simple.py:172-177 -- whose CPU form is the depthwise nn.Conv1d with left padding at
+ * mamba2.py:232-234:   out[b,c,t] = act(bias[c] + sum_k weight[c,k] * x[b,c,t - (width-1) + k]),  x = 0 before the start.
+ *
+ * x, out : (batch, dim, seqlen) io_dtype with strides {batch, dim, seq}; either layout (time or channels contiguous).
+ * weight : (dim, width) contiguous, bias : optional (dim), both w_dtype.  width 2..4.
+ * seq_idx : optional int32 (batch, seqlen) contiguous: taps that reach into another packed sequence read zero.
+ * initial_states : optional (batch, dim, width-1) io_dtype, the inputs before t = 0.
+ * final_states   : optional (batch, dim, width-1) io_dtype, receives the last width-1 inputs (the decode conv state).
+ */
+typedef struct mb200_conv1d_args {
+    const void *x, *weight, *bias;
+    const int32_t *seq_idx;
+    const void *initial_states;
+    void *final_states;
+    void *out;
+    int32_t batch, dim, seqlen, width;
+    int32_t io_dtype, w_dtype;
+    int32_t activation;               /* 0 none, 1 silu */
+    int32_t device;
+    int64_t x_stride[3], out_stride[3], init_stride[3], final_stride[3];
+} mb200_conv1d_args;
+
+int mb200_causal_conv1d_fwd(const mb200_conv1d_args *args, void *stream);
+
+/* Single-token form (causal_conv1d_update of the same package; the reference's own code for it is the roll /
+ * multiply / sum at mamba_ssm/modules/mamba2.py:309-315).  conv_state (batch, dim, state_len >= width-1) is shifted
+ * left by one and x appended, in place; out[b,c] = act(bias[c] + sum_k weight[c,k] * window[k]) over the last width-1
+ * old entries followed by x.  x, out : (batch, dim) io_dtype with strides {batch, dim}. */
+typedef struct mb200_conv1d_update_args {
+    const void *x, *weight, *bias;
+    void *conv_state;
+    void *out;
+    int32_t batch, dim, width, state_len;
+    int32_t io_dtype, w_dtype;
+    int32_t activation;
+    int32_t device;
+    int64_t x_stride[2], out_stride[2], state_stride[3];
+} mb200_conv1d_update_args;
+
+int mb200_causal_conv1d_update(const mb200_conv1d_update_args *args, void *stream);
+
+/* Gated RMSNorm after the SSD scan.  Replaces the launch in rmsnorm_fn / RMSNorm.forward
+ * (mamba_ssm/ops/triton/layernorm_gated.py:415-437; definition rms_norm_ref :18-41), used at
+ * mamba_ssm/modules/mamba2.py:269-270, 338-339:
+ *   norm_before_gate = 1 :  out = x * rstd * weight (+ bias), then * silu(z)
+ *   norm_before_gate = 0 :  x <- x * silu(z) first, then out = x * rstd * weight (+ bias)
+ * with rstd = 1 / sqrt(mean(x^2) + eps) taken over each group of group_size consecutive columns.
+ * x, z, out : (nrows, ncols) io_dtype, unit column stride, row strides given; weight, bias : (ncols) w_dtype. */
+typedef struct mb200_rmsnorm_args {
+    const void *x, *z, *weight, *bias;
+    void *out;
+    int64_t nrows;
+    int32_t ncols, group_size;
+    int32_t io_dtype, w_dtype;
+    int32_t norm_before_gate;
+    float eps;
+    int32_t device;
+    int32_t reserved_;
+    int64_t x_stride, z_stride, out_stride;
+} mb200_rmsnorm_args;
+
+int mb200_rmsnorm_gated_fwd(const mb200_rmsnorm_args *args, void *stream);
 
 #ifdef __cplusplus
 }

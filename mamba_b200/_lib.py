@@ -15,7 +15,7 @@ F32, F16, BF16 = 0, 1, 2
 _DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_NO_DEVICE = 0, -1, -2, -3, -4
-PHASE_LOCAL, PHASE_OUTPUT, PHASE_ALL = 1, 2, 3
+PHASE_LOCAL, PHASE_OUTPUT, PHASE_ALL, PHASE_CB, PHASE_CB_READY = 1, 2, 3, 4, 8
 SSD_STATIC_SCRATCH_BYTES = 32 << 20
 
 c_i32, c_i64, c_vp, c_f = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
@@ -63,6 +63,34 @@ class SsdArgs(ctypes.Structure):
     ]
 
 
+class Conv1dArgs(ctypes.Structure):
+    _fields_ = [
+        ("x", c_vp), ("weight", c_vp), ("bias", c_vp), ("seq_idx", c_vp), ("initial_states", c_vp), ("final_states", c_vp),
+        ("out", c_vp),
+        ("batch", c_i32), ("dim", c_i32), ("seqlen", c_i32), ("width", c_i32), ("io_dtype", c_i32), ("w_dtype", c_i32),
+        ("activation", c_i32), ("device", c_i32),
+        ("x_stride", c_i64 * 3), ("out_stride", c_i64 * 3), ("init_stride", c_i64 * 3), ("final_stride", c_i64 * 3),
+    ]
+
+
+class Conv1dUpdateArgs(ctypes.Structure):
+    _fields_ = [
+        ("x", c_vp), ("weight", c_vp), ("bias", c_vp), ("conv_state", c_vp), ("out", c_vp),
+        ("batch", c_i32), ("dim", c_i32), ("width", c_i32), ("state_len", c_i32), ("io_dtype", c_i32), ("w_dtype", c_i32),
+        ("activation", c_i32), ("device", c_i32),
+        ("x_stride", c_i64 * 2), ("out_stride", c_i64 * 2), ("state_stride", c_i64 * 3),
+    ]
+
+
+class RmsNormArgs(ctypes.Structure):
+    _fields_ = [
+        ("x", c_vp), ("z", c_vp), ("weight", c_vp), ("bias", c_vp), ("out", c_vp),
+        ("nrows", c_i64), ("ncols", c_i32), ("group_size", c_i32), ("io_dtype", c_i32), ("w_dtype", c_i32),
+        ("norm_before_gate", c_i32), ("eps", c_f), ("device", c_i32), ("reserved_", c_i32),
+        ("x_stride", c_i64), ("z_stride", c_i64), ("out_stride", c_i64),
+    ]
+
+
 # every symbol include/mamba_b200.h declares, with its prototype
 _PROTOTYPES = {
     "mb200_version": (ctypes.c_int, []),
@@ -76,6 +104,9 @@ _PROTOTYPES = {
     "mb200_ssd_static_status": (ctypes.c_int, [ctypes.POINTER(SsdArgs), ctypes.POINTER(c_i32)]),
     "mb200_ssd_fold_state": (ctypes.c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_vp]),
     "mb200_ssd_fold_ranges": (ctypes.c_int, [c_vp, c_i64, c_i32, c_i32, c_vp, c_i64, c_i64, c_i32, c_vp]),
+    "mb200_causal_conv1d_fwd": (ctypes.c_int, [ctypes.POINTER(Conv1dArgs), c_vp]),
+    "mb200_causal_conv1d_update": (ctypes.c_int, [ctypes.POINTER(Conv1dUpdateArgs), c_vp]),
+    "mb200_rmsnorm_gated_fwd": (ctypes.c_int, [ctypes.POINTER(RmsNormArgs), c_vp]),
 }
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)
 

@@ -1,0 +1,384 @@
+// The two element-wise steps either side of the scan in the Mamba mixers, for sm_100a:
+//   causal depthwise conv1d (+ SiLU) before the scan -- prefill form and single-token decode form;
+//   gated RMSNorm (optionally per group) after the SSD scan.
+// Both are pure streaming work (every input read once, every output written once), so the kernels are built
+// around 16-byte accesses and keep everything else in registers.
+#include "common.cuh"
+
+namespace mb200 {
+namespace {
+
+constexpr int kMaxWidth = 4;
+
+__device__ __forceinline__ float act_silu(float v, int activation) { return activation ? v / (1.f + __expf(-v)) : v; }
+
+// ---- conv1d, channels contiguous (the layout Mamba-2 hands over: a (batch, seqlen, dim) tensor viewed as
+// (batch, dim, seqlen)).  A thread owns VEC adjacent channels and walks a segment of the sequence with the last
+// width-1 rows of its channels in registers, so every row is read once (plus width-1 rows of halo per segment).
+template <typename T>
+__global__ void __launch_bounds__(128) conv1d_cl_kernel(const mb200_conv1d_args a, const int seg)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int K = kMaxWidth;
+    const int c0 = (blockIdx.x * 128 + threadIdx.x) * VEC;
+    if (c0 >= a.dim) return;
+    const int b = blockIdx.z;
+    const int t_begin = blockIdx.y * seg, t_end = min(t_begin + seg, a.seqlen);
+    const int W = a.width, lead = K - W;        // taps are kept right-aligned: tap k of K reads step t - (K-1) + k, the first `lead` weigh 0
+    float w[K][VEC], bias[VEC], win[K - 1][VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        bias[i] = a.bias ? load_any(a.bias, a.w_dtype, c0 + i) : 0.f;
+#pragma unroll
+        for (int k = 0; k < K; ++k) w[k][i] = k >= lead ? load_any(a.weight, a.w_dtype, (int64_t)(c0 + i) * W + (k - lead)) : 0.f;
+    }
+    const T *x = static_cast<const T *>(a.x) + (int64_t)b * a.x_stride[0] + c0;
+    T *out = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + c0;
+    const int32_t *sid = a.seq_idx ? a.seq_idx + (int64_t)b * a.seqlen : nullptr;
+    auto row = [&](int t, float (&v)[VEC]) {       // x[:, t] for my channels; before the sequence: the initial state or zero
+        if (t >= 0) {
+            Vec16<T> p;
+            p.load(x + (int64_t)t * a.x_stride[2]);
+            p.unpack(v);
+        } else if (a.initial_states && t >= -(W - 1)) {
+            const T *st = static_cast<const T *>(a.initial_states) + (int64_t)b * a.init_stride[0];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[i] = to_float(st[(int64_t)(c0 + i) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[i] = 0.f;
+        }
+    };
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+        if (j >= lead) {
+            row(t_begin - (K - 1) + j, win[j]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) win[j][i] = 0.f;
+        }
+    }
+    for (int t = t_begin; t < t_end; ++t) {
+        float cur[VEC], acc[VEC];
+        row(t, cur);
+        bool keep[K - 1];                           // taps that reach into another packed sequence contribute nothing
+#pragma unroll
+        for (int j = 0; j < K - 1; ++j) {
+            const int tj = t - (K - 1) + j;
+            keep[j] = j >= lead && (!sid || tj < 0 || sid[tj] == sid[t]);
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            float s = fmaf(w[K - 1][i], cur[i], bias[i]);
+#pragma unroll
+            for (int j = 0; j < K - 1; ++j)
+                if (keep[j]) s = fmaf(w[j][i], win[j][i], s);
+            acc[i] = act_silu(s, a.activation);
+        }
+        Vec16<T> o;
+        o.pack(acc);
+        o.store(out + (int64_t)t * a.out_stride[2]);
+#pragma unroll
+        for (int j = 0; j < K - 2; ++j)
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) win[j][i] = win[j + 1][i];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) win[K - 2][i] = cur[i];
+    }
+    if (a.final_states && t_end == a.seqlen) {      // the last width-1 inputs (reaching back into the initial state if need be)
+        T *fs = static_cast<T *>(a.final_states) + (int64_t)b * a.final_stride[0];
+        for (int j = 0; j < W - 1; ++j) {
+            float v[VEC];
+            row(a.seqlen - (W - 1) + j, v);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) fs[(int64_t)(c0 + i) * a.final_stride[1] + (int64_t)j * a.final_stride[2]] = from_float<T>(v[i]);
+        }
+    }
+}
+
+// ---- conv1d, any strides (the Mamba-1 layout, time contiguous, among them): one thread per (channel, run of
+// kRun steps); neighbouring threads walk neighbouring runs of the same row, so the row is read in whole sectors.
+constexpr int kRun = 8;
+template <typename T>
+__global__ void __launch_bounds__(256) conv1d_any_kernel(const mb200_conv1d_args a)
+{
+    constexpr int K = kMaxWidth;
+    const int runs = (a.seqlen + kRun - 1) / kRun;
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int r = (int)(idx % runs);
+    const int c = (int)(idx / runs);
+    const int b = blockIdx.y;
+    if (c >= a.dim) return;
+    const int W = a.width, lead = K - W;
+    float w[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) w[k] = k >= lead ? load_any(a.weight, a.w_dtype, (int64_t)c * W + (k - lead)) : 0.f;
+    const float bias = a.bias ? load_any(a.bias, a.w_dtype, c) : 0.f;
+    const T *x = static_cast<const T *>(a.x) + (int64_t)b * a.x_stride[0] + (int64_t)c * a.x_stride[1];
+    T *out = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + (int64_t)c * a.out_stride[1];
+    const int32_t *sid = a.seq_idx ? a.seq_idx + (int64_t)b * a.seqlen : nullptr;
+    auto at = [&](int t) -> float {
+        if (t >= a.seqlen || t < -(W - 1)) return 0.f;
+        if (t >= 0) return to_float(x[(int64_t)t * a.x_stride[2]]);
+        if (a.initial_states)
+            return to_float(static_cast<const T *>(a.initial_states)[(int64_t)b * a.init_stride[0] + (int64_t)c * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]);
+        return 0.f;
+    };
+    const int t0 = r * kRun;
+    float v[kRun + K - 1];                          // v[i] = x[t0 - (K-1) + i]
+#pragma unroll
+    for (int i = 0; i < kRun + K - 1; ++i) v[i] = at(t0 - (K - 1) + i);
+#pragma unroll
+    for (int i = 0; i < kRun; ++i) {
+        const int t = t0 + i;
+        if (t < a.seqlen) {
+            float s = bias;
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const int tk = t - (K - 1) + k;     // tap k reads step tk
+                if (k >= lead && (!sid || tk < 0 || sid[tk] == sid[t])) s = fmaf(w[k], v[i + k], s);
+            }
+            out[(int64_t)t * a.out_stride[2]] = from_float<T>(act_silu(s, a.activation));
+        }
+    }
+    if (a.final_states && r == runs - 1) {
+        T *fs = static_cast<T *>(a.final_states) + (int64_t)b * a.final_stride[0] + (int64_t)c * a.final_stride[1];
+        for (int j = 0; j < W - 1; ++j) fs[(int64_t)j * a.final_stride[2]] = from_float<T>(at(a.seqlen - (W - 1) + j));
+    }
+}
+
+// ---- decode: one new token per sequence.  conv_state (batch, dim, state_len >= width-1) is shifted left by one
+// and the token appended; out = act(bias + sum_k w[k] * window[k]) over the last width-1 old entries and the token.
+template <typename T>
+__global__ void __launch_bounds__(256) conv1d_update_kernel(const mb200_conv1d_update_args a)
+{
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= (int64_t)a.batch * a.dim) return;
+    const int b = (int)(idx / a.dim), c = (int)(idx % a.dim);
+    const int W = a.width, S = a.state_len;
+    T *st = static_cast<T *>(a.conv_state) + (int64_t)b * a.state_stride[0] + (int64_t)c * a.state_stride[1];
+    const T xt = static_cast<const T *>(a.x)[(int64_t)b * a.x_stride[0] + (int64_t)c * a.x_stride[1]];
+    float s = a.bias ? load_any(a.bias, a.w_dtype, c) : 0.f;
+    s = fmaf(load_any(a.weight, a.w_dtype, (int64_t)c * W + W - 1), to_float(xt), s);
+    for (int j = 0; j < S; ++j) {                   // every old entry is read once and moved one place to the left
+        const T old = st[(int64_t)j * a.state_stride[2]];
+        const int k = j - (S - (W - 1));            // old entry j is tap k when it is among the last width-1
+        if (k >= 0) s = fmaf(load_any(a.weight, a.w_dtype, (int64_t)c * W + k), to_float(old), s);
+        if (j > 0) st[(int64_t)(j - 1) * a.state_stride[2]] = old;
+    }
+    st[(int64_t)(S - 1) * a.state_stride[2]] = xt;
+    static_cast<T *>(a.out)[(int64_t)b * a.out_stride[0] + (int64_t)c * a.out_stride[1]] = from_float<T>(act_silu(s, a.activation));
+}
+
+// ---- gated RMSNorm: one CTA per (row, group).  y = x * rstd * weight (+ bias) with the gate silu(z) applied to x
+// before the statistics (norm_before_gate = 0) or to y after them (= 1); all arithmetic in fp32.
+template <typename T, int PER>      // PER 16-byte packets per thread
+__global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const mb200_rmsnorm_args a, const int threads)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ float red[8];
+    const int64_t rowi = blockIdx.x;
+    const int g = blockIdx.y;
+    const int G = a.group_size;
+    const T *x = static_cast<const T *>(a.x) + rowi * a.x_stride + (int64_t)g * G;
+    const T *z = a.z ? static_cast<const T *>(a.z) + rowi * a.z_stride + (int64_t)g * G : nullptr;
+    T *out = static_cast<T *>(a.out) + rowi * a.out_stride + (int64_t)g * G;
+    float v[PER][VEC], zs[PER][VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+        const int e = (p * threads + threadIdx.x) * VEC;
+        if (e < G) {
+            Vec16<T> px;
+            px.load(x + e);
+            px.unpack(v[p]);
+            if (z) {
+                Vec16<T> pz;
+                pz.load(z + e);
+                pz.unpack(zs[p]);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) zs[p][i] = zs[p][i] / (1.f + __expf(-zs[p][i]));
+                if (!a.norm_before_gate) {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) v[p][i] *= zs[p][i];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) ss = fmaf(v[p][i], v[p][i], ss);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (threads + 31) / 32; ++i) tot += red[i];
+    const float rstd = rsqrtf(tot / (float)G + a.eps);
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+        const int e = (p * threads + threadIdx.x) * VEC;
+        if (e < G) {
+            float y[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                const int col = g * G + e + i;
+                y[i] = v[p][i] * rstd * load_any(a.weight, a.w_dtype, col);
+                if (a.bias) y[i] += load_any(a.bias, a.w_dtype, col);
+                if (z && a.norm_before_gate) y[i] *= zs[p][i];
+            }
+            Vec16<T> po;
+            po.pack(y);
+            po.store(out + e);
+        }
+    }
+}
+
+// general form: any group size and alignment, one warp per (row, group), two passes over the row
+template <typename T>
+__global__ void __launch_bounds__(32) rmsnorm_gated_any_kernel(const mb200_rmsnorm_args a)
+{
+    const int64_t rowi = blockIdx.x;
+    const int g = blockIdx.y, G = a.group_size, lane = threadIdx.x;
+    const T *x = static_cast<const T *>(a.x) + rowi * a.x_stride + (int64_t)g * G;
+    const T *z = a.z ? static_cast<const T *>(a.z) + rowi * a.z_stride + (int64_t)g * G : nullptr;
+    T *out = static_cast<T *>(a.out) + rowi * a.out_stride + (int64_t)g * G;
+    auto gated = [&](int e, float &gate) {
+        float v = to_float(x[e]);
+        gate = 1.f;
+        if (z) {
+            const float zz = to_float(z[e]);
+            gate = zz / (1.f + __expf(-zz));
+            if (!a.norm_before_gate) v *= gate;
+        }
+        return v;
+    };
+    float ss = 0.f, gate;
+    for (int e = lane; e < G; e += 32) {
+        const float v = gated(e, gate);
+        ss = fmaf(v, v, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss / (float)G + a.eps);
+    for (int e = lane; e < G; e += 32) {
+        const float v = gated(e, gate);
+        float y = v * rstd * load_any(a.weight, a.w_dtype, g * G + e);
+        if (a.bias) y += load_any(a.bias, a.w_dtype, g * G + e);
+        if (z && a.norm_before_gate) y *= gate;
+        out[e] = from_float<T>(y);
+    }
+}
+
+bool valid_dtype(int d) { return d == MB200_F32 || d == MB200_F16 || d == MB200_BF16; }
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T>
+int launch_conv1d(const mb200_conv1d_args &a, cudaStream_t stream)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    const bool channels_last = a.x_stride[1] == 1 && a.out_stride[1] == 1 && a.dim % VEC == 0 && aligned16(a.x) && aligned16(a.out) &&
+                               a.x_stride[0] % VEC == 0 && a.x_stride[2] % VEC == 0 && a.out_stride[0] % VEC == 0 && a.out_stride[2] % VEC == 0;
+    if (channels_last) {
+        const int cols = (a.dim / VEC + 127) / 128;
+        // enough segments to fill the GPU several times over, long enough that the halo rows stay a few per cent
+        int seg = 64;
+        while (seg > 16 && (int64_t)cols * a.batch * ((a.seqlen + seg - 1) / seg) < 4 * 148) seg /= 2;
+        conv1d_cl_kernel<T><<<dim3(cols, (a.seqlen + seg - 1) / seg, a.batch), 128, 0, stream>>>(a, seg);
+    } else {
+        const int64_t work = (int64_t)a.dim * ((a.seqlen + kRun - 1) / kRun);
+        conv1d_any_kernel<T><<<dim3((unsigned)((work + 255) / 256), a.batch), 256, 0, stream>>>(a);
+    }
+    return MB200_OK;
+}
+
+template <typename T>
+int launch_rmsnorm(const mb200_rmsnorm_args &a, cudaStream_t stream)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    const int G = a.group_size, ngroups = a.ncols / G;
+    const bool vec_ok = G % VEC == 0 && aligned16(a.x) && aligned16(a.out) && (!a.z || aligned16(a.z)) && a.x_stride % VEC == 0 &&
+                        a.out_stride % VEC == 0 && (!a.z || a.z_stride % VEC == 0) && G <= 256 * 4 * VEC;
+    dim3 grid((unsigned)a.nrows, ngroups);
+    if (!vec_ok) {
+        rmsnorm_gated_any_kernel<T><<<grid, 32, 0, stream>>>(a);
+        return MB200_OK;
+    }
+    const int packets = G / VEC;
+    int threads = 32;
+    while (threads < 256 && threads * 2 <= packets) threads *= 2;      // a packet or two per thread while the group allows
+    const int per = (packets + threads - 1) / threads;
+    if (per <= 1) rmsnorm_gated_kernel<T, 1><<<grid, threads, 0, stream>>>(a, threads);
+    else if (per <= 2) rmsnorm_gated_kernel<T, 2><<<grid, threads, 0, stream>>>(a, threads);
+    else rmsnorm_gated_kernel<T, 4><<<grid, threads, 0, stream>>>(a, threads);
+    return MB200_OK;
+}
+
+}  // namespace
+}  // namespace mb200
+
+extern "C" int mb200_causal_conv1d_fwd(const mb200_conv1d_args *args, void *stream_)
+{
+    using namespace mb200;
+    if (!args) return fail(MB200_ERR_BAD_ARG, "causal_conv1d_fwd: args is NULL");
+    const mb200_conv1d_args &a = *args;
+    MB200_CHECK_ARG(a.batch >= 0 && a.dim > 0 && a.seqlen >= 0, "causal_conv1d_fwd: bad sizes (batch %d dim %d seqlen %d)", a.batch, a.dim, a.seqlen);
+    MB200_CHECK_ARG(a.width >= 2 && a.width <= kMaxWidth, "causal_conv1d only supports width between 2 and 4");
+    MB200_CHECK_ARG(valid_dtype(a.io_dtype) && valid_dtype(a.w_dtype), "causal_conv1d_fwd: unknown dtype code");
+    MB200_CHECK_ARG(a.activation == 0 || a.activation == 1, "causal_conv1d_fwd: activation must be 0 (none) or 1 (silu)");
+    MB200_CHECK_ARG(a.batch <= 65535, "causal_conv1d_fwd: batch must be <= 65535");
+    if (a.batch == 0 || a.seqlen == 0) return MB200_OK;
+    MB200_CHECK_ARG(a.x && a.weight && a.out, "causal_conv1d_fwd: a required tensor is NULL");
+    if (int rc = enter_device(a.device)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc;
+    if (a.io_dtype == MB200_F32) rc = launch_conv1d<float>(a, stream);
+    else if (a.io_dtype == MB200_BF16) rc = launch_conv1d<__nv_bfloat16>(a, stream);
+    else rc = launch_conv1d<__half>(a, stream);
+    if (rc) return rc;
+    MB200_CHECK_LAUNCH("causal_conv1d_fwd");
+    return MB200_OK;
+}
+
+extern "C" int mb200_causal_conv1d_update(const mb200_conv1d_update_args *args, void *stream_)
+{
+    using namespace mb200;
+    if (!args) return fail(MB200_ERR_BAD_ARG, "causal_conv1d_update: args is NULL");
+    const mb200_conv1d_update_args &a = *args;
+    MB200_CHECK_ARG(a.batch >= 0 && a.dim > 0, "causal_conv1d_update: bad sizes (batch %d dim %d)", a.batch, a.dim);
+    MB200_CHECK_ARG(a.width >= 2 && a.width <= kMaxWidth, "causal_conv1d only supports width between 2 and 4");
+    MB200_CHECK_ARG(a.state_len >= a.width - 1, "causal_conv1d_update: conv_state must hold at least width - 1 steps");
+    MB200_CHECK_ARG(valid_dtype(a.io_dtype) && valid_dtype(a.w_dtype), "causal_conv1d_update: unknown dtype code");
+    if (a.batch == 0) return MB200_OK;
+    MB200_CHECK_ARG(a.x && a.weight && a.out && a.conv_state, "causal_conv1d_update: a required tensor is NULL");
+    if (int rc = enter_device(a.device)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const unsigned blocks = (unsigned)(((int64_t)a.batch * a.dim + 255) / 256);
+    if (a.io_dtype == MB200_F32) conv1d_update_kernel<float><<<blocks, 256, 0, stream>>>(a);
+    else if (a.io_dtype == MB200_BF16) conv1d_update_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(a);
+    else conv1d_update_kernel<__half><<<blocks, 256, 0, stream>>>(a);
+    MB200_CHECK_LAUNCH("causal_conv1d_update");
+    return MB200_OK;
+}
+
+extern "C" int mb200_rmsnorm_gated_fwd(const mb200_rmsnorm_args *args, void *stream_)
+{
+    using namespace mb200;
+    if (!args) return fail(MB200_ERR_BAD_ARG, "rmsnorm_gated_fwd: args is NULL");
+    const mb200_rmsnorm_args &a = *args;
+    MB200_CHECK_ARG(a.nrows >= 0 && a.ncols > 0 && a.group_size > 0, "rmsnorm_gated_fwd: bad sizes (rows %lld cols %d group %d)", (long long)a.nrows,
+                    a.ncols, a.group_size);
+    MB200_CHECK_ARG(a.ncols % a.group_size == 0, "rmsnorm_gated_fwd: the row length must be a multiple of group_size");
+    MB200_CHECK_ARG(valid_dtype(a.io_dtype) && valid_dtype(a.w_dtype), "rmsnorm_gated_fwd: unknown dtype code");
+    MB200_CHECK_ARG(a.nrows <= 2147483647LL && a.ncols / a.group_size <= 65535, "rmsnorm_gated_fwd: too many rows or groups");
+    if (a.nrows == 0) return MB200_OK;
+    MB200_CHECK_ARG(a.x && a.weight && a.out, "rmsnorm_gated_fwd: a required tensor is NULL");
+    if (int rc = enter_device(a.device)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int rc;
+    if (a.io_dtype == MB200_F32) rc = launch_rmsnorm<float>(a, stream);
+    else if (a.io_dtype == MB200_BF16) rc = launch_rmsnorm<__nv_bfloat16>(a, stream);
+    else rc = launch_rmsnorm<__half>(a, stream);
+    if (rc) return rc;
+    MB200_CHECK_LAUNCH("rmsnorm_gated_fwd");
+    return MB200_OK;
+}

@@ -413,6 +413,11 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
     const bool has_local = (a.phases & MB200_SSD_PHASE_LOCAL) != 0, has_out = (a.phases & MB200_SSD_PHASE_OUTPUT) != 0;
     const bool tc_out = ssd_tc_local_eligible(a) && ssd_tc_output_eligible(a);     // OUTPUT stages on tensor cores
     const bool tc_loc = (has_local && has_out) ? tc_out : ssd_tc_local_eligible(a);  // LOCAL stages on tensor cores
+    // C.B^T ahead of the exchange of a sequence split: on tensor cores when x, B and C qualify, which both halves can
+    // tell (they are handed the same C); the OUTPUT half uses it only if it is the form its chunk scan reads.
+    const bool tc_cb_early = ssd_tc_local_eligible(a) && ssd_tc_cb_eligible(a);
+    const bool cb_early = has_local && !has_out && (a.phases & MB200_SSD_PHASE_CB) && a.C;
+    const bool cb_ready = !has_local && has_out && (a.phases & MB200_SSD_PHASE_CB_READY) && tc_out == tc_cb_early;
     void *prev16 = tc_out ? static_cast<void *>(base + lay.off_prev16) : nullptr;
     {
         cudaError_t e = cudaMemsetAsync(base + lay.off_status, 0, sizeof(int), stream);
@@ -435,9 +440,14 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         }
         // C.B^T needs nothing the other stages produce: when the whole operator runs on the tensor-core path it goes
         // first and the cumsum is launched as its programmatic dependent, so the two small kernels share the GPU.
-        const bool cb_first = tc_out && has_out;
+        const bool cb_first = (tc_out && has_out) || (cb_early && tc_cb_early);
         if (cb_first)
             if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream, 1)) return rc;
+        if (cb_early && !tc_cb_early) {
+            const int tq = (Q + 63) / 64;
+            ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);
+            MB200_CHECK_LAUNCH("ssd chunk_cb");
+        }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(nc, a.batch, (a.nheads + 31) / 32);
         cfg.blockDim = dim3(256);
@@ -493,11 +503,13 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         MB200_CHECK_LAUNCH("ssd state_passing");
         if (tc_out) {
             // C.B^T already ran ahead of the cumsum when this call includes the LOCAL phase
-            if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream, has_local ? 2 : 3)) return rc;
+            if (int rc = ssd_tc_cb_and_scan(a, lay, fused_states, stream, (has_local || cb_ready) ? 2 : 3)) return rc;
         } else {
             const int tq = (Q + 63) / 64;
-            ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);
-            MB200_CHECK_LAUNCH("ssd chunk_cb");
+            if (!cb_ready) {
+                ssd_cb_kernel<T><<<dim3(tq * tq, a.batch * nc, a.ngroups), kT, 0, stream>>>(a, cb, nc);
+                MB200_CHECK_LAUNCH("ssd chunk_cb");
+            }
             ssd_chunk_scan_kernel<T><<<dim3(tq * ((a.headdim + 63) / 64), a.batch * nc, a.nheads), kT, 0, stream>>>(a, dtb, dAb, states, cb, nc);
             MB200_CHECK_LAUNCH("ssd chunk_scan");
         }
@@ -518,7 +530,11 @@ int check_ssd(const mb200_ssd_args &a)
     MB200_CHECK_ARG(a.io_dtype == MB200_F32 || a.io_dtype == MB200_F16 || a.io_dtype == MB200_BF16, "ssd: unknown io_dtype %d", a.io_dtype);
     MB200_CHECK_ARG(a.dt_dtype == MB200_F32 || a.dt_dtype == MB200_F16 || a.dt_dtype == MB200_BF16, "ssd: unknown dt_dtype %d", a.dt_dtype);
     MB200_CHECK_ARG(a.chunk_size <= 1024, "ssd: chunk_size must be <= 1024");
-    MB200_CHECK_ARG((a.phases & ~MB200_SSD_PHASE_ALL) == 0 && a.phases != 0, "ssd: phases must be a combination of LOCAL and OUTPUT");
+    MB200_CHECK_ARG((a.phases & MB200_SSD_PHASE_ALL) != 0 && (a.phases & ~(MB200_SSD_PHASE_ALL | MB200_SSD_PHASE_CB | MB200_SSD_PHASE_CB_READY)) == 0,
+                    "ssd: phases must be a combination of LOCAL and OUTPUT");
+    MB200_CHECK_ARG(!(a.phases & MB200_SSD_PHASE_CB) || (a.phases & MB200_SSD_PHASE_ALL) == MB200_SSD_PHASE_LOCAL, "ssd: PHASE_CB goes with a LOCAL-only call");
+    MB200_CHECK_ARG(!(a.phases & MB200_SSD_PHASE_CB_READY) || (a.phases & MB200_SSD_PHASE_ALL) == MB200_SSD_PHASE_OUTPUT,
+                    "ssd: PHASE_CB_READY goes with an OUTPUT-only call");
     return MB200_OK;
 }
 
@@ -544,7 +560,7 @@ extern "C" int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream
     MB200_CHECK_ARG(!(a.phases & MB200_SSD_PHASE_OUTPUT) || a.out || a.seqlen == 0 || a.batch == 0, "ssd: out is NULL");
     MB200_CHECK_ARG(!a.cu_seqlens || a.batch == 1, "passing cu_seqlens to get the varlen states is only supported if batch dimension is 1");
     MB200_CHECK_ARG(!a.cu_seqlens || (a.num_seqs >= 0 && a.num_seqs <= 65535), "ssd: num_seqs must be in [0, 65535]");
-    MB200_CHECK_ARG(!(a.seq_idx || a.cu_seqlens) || a.phases == MB200_SSD_PHASE_ALL, "ssd: packed sequences cannot be combined with a sequence split");
+    MB200_CHECK_ARG(!(a.seq_idx || a.cu_seqlens) || (a.phases & MB200_SSD_PHASE_ALL) == MB200_SSD_PHASE_ALL, "ssd: packed sequences cannot be combined with a sequence split");
     if (a.batch == 0) return MB200_OK;   // nothing to do; empty tensors carry NULL pointers
     MB200_CHECK_ARG(a.seqlen == 0 || (a.x && a.dt && a.A && a.B && a.C), "ssd: a required tensor is NULL");
     if (int rc = enter_device(a.device)) return rc;
@@ -557,7 +573,7 @@ extern "C" int mb200_ssd_chunk_scan_fwd(const mb200_ssd_args *args, void *stream
             cudaError_t e = a.initial_states ? cudaMemcpyAsync(a.final_states, a.initial_states, n, cudaMemcpyDeviceToDevice, stream)
                                              : cudaMemsetAsync(a.final_states, 0, n, stream);
             if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd: final state copy: %s", cudaGetErrorString(e));
-        } else if (a.phases == MB200_SSD_PHASE_LOCAL) {
+        } else if ((a.phases & MB200_SSD_PHASE_ALL) == MB200_SSD_PHASE_LOCAL) {
             // an empty range of a sequence split is summarised by the identity: state 0, decay 1
             if (a.final_states) {
                 const cudaError_t e = cudaMemsetAsync(a.final_states, 0, n, stream);

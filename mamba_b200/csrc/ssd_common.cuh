@@ -49,6 +49,7 @@ inline SsdScratch ssd_scratch_layout(const mb200_ssd_args &a)
 // of a sequence split agree on how the LOCAL half ran although they are handed different C / z / out.
 bool ssd_tc_local_eligible(const mb200_ssd_args &a);
 bool ssd_tc_output_eligible(const mb200_ssd_args &a);
+bool ssd_tc_cb_eligible(const mb200_ssd_args &a);      // C as the tensor-core C.B^T kernel needs it
 int ssd_tc_chunk_state(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream);
 // parts: 1 = the C.B^T launch, 2 = the chunk-scan launch, 3 = both
 int ssd_tc_cb_and_scan(const mb200_ssd_args &a, const SsdScratch &lay, bool states_np, cudaStream_t stream, int parts = 3);

@@ -1030,6 +1030,12 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         MB200_CHECK_LAUNCH("ssd chunk_state (tensor core)");
         return MB200_OK;
     }
+    if (parts & 1) {
+        ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_cb_kernel<T>), (int)smem_cb, a.device);
+        ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
+        MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
+    }
+    if (!(parts & 2)) return MB200_OK;       // C.B^T alone (ahead of the exchange of a sequence split): out, z and the states play no part
     if (h_np) {
         const uint64_t d[3] = {(uint64_t)kP, (uint64_t)kN, (uint64_t)a.batch * nc * a.nheads};
         const uint64_t s[2] = {(uint64_t)kP * 2, (uint64_t)kN * kP * 2};
@@ -1058,11 +1064,6 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
             if (!encode_16bit(&tz, fmt, a.z, 4, d, sz, bx128)) return fail(MB200_ERR_LAUNCH, "ssd: tensor map for z failed");
         }
     }
-    if (parts & 1) {
-        ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_cb_kernel<T>), (int)smem_cb, a.device);
-        ssd_tc_cb_kernel<T><<<dim3(a.ngroups, nc * 2, a.batch), kThreadsTc, smem_cb, stream>>>(tC, tB, cb16, nc, a.ngroups, status);
-        MB200_CHECK_LAUNCH("ssd chunk_cb (tensor core)");
-    }
     if (parts & 2) {
         ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_chunk_scan_kernel<T>), (int)smem_scan, a.device);
         ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, h_np ? 1 : 0, status);
@@ -1082,9 +1083,11 @@ bool ssd_tc_local_eligible(const mb200_ssd_args &a)
     return encode_fn() != nullptr;
 }
 
+bool ssd_tc_cb_eligible(const mb200_ssd_args &a) { return a.C && aligned16(a.C) && mult8(a.C_stride, 3); }
+
 bool ssd_tc_output_eligible(const mb200_ssd_args &a)
 {
-    if (!aligned16(a.C) || !mult8(a.C_stride, 3)) return false;
+    if (!ssd_tc_cb_eligible(a)) return false;
     if (!a.out || !aligned16(a.out) || !mult8(a.out_stride, 3)) return false;
     if (a.z && (!aligned16(a.z) || !mult8(a.z_stride, 3))) return false;
     return true;

@@ -374,21 +374,23 @@ def mamba_chunk_scan_combined_noalloc(x, dt, A, B, C, chunk_size, out, D=None, z
     return out
 
 
-def ssd_local_states(x, dt, A, B, chunk_size, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf"))):
+def ssd_local_states(x, dt, A, B, chunk_size, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf")), C=None):
     """First half of a sequence-split SSD scan on this device's contiguous chunk range.
 
     Returns ``(range_state, range_decay, scratch)``: the state at the end of the range given a zero
     incoming state (batch, nheads, headdim, dstate) fp32, the product of the range's chunk decays
-    (batch, nheads) fp32, and the scratch buffer that ``ssd_finish`` must be handed back unchanged.
-    C does not enter this half; B doubles for it in the call.
+    (batch, nheads) fp32, and an opaque scratch handle that ``ssd_finish`` must be handed back unchanged.
+    The recurrence of this half does not read C; when C is given anyway, C.B^T -- which needs nothing from the
+    exchange that follows -- is formed here too, so that it is off the critical path after the exchange.
     """
     batch, seqlen, nheads, headdim = x.shape
     dstate = B.shape[-1]
     range_state = torch.empty(batch, nheads, headdim, dstate, device=x.device, dtype=torch.float32)
     range_decay = torch.empty(batch, nheads, device=x.device, dtype=torch.float32)
-    _, scratch = _ssd_launch(x, dt, A, B, B, chunk_size, None, None, dt_bias, None, None, dt_softplus, dt_limit,
-                             L.PHASE_LOCAL, final_states=range_state, range_decay=range_decay)
-    return range_state, range_decay, scratch
+    cb_early = C is not None and seqlen > 0
+    _, scratch = _ssd_launch(x, dt, A, B, C if cb_early else B, chunk_size, None, None, dt_bias, None, None, dt_softplus, dt_limit,
+                             L.PHASE_LOCAL | (L.PHASE_CB if cb_early else 0), final_states=range_state, range_decay=range_decay)
+    return range_state, range_decay, (scratch, cb_early)
 
 
 def ssd_finish(x, dt, A, B, C, chunk_size, scratch, D=None, z=None, dt_bias=None, incoming_state=None,
@@ -399,8 +401,9 @@ def ssd_finish(x, dt, A, B, C, chunk_size, scratch, D=None, z=None, dt_bias=None
     dstate = B.shape[-1]
     final_states = (torch.empty(batch, nheads, headdim, dstate, device=x.device, dtype=torch.float32)
                     if return_final_states else None)
+    scratch, cb_ready = scratch if isinstance(scratch, tuple) else (scratch, False)
     out, _ = _ssd_launch(x, dt, A, B, C, chunk_size, D, z, dt_bias, incoming_state, None, dt_softplus, dt_limit,
-                         L.PHASE_OUTPUT, final_states=final_states, scratch=scratch)
+                         L.PHASE_OUTPUT | (L.PHASE_CB_READY if cb_ready else 0), final_states=final_states, scratch=scratch)
     return out if not return_final_states else (out, final_states)
 
 

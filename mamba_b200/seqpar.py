@@ -135,8 +135,9 @@ def mamba_chunk_scan_sequence_parallel(x, dt, A, B, C, chunk_size, D=None, z=Non
     clock = _PhaseClock(phases, x.is_cuda)
     if rank < world - 1:
         assert x.shape[1] % chunk_size == 0, "every rank but the last must hold whole chunks"
+    # C goes along so that C.B^T, which needs nothing from the exchange, is formed ahead of it
     range_state, range_decay, scratch = steps.local(x, dt, A, B, chunk_size, dt_bias=dt_bias, dt_softplus=dt_softplus,
-                                                    dt_limit=dt_limit)
+                                                    dt_limit=dt_limit, C=C)
     clock.mark("local")
     if handoff is None:
         handoff = "gather" if world > 2 else "chain"

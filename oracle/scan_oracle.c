@@ -7,6 +7,11 @@
  * Each function restates one of the reference's pure-PyTorch definitions:
  *   oracle_selective_scan     <- mamba_ssm/ops/selective_scan_interface.py:127-193
  *   oracle_state_update       <- mamba_ssm/ops/triton/selective_state_update.py:224-285
+ *   oracle_causal_conv1d      <- the depthwise nn.Conv1d with left padding that the mixers fall back to,
+ *                                mamba_ssm/modules/mamba2.py:232-234 (mamba_simple.py:166-171), with the packed-
+ *                                sequence and carried-state options of the causal-conv1d package it stands in for
+ *   oracle_conv1d_update      <- the single-token roll / multiply / sum at mamba_ssm/modules/mamba2.py:309-315
+ *   oracle_rmsnorm_gated      <- rms_norm_ref, mamba_ssm/ops/triton/layernorm_gated.py:18-41
  *   oracle_ssd_chunk_scan     <- mamba_ssm/ops/triton/ssd_combined.py:687-725, built from
  *                                ssd_chunk_state.py:1094-1122 (chunk states),
  *                                ssd_state_passing.py:327-350 (inter-chunk recurrence) and
@@ -234,4 +239,78 @@ void oracle_ssd_chunk_scan(const float *x, const float *dt, const float *A,
             free(H); free(S); free(dtv); free(cum); free(cb); free(acc);
         }
     }
+}
+
+
+/* ---- causal depthwise conv1d ------------------------------------------------------------------
+ * x, out (batch, dim, seqlen) dense; weight (dim, width); bias (dim) or NULL; seq_idx (batch, seqlen) or NULL;
+ * init (batch, dim, width-1) or NULL; fin (batch, dim, width-1) or NULL. */
+void oracle_causal_conv1d(const float *x, const float *weight, const float *bias, const int *seq_idx, const float *init,
+                          int silu_act, int batch, int dim, int L, int W, float *out, float *fin)
+{
+#pragma omp parallel for collapse(2)
+    for (int b = 0; b < batch; ++b)
+        for (int c = 0; c < dim; ++c) {
+            const float *xr = x + ((size_t)b * dim + c) * L;
+            const float *ir = init ? init + ((size_t)b * dim + c) * (W - 1) : NULL;
+            for (int t = 0; t < L; ++t) {
+                double s = bias ? bias[c] : 0.0;
+                for (int k = 0; k < W; ++k) {
+                    const int tk = t - (W - 1) + k;
+                    double v;
+                    if (tk >= 0) {
+                        if (seq_idx && seq_idx[(size_t)b * L + tk] != seq_idx[(size_t)b * L + t]) continue;
+                        v = xr[tk];
+                    } else {
+                        v = ir ? ir[W - 1 + tk] : 0.0;
+                    }
+                    s += (double)weight[(size_t)c * W + k] * v;
+                }
+                out[((size_t)b * dim + c) * L + t] = (float)(silu_act ? silu(s) : s);
+            }
+            if (fin)
+                for (int j = 0; j < W - 1; ++j) {
+                    const int t = L - (W - 1) + j;
+                    fin[((size_t)b * dim + c) * (W - 1) + j] = t >= 0 ? xr[t] : (ir ? ir[W - 1 + t] : 0.f);
+                }
+        }
+}
+
+/* state (batch, dim, S) updated in place; x, out (batch, dim). */
+void oracle_conv1d_update(float *state, const float *x, const float *weight, const float *bias, int silu_act, int batch,
+                          int dim, int W, int S, float *out)
+{
+    for (int b = 0; b < batch; ++b)
+        for (int c = 0; c < dim; ++c) {
+            float *st = state + ((size_t)b * dim + c) * S;
+            for (int j = 0; j + 1 < S; ++j) st[j] = st[j + 1];
+            st[S - 1] = x[(size_t)b * dim + c];
+            double s = bias ? bias[c] : 0.0;
+            for (int k = 0; k < W; ++k) s += (double)weight[(size_t)c * W + k] * st[S - W + k];
+            out[(size_t)b * dim + c] = (float)(silu_act ? silu(s) : s);
+        }
+}
+
+/* x, z, out (rows, cols) dense; weight, bias (cols). */
+void oracle_rmsnorm_gated(const float *x, const float *z, const float *weight, const float *bias, double eps, int group,
+                          int norm_before_gate, long rows, int cols, float *out)
+{
+#pragma omp parallel for
+    for (long r = 0; r < rows; ++r)
+        for (int g0 = 0; g0 < cols; g0 += group) {
+            double ss = 0.0;
+            for (int e = g0; e < g0 + group; ++e) {
+                double v = x[(size_t)r * cols + e];
+                if (z && !norm_before_gate) v *= silu(z[(size_t)r * cols + e]);
+                ss += v * v;
+            }
+            const double rstd = 1.0 / sqrt(ss / group + eps);
+            for (int e = g0; e < g0 + group; ++e) {
+                double v = x[(size_t)r * cols + e];
+                if (z && !norm_before_gate) v *= silu(z[(size_t)r * cols + e]);
+                double y = v * rstd * weight[e] + (bias ? bias[e] : 0.0);
+                if (z && norm_before_gate) y *= silu(z[(size_t)r * cols + e]);
+                out[(size_t)r * cols + e] = (float)y;
+            }
+        }
 }

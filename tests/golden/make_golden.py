@@ -24,6 +24,7 @@ from mamba_ssm.ops.triton.ssd_combined import ssd_chunk_scan_combined_ref
 from mamba_ssm.ops.triton.ssd_chunk_state import chunk_state_ref
 from mamba_ssm.ops.triton.ssd_state_passing import state_passing_ref
 from mamba_ssm.ops.triton.ssd_chunk_scan import chunk_scan_ref
+from mamba_ssm.ops.triton.layernorm_gated import rms_norm_ref
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -175,8 +176,55 @@ def ssd(name, seed, batch, L, H, P, G, N, Q, dtype=torch.float32, has_z=True, D_
          final_states=final, chunk_size=np.int32(Q), is_bf16=np.int32(dtype == torch.bfloat16))
 
 
+# ----------------------------------------------------------------------------- the steps around the scan
+def conv1d(name, seed, batch, dim, L, width, dtype=torch.float32, activation="silu", steps=0):
+    """The reference's CPU form of the causal conv: a depthwise nn.Conv1d with left padding, cut to seqlen
+    (mamba_ssm/modules/mamba2.py:232-234), and for `steps` further tokens the roll / multiply / sum of :309-315."""
+    g = gen(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    conv = torch.nn.Conv1d(dim, dim, width, groups=dim, padding=width - 1, bias=True)
+    with torch.no_grad():
+        conv.weight.copy_(r(dim, 1, width) * 0.5)
+        conv.bias.copy_(r(dim) * 0.1)
+    x = r(batch, dim, L).to(dtype)
+    act = F.silu if activation else (lambda t: t)
+    with torch.no_grad():
+        out = act(conv(x.float())[..., :L])
+        state = F.pad(x.float(), (width - L, 0)) if L < width else x.float()[..., -width:].clone()     # (batch, dim, width), as Mamba2 keeps it
+        state0 = state.clone()
+        w2 = rearrange(conv.weight, "d 1 w -> d w")
+        xs, outs = [], []
+        for _ in range(steps):
+            xt = r(batch, dim).to(dtype).float()
+            state.copy_(torch.roll(state, shifts=-1, dims=-1))
+            state[:, :, -1] = xt
+            outs.append(act(torch.sum(state * w2, dim=-1) + conv.bias))
+            xs.append(xt)
+    save(name, x=x, weight=w2, bias=conv.bias, out=out, final_states=x.float()[..., -(width - 1):] if L >= width - 1 else None,
+         state0=state0 if steps else None, x_steps=torch.stack(xs) if steps else None, out_steps=torch.stack(outs) if steps else None,
+         state_final=state if steps else None, has_act=np.int32(bool(activation)), is_bf16=np.int32(dtype == torch.bfloat16))
+
+
+def rmsnorm(name, seed, rows, cols, group, norm_before_gate, dtype=torch.float32, has_z=True, has_bias=False):
+    g = gen(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    x, z = r(*rows, cols).to(dtype), (r(*rows, cols).to(dtype) if has_z else None)
+    w, b = 1 + 0.1 * r(cols), (0.1 * r(cols) if has_bias else None)
+    out = rms_norm_ref(x.float(), w, b, z=None if z is None else z.float(), eps=1e-5, group_size=group, norm_before_gate=norm_before_gate)
+    save(name, x=x, z=z, weight=w, bias=b, out=out, group_size=np.int32(group or cols), norm_before_gate=np.int32(norm_before_gate),
+         eps=np.float32(1e-5), is_bf16=np.int32(dtype == torch.bfloat16))
+
+
 def main():
     torch.set_num_threads(os.cpu_count())
+    conv1d("conv_fp32_w4", 41, 2, 24, 70, 4, steps=3)
+    conv1d("conv_fp32_w3_noact", 42, 1, 8, 33, 3, activation=None)
+    conv1d("conv_fp32_w2_short", 43, 2, 8, 1, 2, steps=2)
+    conv1d("conv_bf16_w4", 44, 2, 64, 130, 4, dtype=torch.bfloat16, steps=2)
+    rmsnorm("rms_fp32_group_gate_after", 51, (3, 5), 64, 16, True)
+    rmsnorm("rms_fp32_nogroup_gate_before", 52, (7,), 96, None, False, has_bias=True)
+    rmsnorm("rms_fp32_noz", 53, (4,), 40, 8, True, has_z=False)
+    rmsnorm("rms_bf16_group_gate_before", 54, (2, 9), 256, 128, False, dtype=torch.bfloat16)
     mamba1("m1_fp32_g1", 11, 2, 4, 128, 8, 1, test_style=True)
     mamba1("m1_fp32_g2_odd", 12, 2, 4, 372, 8, 2, has_z=False, test_style=True)
     mamba1("m1_fp32_constbc", 13, 2, 6, 100, 4, 1, const_bc=True, has_D=False)

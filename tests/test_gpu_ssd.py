@@ -204,11 +204,13 @@ def test_prefill_state_continues_in_decode():
 @pytest.mark.parametrize("shape,dtype,tol", [((1, 512, 4, 32, 2, 64, 64), torch.float32, TOL_FP32),
                                              ((2, 1024, 40, 64, 2, 128, 256), torch.bfloat16, TOL_BF16),
                                              ((1, 1300, 80, 64, 8, 128, 256), torch.float16, TOL_BF16)])
-def test_sequence_split_in_two_ranges(shape, dtype, tol):
+@pytest.mark.parametrize("cb_early", [False, True])
+def test_sequence_split_in_two_ranges(shape, dtype, tol, cb_early):
     """The two-phase entry used when a sequence is split across devices: both ranges run LOCAL, the
     first range's summary is folded and handed to the second, then both run OUTPUT.  Equal to one call.
     The 16-bit shapes have enough (batch, head) pairs for the fused state-stream path, where the OUTPUT half
-    adds the incoming state's share to the entering states the LOCAL half stored."""
+    adds the incoming state's share to the entering states the LOCAL half stored.  With `cb_early` the LOCAL
+    half is given C and forms C.B^T ahead of the exchange."""
     from mamba_b200 import ssd_finish, ssd_fold_state, ssd_local_states
     b, L, H, P, G, N, Q = shape
     inp = make(14, b, L, H, P, G, N, dtype, has_z=False)
@@ -218,13 +220,15 @@ def test_sequence_split_in_two_ranges(shape, dtype, tol):
                         return_final_states=True)
     half = (L // 2) // Q * Q
     sl = [slice(0, half), slice(half, L)]
-    loc = [ssd_local_states(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], Q, dt_bias=c["dt_bias"], dt_softplus=True)
+    loc = [ssd_local_states(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], Q, dt_bias=c["dt_bias"], dt_softplus=True,
+                            C=c["C"][:, s] if cb_early else None)
            for s in sl]
     incoming = [None, ssd_fold_state(None, loc[0][1], loc[0][0])]
     outs, fin = [], None
     for r, s in enumerate(sl):
         o, fin = ssd_finish(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], c["C"][:, s], Q, loc[r][2], D=c["D"],
                             dt_bias=c["dt_bias"], incoming_state=incoming[r], dt_softplus=True, return_final_states=True)
+        assert _status() == 0
         outs.append(o)
     assert_close(torch.cat(outs, dim=1), whole, TOL_FP32_, "split out")
     assert_close(fin, wfin, TOL_FP32_, "split final")
@@ -248,7 +252,10 @@ def test_sequence_split_when_only_the_output_half_is_misaligned():
     assert _status() == 0
     half = L // 2
     sl = [slice(0, half), slice(half, L)]
-    loc = [ssd_local_states(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], Q, dt_bias=c["dt_bias"], dt_softplus=True) for s in sl]
+    # C goes to the LOCAL half too: its early tensor-core C.B^T is then of no use to the general chunk scan of the
+    # OUTPUT half, which must form its own
+    loc = [ssd_local_states(c["x"][:, s], c["dt"][:, s], c["A"], c["B"][:, s], Q, dt_bias=c["dt_bias"], dt_softplus=True, C=c["C"][:, s])
+           for s in sl]
     incoming = [None, ssd_fold_state(None, loc[0][1], loc[0][0])]
     outs, fin = [], None
     for r, s in enumerate(sl):

@@ -76,3 +76,43 @@ def test_oracle_ssd_equals_recurrence():
                                    return_last_state=True)
     assert_close(out.permute(0, 2, 3, 1).reshape(b, H * P, L), o1, 1e-6, "ssd vs scan")
     assert_close(fin.reshape(b, H * P, N), l1, 1e-6, "final vs last")
+
+
+@pytest.mark.parametrize("name", golden_names("conv_"))
+def test_causal_conv1d_pinned(name):
+    """Prefill conv and the single-token steps that follow it, against the reference's nn.Conv1d / roll-and-sum forms."""
+    d = load_golden(name)
+    act = "silu" if d["has_act"] else None
+    out, fin = oracle.causal_conv1d(d["x"], d["weight"], d["bias"], activation=act, return_final_states=True)
+    assert_close(out, d["out"], PIN, name + " out")
+    if "final_states" in d:
+        assert_close(fin, d["final_states"], PIN, name + " final_states")
+    if "x_steps" in d:
+        state = d["state0"].clone()
+        for s in range(d["x_steps"].shape[0]):
+            o = oracle.causal_conv1d_update(d["x_steps"][s], state, d["weight"], d["bias"], act)
+            assert_close(o, d["out_steps"][s], PIN, f"{name} step {s}")
+        assert_close(state, d["state_final"], PIN, name + " state")
+
+
+def test_causal_conv1d_options_agree_with_their_definition():
+    """Carried state = the conv of the concatenated input; packed sequences = each sequence on its own."""
+    g = torch.Generator().manual_seed(3)
+    x, w, b = torch.randn(1, 5, 40, generator=g), torch.randn(5, 4, generator=g), torch.randn(5, generator=g)
+    whole = oracle.causal_conv1d(x, w, b, activation="silu")
+    first, fin = oracle.causal_conv1d(x[..., :17], w, b, activation="silu", return_final_states=True)
+    second = oracle.causal_conv1d(x[..., 17:], w, b, initial_states=fin, activation="silu")
+    assert_close(torch.cat([first, second], dim=-1), whole, 1e-6, "carried state")
+    seq_idx = torch.cat([torch.zeros(17), torch.ones(23)]).int()[None]
+    packed = oracle.causal_conv1d(x, w, b, seq_idx=seq_idx, activation="silu")
+    alone = oracle.causal_conv1d(x[..., 17:], w, b, activation="silu")
+    assert_close(packed[..., 17:], alone, 1e-6, "packed second sequence")
+    assert_close(packed[..., :17], first, 1e-6, "packed first sequence")
+
+
+@pytest.mark.parametrize("name", golden_names("rms_"))
+def test_rmsnorm_gated_pinned(name):
+    d = load_golden(name)
+    out = oracle.rmsnorm_gated(d["x"], d["weight"], d.get("bias"), d.get("z"), eps=float(d["eps"]), group_size=int(d["group_size"]),
+                               norm_before_gate=bool(d["norm_before_gate"]))
+    assert_close(out, d["out"], PIN, name)

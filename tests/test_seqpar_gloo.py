@@ -31,7 +31,7 @@ def _oracle_steps():
     import torch.nn.functional as F
     from mamba_b200.seqpar import SsdSteps
 
-    def local(x, dt, A, B, Q, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf"))):
+    def local(x, dt, A, B, Q, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf")), C=None):
         if x.shape[1] == 0:      # an empty range is summarised by the identity, as the library does
             return torch.zeros(x.shape[0], x.shape[2], x.shape[3], B.shape[3]), torch.ones(x.shape[0], x.shape[2]), None
         _, state = oracle.ssd_chunk_scan(x, dt, A, B, B, Q, dt_bias=dt_bias, dt_softplus=dt_softplus, dt_limit=dt_limit)
