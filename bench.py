@@ -509,6 +509,24 @@ def measure(name, dev, rank, world, local, steps, warmup, batch, cpu_budget):
         out["roofline"]["tensor"] = {"flops_per_launch": w.flops, "achieved_tflops": tf, "peak_tflops": peak_tf,
                                      "frac": tf / peak_tf if peak_tf else None,
                                      "hbm_time_ms": w.alg_bytes / peak_gbs / 1e6, "tensor_time_ms": w.flops / peak_tf / 1e9 if peak_tf else None}
+    if name == "c2" and not dist and not w.reduced:
+        # the same launch group on packed input: `seqs` sequences of equal length per batch row (continuous batching)
+        seqs = 8
+        L = w.shape["seqlen"]
+        seq_idx = (torch.arange(L, device=dev, dtype=torch.int32) // (L // seqs))[None].expand(w.shape["batch"], L).contiguous()
+        d = w.d
+        packed = lambda: w.mb.mamba_chunk_scan_combined(d["x"], d["dt"], d["A"], d["B"], d["C"], 256, D=d["D"], z=d["z"], dt_bias=d["dt_bias"],
+                                                        seq_idx=seq_idx, dt_softplus=True, return_final_states=True)
+        for _ in range(3):
+            packed()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            packed()
+        e1.record()
+        torch.cuda.synchronize()
+        out["packed_sequences"] = {"sequences_per_row": seqs, "ms_per_step": e0.elapsed_time(e1) / steps,
+                                   "ratio_to_unpacked": e0.elapsed_time(e1) / steps / (per_step * 1e3)}
     if name == "c3" and dist:
         out["parity"] = w.c3_parity()
         phases = {}
@@ -601,8 +619,9 @@ def main():
         t_e2e = all_max([t_e2e], dist, dev)[0]
         line["e2e"] = {"value": w.global_tokens * e2e_steps / t_e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                        "steps": e2e_steps, "bytes": "this GPU's share per step"}
-    if "cpu_baseline" in head:
-        line["cpu_baseline"] = head["cpu_baseline"]
+    for k in ("cpu_baseline", "packed_sequences", "parity", "phases_ms"):
+        if k in head:
+            line[k] = head[k]
     del w
     torch.cuda.empty_cache()
     if not args.only:

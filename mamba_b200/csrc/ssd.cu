@@ -65,7 +65,8 @@ __device__ __forceinline__ int seq_at(const mb200_ssd_args &a, int b, int t)
 // One CTA per (chunk, batch, 32 heads): coalesced read of dt over heads, transposed in shared
 // memory, then a warp scan along the chunk per head.
 template <typename TD>
-__global__ void __launch_bounds__(256) ssd_cumsum_kernel(const mb200_ssd_args a, float *dt_out, float *dA_out, int nchunks)
+__global__ void __launch_bounds__(256) ssd_cumsum_kernel(const mb200_ssd_args a, float *dt_out, float *dA_out, int nchunks, uint8_t *seq_start,
+                                                         uint8_t *seq_carry)
 {
     extern __shared__ float sm[];   // Q x 33
     const int Q = a.chunk_size;
@@ -123,6 +124,25 @@ __global__ void __launch_bounds__(256) ssd_cumsum_kernel(const mb200_ssd_args a,
             }
             carry = __shfl_sync(0xffffffffu, v, 31);
         }
+    }
+    // Packed sequences on the tensor-core path (chunk of 256 = one position per thread): where, inside the chunk, the
+    // sequence of every position starts, and whether the chunk's first position continues the previous chunk's last
+    // sequence.  The chunk-scan kernel masks with these two instead of comparing ids.
+    if (seq_start && blockIdx.z == 0) {
+        __syncthreads();            // the transposing buffer is free
+        int *wmax = reinterpret_cast<int *>(sm);
+        const int32_t *sid = a.seq_idx + (int64_t)b * a.seqlen;
+        const int k = threadIdx.x;
+        const int me = sid[min(t0 + k, a.seqlen - 1)];
+        const int before = k > 0 ? sid[min(t0 + k - 1, a.seqlen - 1)] : me;
+        int start = (k > 0 && me != before) ? k : 0;            // a sequence starts here
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) start = max(start, __shfl_up_sync(0xffffffffu, start, o) * (lane >= o ? 1 : 0));
+        if (lane == 31) wmax[warp] = start;
+        __syncthreads();
+        for (int w2 = 0; w2 < warp; ++w2) start = max(start, wmax[w2]);
+        seq_start[((int64_t)b * nchunks + c) * Q + k] = (uint8_t)start;
+        if (k == 0) seq_carry[(int64_t)b * nchunks + c] = me == (c > 0 ? sid[t0 - 1] : 0) ? 1 : 0;
     }
     // When launched as the programmatic dependent of the C.B^T kernel this grid runs alongside it; it must not be
     // complete before that kernel is, because later launches only wait for this one.  (Returns at once otherwise.)
@@ -337,7 +357,7 @@ __global__ void __launch_bounds__(kT) ssd_chunk_scan_kernel(const mb200_ssd_args
 // the chunk that holds its last token, plus the state entering that chunk if the sequence began earlier.
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_varlen_state_kernel(const mb200_ssd_args a, const float *dtb, const float *dAb,
-                                                               const float *states, int nchunks)
+                                                               const float *states, int nchunks, const void *prev16, int prev_np)
 {
     const int P = a.headdim, N = a.dstate, Q = a.chunk_size;
     const int e = blockIdx.x * 256 + threadIdx.x;
@@ -362,7 +382,13 @@ __global__ void __launch_bounds__(256) ssd_varlen_state_kernel(const mb200_ssd_a
     for (int t = max(start, t0); t < end; ++t)
         acc = fmaf(to_float(x[(int64_t)t * a.x_stride[1]]) * (__expf(fminf(dA_end - dAc[t - t0], 0.f)) * dtc[t - t0]),
                    to_float(B[(int64_t)t * a.B_stride[1]]), acc);
-    if (start < t0) acc = fmaf(states[(((int64_t)c) * a.nheads + h) * (int64_t)P * N + e], __expf(dA_end), acc);
+    if (start < t0) {
+        // the state entering chunk c: fp32 [p][n] from the general stages; on the tensor-core path the 16-bit copy the
+        // chunk scan reads, [n][p] when the streaming launch wrote it
+        const int64_t slot = (((int64_t)c) * a.nheads + h) * (int64_t)P * N;
+        const float entering = prev16 ? load_any(prev16, a.io_dtype, slot + (prev_np ? (int64_t)n * P + p : (int64_t)e)) : states[slot + e];
+        acc = fmaf(entering, __expf(dA_end), acc);
+    }
     *dst = acc;
 }
 
@@ -459,10 +485,13 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
         cfg.attrs = attr;
         cfg.numAttrs = cb_first ? 1 : 0;
         int ncv = nc;
+        // the sequence-start table is only read by the tensor-core chunk scan (chunk of 256 positions = one per thread)
+        uint8_t *seq_start = (a.seq_idx && tc_out) ? reinterpret_cast<uint8_t *>(base + lay.off_seq_start) : nullptr;
+        uint8_t *seq_carry = reinterpret_cast<uint8_t *>(base + lay.off_seq_carry);
         cudaError_t ce;
-        if (a.dt_dtype == MB200_F32) ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<float>, a, dtb, dAb, ncv);
-        else if (a.dt_dtype == MB200_BF16) ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<__nv_bfloat16>, a, dtb, dAb, ncv);
-        else ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<__half>, a, dtb, dAb, ncv);
+        if (a.dt_dtype == MB200_F32) ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<float>, a, dtb, dAb, ncv, seq_start, seq_carry);
+        else if (a.dt_dtype == MB200_BF16) ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<__nv_bfloat16>, a, dtb, dAb, ncv, seq_start, seq_carry);
+        else ce = cudaLaunchKernelEx(&cfg, ssd_cumsum_kernel<__half>, a, dtb, dAb, ncv, seq_start, seq_carry);
         if (ce != cudaSuccess) return fail(MB200_ERR_LAUNCH, "ssd chunk_cumsum: %s", cudaGetErrorString(ce));
         MB200_CHECK_LAUNCH("ssd chunk_cumsum");
         if (fused_states) {
@@ -514,7 +543,8 @@ int run_ssd(const mb200_ssd_args &a, const SsdScratch &lay, cudaStream_t stream)
             MB200_CHECK_LAUNCH("ssd chunk_scan");
         }
         if (a.cu_seqlens && a.varlen_states && a.num_seqs > 0) {
-            ssd_varlen_state_kernel<T><<<dim3((unsigned)((PN + 255) / 256), a.num_seqs, a.nheads), 256, 0, stream>>>(a, dtb, dAb, states, nc);
+            ssd_varlen_state_kernel<T><<<dim3((unsigned)((PN + 255) / 256), a.num_seqs, a.nheads), 256, 0, stream>>>(a, dtb, dAb, states, nc, prev16,
+                                                                                                                   (fused_states && tc_out) ? 1 : 0);
             MB200_CHECK_LAUNCH("ssd varlen states");
         }
     }

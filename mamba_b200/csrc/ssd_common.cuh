@@ -17,10 +17,13 @@ namespace mb200 {
 //   aux     sequence-split hand-over of the fused state-stream path, written by the LOCAL phase for the OUTPUT
 //           phase: prefix decay (batch, nheads, nchunks), the range's end state from a zero incoming state
 //           (batch, nheads, P, N) and the range decay (batch, nheads), all fp32
+//   seq     packed sequences on the tensor-core path: for every position the offset inside its chunk at which its
+//           sequence starts (batch, nchunks, Q) uint8, and per chunk whether its first position continues the
+//           sequence that ended the previous chunk (batch, nchunks) uint8
 //   status  one int32 in the last 256 bytes    0 after a clean run; a kernel that gave up a bounded wait
 //                                              leaves its code here (the output is then invalid)
 struct SsdScratch {
-    size_t off_dt, off_dA, off_states, off_cb, off_prev16, off_aux, off_aux_state, off_aux_decay, off_status, total;
+    size_t off_dt, off_dA, off_states, off_cb, off_prev16, off_aux, off_aux_state, off_aux_decay, off_seq_start, off_seq_carry, off_status, total;
     int nchunks;
 };
 
@@ -39,7 +42,9 @@ inline SsdScratch ssd_scratch_layout(const mb200_ssd_args &a)
     s.off_aux = align256(s.off_prev16 + (size_t)a.batch * s.nchunks * a.nheads * a.headdim * a.dstate * 2);
     s.off_aux_state = align256(s.off_aux + (size_t)a.batch * a.nheads * s.nchunks * sizeof(float));
     s.off_aux_decay = align256(s.off_aux_state + (size_t)a.batch * a.nheads * a.headdim * a.dstate * sizeof(float));
-    s.off_status = align256(s.off_aux_decay + (size_t)a.batch * a.nheads * sizeof(float));
+    s.off_seq_start = align256(s.off_aux_decay + (size_t)a.batch * a.nheads * sizeof(float));
+    s.off_seq_carry = align256(s.off_seq_start + (size_t)a.batch * s.nchunks * a.chunk_size);      // sizes do not depend on pointers
+    s.off_status = align256(s.off_seq_carry + (size_t)a.batch * s.nchunks);
     s.total = s.off_status + 256;
     return s;
 }

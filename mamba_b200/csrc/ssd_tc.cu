@@ -186,7 +186,8 @@ constexpr int kStateThreads = 288;
 template <typename T>
 __global__ void __launch_bounds__(kStateThreads) ssd_tc_chunk_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
                                                                           const float *dtb, const float *dAb, float *states, int nchunks,
-                                                                          int nheads, int heads_per_group, int *status)
+                                                                          int nheads, int heads_per_group, const int32_t *seq_idx, int seqlen,
+                                                                          int *status)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = align1024(smem_raw);
@@ -205,6 +206,11 @@ __global__ void __launch_bounds__(kStateThreads) ssd_tc_chunk_state_kernel(const
         pre_last = dAc[kQ - 1];
         pre_dA = dAc[threadIdx.x];
         pre_dt = dtc[threadIdx.x];
+        if (seq_idx) {      // packed sequences: only steps of the chunk's last sequence reach its end state
+            const int32_t *sid = seq_idx + (int64_t)b * seqlen;
+            const int t = c * kQ + threadIdx.x, t_last = min(c * kQ + kQ, seqlen) - 1;
+            if (t < seqlen && sid[t] != sid[t_last]) pre_dt = 0.f;
+        }
     }
     if (threadIdx.x == 256) {
         mbar_init(&bars[0], 1);      // B landed
@@ -304,7 +310,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
 ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_B,
                            const __grid_constant__ CUtensorMap tm_Hs, const float *dtb, const float *dAb, const float *initial,
                            float *final_states, float *range_decay, float *prefix_decay, float *state_copy, float *decay_copy,
-                           int store_entering, int nchunks, int nheads, int heads_per_group, int unit0, int *status)
+                           int store_entering, int nchunks, int nheads, int heads_per_group, int unit0, const int32_t *seq_idx, int seqlen,
+                           int *status)
 {
     using Cfg = StreamCfg<HEADS>;
     constexpr int NST = Cfg::kStages;
@@ -395,14 +402,26 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
         for (int hd = 0; hd < HEADS; ++hd)
 #pragma unroll
             for (int j = 0; j < 16; ++j) H[hd][j] = initial ? initial[(bh0 + hd) * (kP * kN) + (int64_t)(p0 + j) * kN + n] : 0.f;
-        // per chunk: dA and dt of my two x rows (my weighting head), and every head's dA at the end of the chunk
-        auto scalars = [&](int c, float (&v)[4 + HEADS]) {
+        // per chunk: dA and dt of my two x rows (my weighting head), and every head's dA at the end of the chunk.
+        // Packed sequences: a row of another sequence than the chunk's last weighs nothing (dt = 0), and a chunk
+        // whose last step belongs to another sequence than the previous chunk's carries nothing over (decay 0).
+        const int32_t *sid = seq_idx ? seq_idx + (int64_t)b * seqlen : nullptr;
+        auto scalars = [&](int c, float (&v)[5 + HEADS]) {
             const float *dAc = dAb + ((bh0 + whead) * nchunks + c) * kQ, *dtc = dtb + ((bh0 + whead) * nchunks + c) * kQ;
             v[0] = dAc[r]; v[1] = dtc[r]; v[2] = dAc[128 + r]; v[3] = dtc[128 + r];
 #pragma unroll
             for (int hd = 0; hd < HEADS; ++hd) v[4 + hd] = dAb[((bh0 + hd) * nchunks + c) * kQ + kQ - 1];
+            v[4 + HEADS] = 1.f;         // 0 when nothing carries over into the state after this chunk
+            if (sid) {
+                const int t_last = min(c * kQ + kQ, seqlen) - 1;
+                const int s_last = sid[t_last], s_prev = c > 0 ? sid[c * kQ - 1] : 0;
+                const int t0r = c * kQ + r, t1r = t0r + 128;
+                if (t0r < seqlen && sid[t0r] != s_last) v[1] = 0.f;
+                if (t1r < seqlen && sid[t1r] != s_last) v[3] = 0.f;
+                if (s_last != s_prev) v[4 + HEADS] = 0.f;
+            }
         };
-        float nxt[4 + HEADS];
+        float nxt[5 + HEADS];
         scalars(0, nxt);
         float dec_prev[HEADS], dA_total[HEADS];
 #pragma unroll
@@ -425,9 +444,9 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
                 for (int j = 0; j < 16; ++j) H[hd][j] = fmaf(dec_prev[hd], H[hd][j], v[hd][j]);
         };
         for (int c = 0; c < nchunks && ok; ++c) {
-            float cur[4 + HEADS];
+            float cur[5 + HEADS];
 #pragma unroll
-            for (int q = 0; q < 4 + HEADS; ++q) cur[q] = nxt[q];
+            for (int q = 0; q < 5 + HEADS; ++q) cur[q] = nxt[q];
             if (c + 1 < nchunks) scalars(c + 1, nxt);
             float my_last = cur[4];
 #pragma unroll
@@ -460,7 +479,7 @@ ssd_tc_state_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
             if (c > 0) fold(c - 1);
 #pragma unroll
             for (int hd = 0; hd < HEADS; ++hd) {
-                dec_prev[hd] = __expf(cur[4 + hd]);
+                dec_prev[hd] = __expf(cur[4 + hd]) * cur[4 + HEADS];
                 if (tid == 0 && prefix_decay) prefix_decay[(bh0 + hd) * nchunks + c] = __expf(dA_total[hd]);   // decay from the range start to chunk c
                 dA_total[hd] += cur[4 + hd];
             }
@@ -558,7 +577,8 @@ __global__ void __launch_bounds__(kScanThreads, 3)
 ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_C,
                          const __grid_constant__ CUtensorMap tm_H, const __grid_constant__ CUtensorMap tm_CB,
                          const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_out, const mb200_ssd_args a,
-                         const float *dtb, const float *dAb, int nchunks, int h_np, int *status)
+                         const float *dtb, const float *dAb, int nchunks, int h_np, const uint8_t *seq_start, const uint8_t *seq_carry,
+                         int *status)
 {
     extern __shared__ __align__(1024) uint8_t sm[];
     constexpr uint32_t kSlot = 24576, kSlotX = 16384;   // a slot: 16 KB tile (C half or CB block), then 8 KB (H half or 64 rows of x)
@@ -585,8 +605,18 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     const float *dtc = dtb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
     const float *dAc = dAb + (((int64_t)b * a.nheads + h) * nchunks + c) * kQ;
     float pre_dk = 0.f, pre_tk = 0.f, pre_ref = 0.f, pre_prev = 0.f;
+    // Packed sequences: `lo` = first column of my row's sequence inside the chunk (columns before it belong to other
+    // sequences and are masked like the columns past the diagonal); `carry` = my row continues the sequence that
+    // ended the previous chunk, so the state entering the chunk reaches it.
+    int lo = 0;
+    bool carry = true;
     if (threadIdx.x < 256) {
         const int k = threadIdx.x;
+        if (seq_start) {
+            const int64_t bc = (int64_t)b * nchunks + c;
+            lo = seq_start[bc * kQ + mb * 128 + (k & 127)];
+            carry = lo == 0 && seq_carry[bc] != 0;
+        }
         pre_dk = dAc[k];
         pre_tk = dtc[k];
         pre_ref = dAc[k | 31];
@@ -722,7 +752,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         // lane (two tile buffers of 32 columns, used alternately by the ring items).
         // First the two K halves of C, row-scaled by exp(dA_m), so that C.H^T lands in the same accumulator.
         {
-            const float rs = ex2(dAm);
+            const float rs = carry ? ex2(dAm) : 0.f;
             const uint32_t rs2 = Pack2<T>::pack(rs, rs);
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb) {
@@ -755,10 +785,10 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             if (ok) {
                 tc_fence_after_sync();
                 uint32_t w[16];
-                if (klo > m) {
+                if (klo > m || klo + 31 < lo) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) w[i] = 0u;
-                } else if (klo + 31 <= m && factor_ok) {
+                } else if (klo >= lo && klo + 31 <= m && factor_ok) {
                     const float rm = ex2(dAm - dA2[klo + 31]);
                     const uint64_t rm2 = pack2(rm, rm);
 #pragma unroll
@@ -775,7 +805,7 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                             w[4 * ch + q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
                         }
                     }
-                } else if (factor_ok && dA2[klo] - dA2[klo + 31] <= kMaxDiagSpan) {
+                } else if (klo >= lo && factor_ok && dA2[klo] - dA2[klo + 31] <= kMaxDiagSpan) {
                     // the range holds the diagonal but its decay span is moderate: same split with ref = last column
                     // (the row factor is then >= 1, bounded by 2^kMaxDiagSpan), columns past the diagonal masked
                     const float rm = ex2(dAm - dA2[klo + 31]);
@@ -810,8 +840,8 @@ ssd_tc_chunk_scan_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             const float2 tk = Pack2<__nv_bfloat16>::unpack(tw[q]);
-                            const float l0 = (kc + 2 * q <= m) ? ex2(fminf(dAm - dk[2 * q], 0.f)) * tk.x : 0.f;
-                            const float l1 = (kc + 2 * q + 1 <= m) ? ex2(fminf(dAm - dk[2 * q + 1], 0.f)) * tk.y : 0.f;
+                            const float l0 = (kc + 2 * q <= m && kc + 2 * q >= lo) ? ex2(fminf(dAm - dk[2 * q], 0.f)) * tk.x : 0.f;
+                            const float l1 = (kc + 2 * q + 1 <= m && kc + 2 * q + 1 >= lo) ? ex2(fminf(dAm - dk[2 * q + 1], 0.f)) * tk.y : 0.f;
                             w[4 * ch + q] = Pack2<T>::mul(e[q], Pack2<T>::pack(l0, l1));
                         }
                     }
@@ -1010,7 +1040,8 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
         if (paired > 0) {
             ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_state_stream_kernel<T, 2>), (int)StreamCfg<2>::kSmem, a.device);
             ssd_tc_state_stream_kernel<T, 2><<<(unsigned)paired, kStreamThreads, StreamCfg<2>::kSmem, stream>>>(
-                tx, tB, tHs, dtb, dAb, init, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1, nc, a.nheads, hpg, 0, status);
+                tx, tB, tHs, dtb, dAb, init, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1, nc, a.nheads, hpg, 0, a.seq_idx,
+                a.seqlen, status);
             MB200_CHECK_LAUNCH("ssd state stream (tensor core, head pairs)");
         }
         const int64_t singles = (int64_t)a.batch * a.nheads - 2 * paired;
@@ -1018,7 +1049,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
             ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_state_stream_kernel<T, 1>), (int)StreamCfg<1>::kSmem, a.device);
             ssd_tc_state_stream_kernel<T, 1><<<(unsigned)singles, kStreamThreads, StreamCfg<1>::kSmem, stream>>>(
                 tx, tB, tHs, dtb, dAb, init, a.final_states, a.range_decay, aux_prefix, aux_state, aux_decay, 1, nc, a.nheads, hpg,
-                (int)(2 * paired), status);
+                (int)(2 * paired), a.seq_idx, a.seqlen, status);
         }
         MB200_CHECK_LAUNCH("ssd state stream (tensor core)");
         return MB200_OK;
@@ -1026,7 +1057,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
     if (stage == 0) {
         ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_chunk_state_kernel<T>), (int)smem_state, a.device);
         ssd_tc_chunk_state_kernel<T><<<dim3(a.nheads, nc, a.batch), kStateThreads, smem_state, stream>>>(tx, tB, dtb, dAb, states, nc, a.nheads,
-                                                                                                   a.nheads / a.ngroups, status);
+                                                                                                   a.nheads / a.ngroups, a.seq_idx, a.seqlen, status);
         MB200_CHECK_LAUNCH("ssd chunk_state (tensor core)");
         return MB200_OK;
     }
@@ -1066,7 +1097,10 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
     }
     if (parts & 2) {
         ensure_dynamic_smem(reinterpret_cast<const void *>(&ssd_tc_chunk_scan_kernel<T>), (int)smem_scan, a.device);
-        ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, h_np ? 1 : 0, status);
+        const uint8_t *seq_start = a.seq_idx ? reinterpret_cast<const uint8_t *>(base + lay.off_seq_start) : nullptr;
+        const uint8_t *seq_carry = reinterpret_cast<const uint8_t *>(base + lay.off_seq_carry);
+        ssd_tc_chunk_scan_kernel<T><<<dim3(a.nheads, nc * 2, a.batch), kScanThreads, smem_scan, stream>>>(tx, tC, tH, tCB, tz, tout, a, dtb, dAb, nc, h_np ? 1 : 0,
+                                                                                                          seq_start, seq_carry, status);
         MB200_CHECK_LAUNCH("ssd chunk_scan (tensor core)");
     }
     return MB200_OK;
@@ -1077,7 +1111,7 @@ int run_tc(const mb200_ssd_args &a, const SsdScratch &lay, int stage, bool h_np,
 bool ssd_tc_local_eligible(const mb200_ssd_args &a)
 {
     if (a.io_dtype != MB200_BF16 && a.io_dtype != MB200_F16) return false;
-    if (a.headdim != kP || a.dstate != kN || a.chunk_size != kQ || a.seq_idx || a.cu_seqlens) return false;
+    if (a.headdim != kP || a.dstate != kN || a.chunk_size != kQ) return false;
     if (!aligned16(a.x) || !aligned16(a.B) || !mult8(a.x_stride, 3) || !mult8(a.B_stride, 3)) return false;
     if ((int64_t)a.batch * ((a.seqlen + kQ - 1) / kQ) * a.nheads > INT32_MAX) return false;
     return encode_fn() != nullptr;

@@ -317,6 +317,35 @@ def test_packed_sequences(dtype, tol, Q, lens):
     assert_close(fin, var[-1:], tol, "final state is the last sequence's")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_packed_sequences_on_the_streaming_tensor_core_path(dtype):
+    """Enough heads for the fused state-stream launch, sequences that start and end inside chunks, at chunk borders and
+    that span several chunks; with an initial state for the first sequence.  Each sequence equals its own run."""
+    H, P, G, N, Q = 80, 64, 2, 128, 256
+    lens = [300, 212, 256, 700, 1, 67]                      # boundaries at 300, 512 (chunk border), 768 (border), 1468, 1469
+    inp, seq_idx, cu = _packed(77, lens, H, P, G, N, dtype)
+    g = torch.Generator().manual_seed(78)
+    init = 0.5 * torch.randn(1, H, P, N, generator=g)
+    c = {k: _c(v) for k, v in inp.items()}
+    out, fin, var = _fn()(c["x"], c["dt"], c["A"], c["B"], c["C"], Q, D=c["D"], z=c["z"], dt_bias=c["dt_bias"], initial_states=init.to(DEV),
+                          seq_idx=seq_idx.to(DEV), cu_seqlens=cu.to(DEV), dt_softplus=True, return_final_states=True, return_varlen_states=True)
+    assert _status() == 0
+    f = lambda t: None if t is None else t.float()
+    for i in (0, 1, 3, 4, 5):
+        sl = slice(int(cu[i]), int(cu[i + 1]))
+        # every ninth head keeps the oracle's share of the test short; heads 0, 9, ... 72 cover both groups
+        hs = list(range(0, H, 9))
+        gs = sorted({h // (H // G) for h in hs})
+        for gi in gs:
+            hg = [h for h in hs if h // (H // G) == gi]
+            want, wfin = oracle.ssd_chunk_scan(f(inp["x"][:, sl][:, :, hg]), f(inp["dt"][:, sl][:, :, hg]), inp["A"][hg], f(inp["B"][:, sl, gi:gi + 1]),
+                                               f(inp["C"][:, sl, gi:gi + 1]), Q, inp["D"][hg], f(inp["z"][:, sl][:, :, hg]), inp["dt_bias"][hg],
+                                               init[:, hg] if i == 0 else None, dt_softplus=True)
+            assert_close(out[:, sl][:, :, hg], want, TOL_BF16, f"packed out seq {i} group {gi}")
+            assert_close(var[i:i + 1][:, hg], wfin, TOL_BF16, f"varlen state seq {i} group {gi}")
+    assert_close(fin, var[-1:], TOL_BF16, "final state is the last sequence's")
+
+
 def test_seq_idx_without_varlen_states():
     inp, seq_idx, cu = _packed(61, [100, 92], 2, 16, 1, 16, torch.float32)
     c = {k: _c(v) for k, v in inp.items()}
