@@ -407,6 +407,9 @@ def fence(dist):
         torch.cuda.synchronize()
 
 
+BLOCKS_OVERRIDE = None      # --blocks: fixed number of timed blocks (profiling captures)
+
+
 def time_blocks(w, steps, warmup, dist, clock_index, target_s=0.3):
     """Median (over R blocks) of the device time of exactly `steps` steps, maximum over ranks per block."""
     for _ in range(warmup):
@@ -420,7 +423,7 @@ def time_blocks(w, steps, warmup, dist, clock_index, target_s=0.3):
     e1.record()
     torch.cuda.synchronize()
     est = all_max([e0.elapsed_time(e1) / 1e3], dist, w.dev)[0]
-    R = int(min(400, max(5, math.ceil(target_s / max(est, 1e-6)))))
+    R = int(min(400, max(5, math.ceil(target_s / max(est, 1e-6))))) if BLOCKS_OVERRIDE is None else BLOCKS_OVERRIDE
     times = []
     with ClockSampler(clock_index) as clk:
         for _ in range(R):
@@ -584,9 +587,12 @@ def main():
     ap.add_argument("--workload", dest="only", choices=["c0", "c1", "c2", "c3", "c4"], help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--blocks", type=int, default=None, help="fixed number of timed blocks instead of >= 0.3 s worth (profiling captures)")
     ap.add_argument("--batch", type=int, default=None,
                     help="shrink the problem (for ncu captures of a small case; not a benchmark result)")
     args = ap.parse_args()
+    global BLOCKS_OVERRIDE
+    BLOCKS_OVERRIDE = args.blocks
     warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

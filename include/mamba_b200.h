@@ -68,9 +68,21 @@ typedef struct mb200_scan_args {
     int64_t u_stride[2], delta_stride[2], z_stride[2], out_stride[2], pregate_stride[2]; /* {batch, dim} */
     int64_t A_stride[2];              /* {dim, dstate} */
     int64_t B_stride[3], C_stride[3];
+    void *scratch;                    /* optional, 16-byte aligned, see mb200_scan_scratch_bytes; NULL = none */
+    size_t scratch_bytes;
 } mb200_scan_args;
 
 int mb200_selective_scan_fwd(const mb200_scan_args *args, void *stream);
+
+/* No counterpart in the reference (its kernel walks a sequence from end to end inside one CTA,
+ * csrc/selective_scan/selective_scan_fwd_kernel.cuh:102-103).  A call with few (batch, channel) rows -- one batch
+ * row of a batch that was divided over several GPUs, say -- leaves most of the GPU idle if every row is walked from
+ * end to end.  Lent a scratch buffer, the library cuts the sequence into segments that run side by side: a first
+ * launch summarises each segment (end state from zero, product of decays), a fold chains the summaries, a second
+ * launch runs every segment from its true entering state.  *bytes receives the size that enables this for the sizes
+ * in args (pointers are not read), or 0 when the one-pass kernel is the faster choice.  Results agree with the
+ * one-pass scan to fp32 rounding. */
+int mb200_scan_scratch_bytes(const mb200_scan_args *args, size_t *bytes);
 
 /* Diagnostic, no counterpart in the reference.  The TMA-fed scan kernel bounds every wait on a copy or on
  * another warp; when a wait runs out it stops and records a non-zero code in a per-device word instead of

@@ -31,6 +31,7 @@ class ScanArgs(ctypes.Structure):
         ("u_stride", c_i64 * 2), ("delta_stride", c_i64 * 2), ("z_stride", c_i64 * 2),
         ("out_stride", c_i64 * 2), ("pregate_stride", c_i64 * 2), ("A_stride", c_i64 * 2),
         ("B_stride", c_i64 * 3), ("C_stride", c_i64 * 3),
+        ("scratch", c_vp), ("scratch_bytes", ctypes.c_size_t),
     ]
 
 
@@ -96,6 +97,7 @@ _PROTOTYPES = {
     "mb200_version": (ctypes.c_int, []),
     "mb200_last_error": (ctypes.c_char_p, []),
     "mb200_selective_scan_fwd": (ctypes.c_int, [ctypes.POINTER(ScanArgs), c_vp]),
+    "mb200_scan_scratch_bytes": (ctypes.c_int, [ctypes.POINTER(ScanArgs), ctypes.POINTER(ctypes.c_size_t)]),
     "mb200_scan_status": (ctypes.c_int, [c_i32, ctypes.POINTER(c_i32)]),
     "mb200_selective_state_update": (ctypes.c_int, [ctypes.POINTER(SsuArgs), c_vp]),
     "mb200_ssd_scratch_bytes": (ctypes.c_int, [ctypes.POINTER(SsdArgs), ctypes.POINTER(ctypes.c_size_t)]),

@@ -58,32 +58,42 @@ __global__ void __launch_bounds__(128) conv1d_cl_kernel(const mb200_conv1d_args 
             for (int i = 0; i < VEC; ++i) win[j][i] = 0.f;
         }
     }
-    for (int t = t_begin; t < t_end; ++t) {
-        float cur[VEC], acc[VEC];
-        row(t, cur);
-        bool keep[K - 1];                           // taps that reach into another packed sequence contribute nothing
+    constexpr int U = 4;                            // rows requested before any is used: the loads of a thread overlap
+    for (int tb = t_begin; tb < t_end; tb += U) {
+        float nxt[U][VEC];
 #pragma unroll
-        for (int j = 0; j < K - 1; ++j) {
-            const int tj = t - (K - 1) + j;
-            keep[j] = j >= lead && (!sid || tj < 0 || sid[tj] == sid[t]);
+        for (int u = 0; u < U; ++u)
+            if (tb + u < t_end) row(tb + u, nxt[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int t = tb + u;
+            if (t < t_end) {
+                float acc[VEC];
+                bool keep[K - 1];                   // taps that reach into another packed sequence contribute nothing
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) {
+                    const int tj = t - (K - 1) + j;
+                    keep[j] = j >= lead && (!sid || tj < 0 || sid[tj] == sid[t]);
+                }
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    float s = fmaf(w[K - 1][i], nxt[u][i], bias[i]);
+#pragma unroll
+                    for (int j = 0; j < K - 1; ++j)
+                        if (keep[j]) s = fmaf(w[j][i], win[j][i], s);
+                    acc[i] = act_silu(s, a.activation);
+                }
+                Vec16<T> o;
+                o.pack(acc);
+                o.store(out + (int64_t)t * a.out_stride[2]);
+#pragma unroll
+                for (int j = 0; j < K - 2; ++j)
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) win[j][i] = win[j + 1][i];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) win[K - 2][i] = nxt[u][i];
+            }
         }
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-            float s = fmaf(w[K - 1][i], cur[i], bias[i]);
-#pragma unroll
-            for (int j = 0; j < K - 1; ++j)
-                if (keep[j]) s = fmaf(w[j][i], win[j][i], s);
-            acc[i] = act_silu(s, a.activation);
-        }
-        Vec16<T> o;
-        o.pack(acc);
-        o.store(out + (int64_t)t * a.out_stride[2]);
-#pragma unroll
-        for (int j = 0; j < K - 2; ++j)
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) win[j][i] = win[j + 1][i];
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) win[K - 2][i] = cur[i];
     }
     if (a.final_states && t_end == a.seqlen) {      // the last width-1 inputs (reaching back into the initial state if need be)
         T *fs = static_cast<T *>(a.final_states) + (int64_t)b * a.final_stride[0];

@@ -557,6 +557,16 @@ constexpr int kHB = 8;             // steps per hand-off
 
 struct ScanMaps { CUtensorMap u, dt, z, out, B, C; };
 
+// Sequence split inside one launch: CTA (group of channels, batch row, segment) walks steps [s * seg_len, (s+1) * seg_len)
+// from the state h0[b][s] (zero when h0 is NULL).  A SUMMARY launch computes, for every segment but the last, the state
+// at its end from a zero start (hend) and the product of its decays (pdec); after a fold over the segments a second,
+// full launch runs every segment from its true entering state.  nseg = 1 is the plain one-pass scan.
+struct ScanSplit {
+    int nseg, seg_len;
+    const float *h0;        // (batch, nseg, dim, dstate) or NULL
+    float *hend, *pdec;     // (batch, nseg, dim, dstate), SUMMARY launches only
+};
+
 template <typename T, int NS>
 struct __align__(256) StreamSmem {
     uint8_t u[2][kStreamCh * 32];
@@ -577,8 +587,8 @@ struct __align__(256) StreamSmem {
 // byte offset of 16-byte chunk `chunk` of row `row` in a [rows x 32 B] SWIZZLE_32B tile (256-byte aligned)
 __device__ __forceinline__ int sw32_offset(int row, int chunk) { return row * 32 + ((chunk ^ ((row >> 2) & 1)) << 4); }
 
-template <typename T, int NS>
-__global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_args a, const __grid_constant__ ScanMaps maps)
+template <typename T, int NS, bool SUMMARY>
+__global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_args a, const __grid_constant__ ScanMaps maps, const ScanSplit sp)
 {
     using namespace tc;
     constexpr int TB = 32 / sizeof(T);                 // steps per tile (32 bytes of a row)
@@ -588,13 +598,17 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
     extern __shared__ __align__(256) uint8_t smem_raw[];
     StreamSmem<T, NS> &sm = *reinterpret_cast<StreamSmem<T, NS> *>(smem_raw);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int N = a.dstate, L = a.seqlen;
-    const int b = blockIdx.y;
+    const int N = a.dstate;
+    const int b = blockIdx.y / sp.nseg, seg = blockIdx.y % sp.nseg;
+    const int t_begin = seg * sp.seg_len;              // a multiple of the tile length
+    const int L = min(a.seqlen, t_begin + sp.seg_len) - t_begin;      // steps of my segment
     const int ch0 = blockIdx.x * kStreamCh;
     const int d = ch0 + lane;                          // my channel (dim is a multiple of 32 on this path)
     const int g = ch0 / (a.dim / a.ngroups);
     const int ntiles = (L + TB - 1) / TB, nhb = (L + kHB - 1) / kHB;
-    const bool has_z = a.z != nullptr;
+    const bool has_z = !SUMMARY && a.z != nullptr;
+    if (SUMMARY && seg == sp.nseg - 1) return;         // the last segment's end state is the full launch's business
+    if (L <= 0) return;                                // a segment past the end of a short sequence
     int *status = &g_scan_status;
     if (smem_u32(smem_raw) & 255u) {                   // the swizzle pattern of the tiles assumes this alignment
         if (threadIdx.x == 0) atomicCAS(status, 0, kStScanAlign);
@@ -614,24 +628,24 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
 
     if (warp == 0) {
         // ------------------------------------------------------------------ scalar warp
-        constexpr uint32_t kTileBytes = 2 * kStreamCh * 32 + 2 * NS * 32;
+        constexpr uint32_t kTileBytes = 2 * kStreamCh * 32 + (SUMMARY ? 1 : 2) * NS * 32;      // a summary needs no C
         auto issue_tile = [&](int k) {          // lane 0 only
             const int s = k & 1;
             mbar_expect_tx(&sm.full[s], kTileBytes);
-            tma_load_3d(sm.u[s], &maps.u, &sm.full[s], k * TB, ch0, b);
-            tma_load_3d(sm.dt[s], &maps.dt, &sm.full[s], k * TB, ch0, b);
-            tma_load_4d(sm.B[s], &maps.B, &sm.full[s], k * TB, 0, g, b);
-            tma_load_4d(sm.C[s], &maps.C, &sm.full[s], k * TB, 0, g, b);
+            tma_load_3d(sm.u[s], &maps.u, &sm.full[s], t_begin + k * TB, ch0, b);
+            tma_load_3d(sm.dt[s], &maps.dt, &sm.full[s], t_begin + k * TB, ch0, b);
+            tma_load_4d(sm.B[s], &maps.B, &sm.full[s], t_begin + k * TB, 0, g, b);
+            if (!SUMMARY) tma_load_4d(sm.C[s], &maps.C, &sm.full[s], t_begin + k * TB, 0, g, b);
         };
         auto issue_z = [&](int k) {             // lane 0 only
             const int s = k & 1;
             mbar_expect_tx(&sm.zfull[s], kStreamCh * 32);
-            tma_load_3d(sm.z[s], &maps.z, &sm.zfull[s], k * TB, ch0, b);
+            tma_load_3d(sm.z[s], &maps.z, &sm.zfull[s], t_begin + k * TB, ch0, b);
         };
         int issued = 0, zissued = 0, waited = 0, zwaited = 0;     // tiles requested / consumed (uniform across the warp)
         if (lane == 0) {
-            prefetch_tmap(&maps.u); prefetch_tmap(&maps.dt); prefetch_tmap(&maps.B); prefetch_tmap(&maps.C);
-            prefetch_tmap(&maps.out);
+            prefetch_tmap(&maps.u); prefetch_tmap(&maps.dt); prefetch_tmap(&maps.B);
+            if (!SUMMARY) { prefetch_tmap(&maps.C); prefetch_tmap(&maps.out); }
             if (has_z) prefetch_tmap(&maps.z);
         }
         for (int k = 0; k < 2 && k < ntiles; ++k) {
@@ -641,7 +655,7 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
         const float bias = a.delta_bias ? a.delta_bias[d] : 0.f;
         const float Dd = a.D ? a.D[d] : 0.f;
         const int st_t = lane / NS, st_n = lane % NS;     // my (tensor, state row) in the B/C conversion
-        const bool st_on = lane < 2 * NS;
+        const bool st_on = lane < (SUMMARY ? 1 : 2) * NS;
         bool ok = true;
 
         auto prologue = [&](int hb) {
@@ -704,6 +718,7 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
         auto epilogue = [&](int hb) {
             const int k = hb / HPT, s = k & 1, part = hb % HPT, buf = hb & 1;
             if (!mbar_wait(&sm.ydone[buf], (hb >> 1) & 1, status, kStScanYdone)) { ok = false; return; }
+            if (SUMMARY) return;                // nothing to put out: the wait only hands the buffers back
             if (part == 0) {
                 if (has_z) {
                     if (!mbar_wait(&sm.zfull[s], (k >> 1) & 1, status, kStScanZ)) { ok = false; return; }
@@ -755,7 +770,7 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
                 __syncwarp();
                 if (lane == 0) {
                     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(&maps.out),
-                                 "r"(smem_u32(sm.out[s])), "r"(k * TB), "r"(ch0), "r"(b)
+                                 "r"(smem_u32(sm.out[s])), "r"(t_begin + k * TB), "r"(ch0), "r"(b)
                                  : "memory");
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     if (has_z && k + 2 < ntiles) issue_z(k + 2);
@@ -790,8 +805,16 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
                 av[e] = n < N ? a.A[(int64_t)d * a.A_stride[0] + (int64_t)n * a.A_stride[1]] * kLog2e : 0.f;
             }
             A2[j] = pack2(av[0], av[1]);
-            h[j] = pack2(0.f, 0.f);
+            float h0v[2] = {0.f, 0.f};
+            if (sp.h0) {
+                const float *hp = sp.h0 + (((int64_t)b * sp.nseg + seg) * a.dim + d) * N;
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                    if (w * HS + 2 * j + e < N) h0v[e] = hp[w * HS + 2 * j + e];
+            }
+            h[j] = pack2(h0v[0], h0v[1]);
         }
+        float sum_dl = 0.f;          // SUMMARY: the decay product of the segment is 2^(A log2e * sum of dt)
         for (int hb = 0; hb < nhb; ++hb) {
             const int buf = hb & 1;
             if (!mbar_wait(&sm.ready[buf], (hb >> 1) & 1, status, kStScanReady)) break;
@@ -809,27 +832,49 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
                     const uint64_t dl2 = pack2(dls[i4], dls[i4]), du2 = pack2(dus[i4], dus[i4]);
                     uint64_t bp[HS / 2], cp[HS / 2];
                     lds_pairs<HS>(Bt + i * NS, bp);
-                    lds_pairs<HS>(Ct + i * NS, cp);
-                    uint64_t ya = pack2(0.f, 0.f), yb = pack2(0.f, 0.f);
+                    if (SUMMARY) {
+                        sum_dl += dls[i4];
 #pragma unroll
-                    for (int j = 0; j < HS / 2; ++j) {
-                        float x0, x1;
-                        unpack2(mul2(dl2, A2[j]), x0, x1);
-                        h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(du2, bp[j]));
-                        if (j & 1) yb = fma2(h[j], cp[j], yb);
-                        else ya = fma2(h[j], cp[j], ya);
+                        for (int j = 0; j < HS / 2; ++j) {
+                            float x0, x1;
+                            unpack2(mul2(dl2, A2[j]), x0, x1);
+                            h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(du2, bp[j]));
+                        }
+                        ys[i4] = 0.f;
+                    } else {
+                        lds_pairs<HS>(Ct + i * NS, cp);
+                        uint64_t ya = pack2(0.f, 0.f), yb = pack2(0.f, 0.f);
+#pragma unroll
+                        for (int j = 0; j < HS / 2; ++j) {
+                            float x0, x1;
+                            unpack2(mul2(dl2, A2[j]), x0, x1);
+                            h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(du2, bp[j]));
+                            if (j & 1) yb = fma2(h[j], cp[j], yb);
+                            else ya = fma2(h[j], cp[j], ya);
+                        }
+                        float s0, s1, s2, s3;
+                        unpack2(ya, s0, s1);
+                        unpack2(yb, s2, s3);
+                        ys[i4] = (s0 + s1) + (s2 + s3);
                     }
-                    float s0, s1, s2, s3;
-                    unpack2(ya, s0, s1);
-                    unpack2(yb, s2, s3);
-                    ys[i4] = (s0 + s1) + (s2 + s3);
                 }
-                *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(sm.yp[buf][w]) + off) = make_float4(ys[0], ys[1], ys[2], ys[3]);
+                if (!SUMMARY) *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(sm.yp[buf][w]) + off) = make_float4(ys[0], ys[1], ys[2], ys[3]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.ydone[buf]);
         }
-        if (a.last_state) {
+        if (SUMMARY) {
+            const int64_t o = (((int64_t)b * sp.nseg + seg) * a.dim + d) * N;
+#pragma unroll
+            for (int j = 0; j < HS / 2; ++j) {
+                float lo, hi, a0, a1;
+                unpack2(h[j], lo, hi);
+                unpack2(A2[j], a0, a1);
+                const int n = w * HS + 2 * j;
+                if (n < N) { sp.hend[o + n] = lo; sp.pdec[o + n] = ex2(a0 * sum_dl); }
+                if (n + 1 < N) { sp.hend[o + n + 1] = hi; sp.pdec[o + n + 1] = ex2(a1 * sum_dl); }
+            }
+        } else if (a.last_state && seg == sp.nseg - 1) {
             float *ls = a.last_state + ((int64_t)b * a.dim + d) * N;
 #pragma unroll
             for (int j = 0; j < HS / 2; ++j) {
@@ -842,7 +887,24 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
     }
 }
 
+// h0[b][s+1] = pdec[b][s] * h0[b][s] + hend[b][s] over the segments of a split sequence, one thread per (row, channel, state)
+__global__ void __launch_bounds__(256) scan_fold_segments_kernel(float *h0, const float *hend, const float *pdec, int nseg, int64_t per_seg,
+                                                                 int64_t rows)
+{
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= rows * per_seg) return;
+    const int64_t b = i / per_seg, e = i % per_seg;
+    float h = 0.f;
+    for (int s = 0; s < nseg; ++s) {
+        const int64_t o = (b * nseg + s) * per_seg + e;
+        h0[o] = h;
+        if (s + 1 < nseg) h = fmaf(pdec[o], h, hend[o]);
+    }
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T> int split_segments(const mb200_scan_args &a);
 
 // The warp-specialised kernel needs TMA-describable operands: 16-byte aligned bases and row strides, whole
 // groups of 32 channels, input-dependent B and C, and no separate pre-gate output.
@@ -852,7 +914,7 @@ bool stream_eligible(const mb200_scan_args &a)
     constexpr int VEC = 16 / sizeof(T);
     if (a.dstate > 16 || !a.B_variable || !a.C_variable || a.out_pregate) return false;
     if ((a.dim / a.ngroups) % kStreamCh != 0) return false;
-    if ((int64_t)a.batch * a.dim < 2LL * 32 * 148) return false;
+    if ((int64_t)a.batch * a.dim < 2LL * 32 * 148 && split_segments<T>(a) <= 1) return false;
     auto ok2 = [&](const void *p, const int64_t *s) { return aligned16(p) && s[0] > 0 && s[1] > 0 && s[0] % VEC == 0 && s[1] % VEC == 0; };
     auto ok3 = [&](const void *p, const int64_t *s) {
         return aligned16(p) && s[0] > 0 && s[1] > 0 && s[2] > 0 && s[0] % VEC == 0 && s[1] % VEC == 0 && s[2] % VEC == 0;
@@ -861,6 +923,24 @@ bool stream_eligible(const mb200_scan_args &a)
     if (a.z && !ok2(a.z, a.z_stride)) return false;
     if (!ok3(a.B, a.B_stride) || !ok3(a.C, a.C_stride)) return false;
     return encode_fn() != nullptr;
+}
+
+// How many segments the sequence is cut into (1 = one pass).  Cutting pays when the channel groups alone leave most
+// of the GPU idle: with G = batch * dim / 32 groups, nseg is the largest power of two with G * nseg CTAs in one wave
+// of 9 per SM.  It costs a second pass over every segment but the last, so it is used only from nseg = 8 up (fewer
+// segments measured no faster than one pass), with segments of at least 128 steps, and only when the caller lent
+// scratch for the summaries.
+template <typename T>
+int split_segments(const mb200_scan_args &a)
+{
+    const int64_t groups = (int64_t)a.batch * a.dim / kStreamCh;
+    if (groups <= 0) return 1;
+    int nseg = 1;
+    while (nseg < 16 && groups * nseg * 2 <= 9 * 148 && a.seqlen / (nseg * 2) >= 128) nseg *= 2;
+    if (nseg < 8) return 1;
+    const size_t need = 3 * sizeof(float) * (size_t)a.batch * nseg * a.dim * a.dstate;
+    if (!a.scratch || a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 15)) return 1;
+    return nseg;
 }
 
 template <typename T>
@@ -887,9 +967,31 @@ int launch_stream(const mb200_scan_args &a, cudaStream_t stream)
     if (a.z) ok = ok && rows(&maps.z, a.z, a.z_stride);
     else maps.z = maps.u;
     if (!ok) return 1;      // the driver refused a map (unusual strides): the caller uses the register-staged kernel
-    dim3 grid(a.dim / kStreamCh, a.batch);
-    if (ns == 8) scan_stream_kernel<T, 8><<<grid, 96, sizeof(StreamSmem<T, 8>), stream>>>(a, maps);
-    else scan_stream_kernel<T, 16><<<grid, 96, sizeof(StreamSmem<T, 16>), stream>>>(a, maps);
+    int nseg = split_segments<T>(a);
+    int seg_len = (int)((a.seqlen + TB - 1) / TB * TB);
+    if (nseg > 1) {
+        seg_len = (int)(((a.seqlen + nseg - 1) / nseg + TB - 1) / TB * TB);     // whole tiles per segment
+        nseg = (a.seqlen + seg_len - 1) / seg_len;                              // rounding up may leave the last ones empty
+    }
+    if (nseg <= 1) {
+        const ScanSplit one = {1, seg_len, nullptr, nullptr, nullptr};
+        dim3 grid(a.dim / kStreamCh, a.batch);
+        if (ns == 8) scan_stream_kernel<T, 8, false><<<grid, 96, sizeof(StreamSmem<T, 8>), stream>>>(a, maps, one);
+        else scan_stream_kernel<T, 16, false><<<grid, 96, sizeof(StreamSmem<T, 16>), stream>>>(a, maps, one);
+        return MB200_OK;
+    }
+    // Few channel groups: the sequence is cut into nseg segments that run side by side.  A first launch summarises
+    // every segment but the last from a zero state (end state + decay product), a fold turns the summaries into the
+    // state entering each segment, a second launch runs every segment from there.
+    const int64_t per_seg = (int64_t)a.dim * a.dstate, region = (int64_t)a.batch * nseg * per_seg;
+    float *h0 = static_cast<float *>(a.scratch), *hend = h0 + region, *pdec = hend + region;
+    const ScanSplit sum = {nseg, seg_len, nullptr, hend, pdec}, full = {nseg, seg_len, h0, nullptr, nullptr};
+    dim3 grid(a.dim / kStreamCh, a.batch * nseg);       // in the summary launch the CTAs of the last segment return at once
+    if (ns == 8) scan_stream_kernel<T, 8, true><<<grid, 96, sizeof(StreamSmem<T, 8>), stream>>>(a, maps, sum);
+    else scan_stream_kernel<T, 16, true><<<grid, 96, sizeof(StreamSmem<T, 16>), stream>>>(a, maps, sum);
+    scan_fold_segments_kernel<<<(unsigned)((a.batch * per_seg + 255) / 256), 256, 0, stream>>>(h0, hend, pdec, nseg, per_seg, a.batch);
+    if (ns == 8) scan_stream_kernel<T, 8, false><<<grid, 96, sizeof(StreamSmem<T, 8>), stream>>>(a, maps, full);
+    else scan_stream_kernel<T, 16, false><<<grid, 96, sizeof(StreamSmem<T, 16>), stream>>>(a, maps, full);
     return MB200_OK;
 }
 
@@ -948,6 +1050,22 @@ int launch_scan(const mb200_scan_args &a, cudaStream_t stream)
 
 }  // namespace
 }  // namespace mb200
+
+extern "C" int mb200_scan_scratch_bytes(const mb200_scan_args *args, size_t *bytes)
+{
+    using namespace mb200;
+    if (!args || !bytes) return fail(MB200_ERR_BAD_ARG, "scan_scratch_bytes: NULL argument");
+    const mb200_scan_args &a = *args;
+    *bytes = 0;
+    if (a.batch <= 0 || a.dim <= 0 || a.dstate <= 0 || a.dstate > 16 || a.seqlen <= 0) return MB200_OK;
+    // the size that would let the sequence be cut: ask the policy with a scratch that is certainly large enough
+    mb200_scan_args probe = a;
+    probe.scratch = reinterpret_cast<void *>(uintptr_t(256));
+    probe.scratch_bytes = ~size_t(0);
+    const int nseg = split_segments<float>(probe);
+    if (nseg > 1) *bytes = 3 * sizeof(float) * (size_t)a.batch * nseg * a.dim * a.dstate;
+    return MB200_OK;
+}
 
 extern "C" int mb200_scan_status(int device, int *status)
 {

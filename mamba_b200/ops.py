@@ -99,6 +99,11 @@ def _selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_so
     L.set_strides(a.A_stride, A, 2)
     L.set_strides(a.B_stride, B, 3 if B_var else 2)
     L.set_strides(a.C_stride, C, 3 if C_var else 2)
+    # few (batch, channel) rows: lend the library scratch so that it can cut the sequence into segments that run side by side
+    need = ctypes.c_size_t(0)
+    L.check(L.lib().mb200_scan_scratch_bytes(ctypes.byref(a), ctypes.byref(need)))
+    scratch = torch.empty(need.value, dtype=torch.uint8, device=u.device) if need.value else None
+    a.scratch, a.scratch_bytes = L.ptr(scratch), need.value
     L.check(L.lib().mb200_selective_scan_fwd(ctypes.byref(a), L.stream_ptr(u.device)))
     return out if not return_last_state else (out, last_state)
 

@@ -136,6 +136,35 @@ def test_tma_fed_kernel(dtype, tol, L, N, groups, gated):
     assert_close(got_last, want_last, tol, "tma-fed last_state")
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_FP32), (torch.bfloat16, TOL_BF16)])
+@pytest.mark.parametrize("batch,dim,L,N,gated", [(1, 5120, 2048, 16, True), (1, 1024, 2100, 16, True), (2, 512, 4096, 8, False), (1, 2048, 1030, 12, True)])
+def test_few_channel_rows_cut_the_sequence_into_segments(dtype, tol, batch, dim, L, N, gated):
+    """Few (batch, channel) rows -- one batch row of a divided batch -- make the library cut the sequence into segments
+    that run side by side (summary launch, fold, full launch).  Output and last state equal the oracle's, which walks
+    every row from end to end; ragged lengths leave the last segment short or empty."""
+    from mamba_b200 import _lib, ops
+    import ctypes
+    inp = make_inputs(300 + L, batch, dim, L, N, 1, dtype, has_z=gated, has_D=gated, bench_style=True)
+    a = _lib.ScanArgs()
+    a.batch, a.dim, a.seqlen, a.dstate, a.ngroups = batch, dim, L, N, 1
+    need = ctypes.c_size_t(0)
+    _lib.check(_lib.lib().mb200_scan_scratch_bytes(ctypes.byref(a), ctypes.byref(need)))
+    assert need.value > 0, "this shape is meant to take the segmented path"
+    want, want_last = oracle.selective_scan(inp["u"].float(), inp["delta"].float(), inp["A"], inp["B"].float(),
+                                            inp["C"].float(), inp["D"], None if inp["z"] is None else inp["z"].float(),
+                                            inp["delta_bias"], delta_softplus=True, return_last_state=True)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    for k in ("u", "delta", "z", "B", "C"):
+        if c[k] is not None:
+            c[k] = _row_padded(c[k])
+    out = _row_padded(torch.empty_like(c["u"]))
+    got, got_last = ops._selective_scan(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], c["z"], c["delta_bias"],
+                                        delta_softplus=True, return_last_state=True, out=out)
+    assert ops.scan_status() == 0
+    assert_close(got, want, tol, "segmented out")
+    assert_close(got_last, want_last, tol, "segmented last_state")
+
+
 def test_tma_fed_kernel_plain_delta():
     """The same kernel without softplus, bias, skip and gate (delta used as given)."""
     from mamba_b200 import ops
