@@ -3,6 +3,8 @@
 //   gated RMSNorm (optionally per group) after the SSD scan.
 // Both are pure streaming work (every input read once, every output written once), so the kernels are built
 // around 16-byte accesses and keep everything else in registers.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace mb200 {
@@ -12,96 +14,146 @@ constexpr int kMaxWidth = 4;
 
 __device__ __forceinline__ float act_silu(float v, int activation) { return activation ? v / (1.f + __expf(-v)) : v; }
 
+// VEC consecutive parameters (weight or bias) starting at a column that is a multiple of VEC, as floats: one or two
+// 16-byte loads when the parameter tensor allows, element loads otherwise.
+template <int VEC>
+__device__ __forceinline__ void load_params(const void *p, int dtype, bool vec_ok, int col, float (&f)[VEC])
+{
+    if (vec_ok && dtype == MB200_F32) {
+#pragma unroll
+        for (int q = 0; q < VEC / 4; ++q) {
+            const float4 v = reinterpret_cast<const float4 *>(static_cast<const float *>(p) + col)[q];
+            f[4 * q] = v.x; f[4 * q + 1] = v.y; f[4 * q + 2] = v.z; f[4 * q + 3] = v.w;
+        }
+    } else if (vec_ok && VEC == 8 && dtype == MB200_BF16) {
+        Vec16<__nv_bfloat16> v;
+        v.load(static_cast<const __nv_bfloat16 *>(p) + col);
+        float t[8];
+        v.unpack(t);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) f[i] = t[i % 8];
+    } else if (vec_ok && VEC == 8 && dtype == MB200_F16) {
+        Vec16<__half> v;
+        v.load(static_cast<const __half *>(p) + col);
+        float t[8];
+        v.unpack(t);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) f[i] = t[i % 8];
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) f[i] = load_any(p, dtype, col + i);
+    }
+}
+
+// silu for the element-wise kernels: exact form for fp32 tensors, the single-MUFU tanh form (relative error 2^-11,
+// below the rounding step of a 16-bit result) for 16-bit ones
+template <typename T> __device__ __forceinline__ float silu_io(float z)
+{
+    if constexpr (sizeof(T) == 2) return silu_for_bf16(z);
+    else return z / (1.f + __expf(-z));
+}
+
 // ---- conv1d, channels contiguous (the layout Mamba-2 hands over: a (batch, seqlen, dim) tensor viewed as
 // (batch, dim, seqlen)).  A thread owns VEC adjacent channels and walks a segment of the sequence with the last
 // width-1 rows of its channels in registers, so every row is read once (plus width-1 rows of halo per segment).
+constexpr int kConvSteps = 16;      // output steps per thread of the channels-contiguous kernel
 template <typename T>
-__global__ void __launch_bounds__(128) conv1d_cl_kernel(const mb200_conv1d_args a, const int seg)
+__global__ void __launch_bounds__(128, 3) conv1d_cl_kernel(const mb200_conv1d_args a)
 {
     constexpr int VEC = 16 / sizeof(T);
-    constexpr int K = kMaxWidth;
+    constexpr int K = kMaxWidth, TT = kConvSteps;
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * VEC;
     if (c0 >= a.dim) return;
     const int b = blockIdx.z;
-    const int t_begin = blockIdx.y * seg, t_end = min(t_begin + seg, a.seqlen);
+    const int t0 = blockIdx.y * TT;
     const int W = a.width, lead = K - W;        // taps are kept right-aligned: tap k of K reads step t - (K-1) + k, the first `lead` weigh 0
-    float w[K][VEC], bias[VEC], win[K - 1][VEC];
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        bias[i] = a.bias ? load_any(a.bias, a.w_dtype, c0 + i) : 0.f;
-#pragma unroll
-        for (int k = 0; k < K; ++k) w[k][i] = k >= lead ? load_any(a.weight, a.w_dtype, (int64_t)(c0 + i) * W + (k - lead)) : 0.f;
-    }
     const T *x = static_cast<const T *>(a.x) + (int64_t)b * a.x_stride[0] + c0;
     T *out = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + c0;
     const int32_t *sid = a.seq_idx ? a.seq_idx + (int64_t)b * a.seqlen : nullptr;
-    auto row = [&](int t, float (&v)[VEC]) {       // x[:, t] for my channels; before the sequence: the initial state or zero
-        if (t >= 0) {
-            Vec16<T> p;
-            p.load(x + (int64_t)t * a.x_stride[2]);
-            p.unpack(v);
-        } else if (a.initial_states && t >= -(W - 1)) {
-            const T *st = static_cast<const T *>(a.initial_states) + (int64_t)b * a.init_stride[0];
+    // rows t0 - (K-1) .. t0 + TT - 1 of my channels: every load is issued before any row is used
+    Vec16<T> raw[TT + K - 1];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) v[i] = to_float(st[(int64_t)(c0 + i) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]);
-        } else {
+    for (int r = 0; r < TT + K - 1; ++r) {
+        const int t = t0 - (K - 1) + r;
+        raw[r].raw = make_uint4(0u, 0u, 0u, 0u);
+        if (t >= 0 && t < a.seqlen && r >= lead) raw[r].load(x + (int64_t)t * a.x_stride[2]);
+    }
+    float w[K][VEC], bias[VEC];
+    const bool wvec = (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0;
+    if (a.bias) load_params<VEC>(a.bias, a.w_dtype, wvec, c0, bias);
+    if (!a.bias) {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) v[i] = 0.f;
-        }
-    };
+        for (int i = 0; i < VEC; ++i) bias[i] = 0.f;
+    }
+    if (W == K && (reinterpret_cast<uintptr_t>(a.weight) & 15) == 0) {
+        // the K taps of my VEC channels are VEC * K consecutive parameters: whole packets
+        float flat[K][VEC];                          // flat[q][j] = parameter q * VEC + j = tap (q * VEC + j) % K of channel (q * VEC + j) / K
+#pragma unroll
+        for (int q = 0; q < K; ++q) load_params<VEC>(a.weight, a.w_dtype, true, c0 * K + q * VEC, flat[q]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+#pragma unroll
+            for (int k = 0; k < K; ++k) w[k][i] = flat[(i * K + k) / VEC][(i * K + k) % VEC];
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+#pragma unroll
+            for (int k = 0; k < K; ++k) w[k][i] = k >= lead ? load_any(a.weight, a.w_dtype, (int64_t)(c0 + i) * W + (k - lead)) : 0.f;
+    }
+    float win[K - 1][VEC];                          // the K-1 rows before the step being formed
 #pragma unroll
     for (int j = 0; j < K - 1; ++j) {
-        if (j >= lead) {
-            row(t_begin - (K - 1) + j, win[j]);
+        const int t = t0 - (K - 1) + j;
+        if (t < 0 && j >= lead && a.initial_states) {       // before the sequence: the carried state
+            const T *st = static_cast<const T *>(a.initial_states) + (int64_t)b * a.init_stride[0];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) win[j][i] = to_float(st[(int64_t)(c0 + i) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]);
         } else {
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) win[j][i] = 0.f;
+            raw[j].unpack(win[j]);
         }
     }
-    constexpr int U = 4;                            // rows requested before any is used: the loads of a thread overlap
-    for (int tb = t_begin; tb < t_end; tb += U) {
-        float nxt[U][VEC];
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-            if (tb + u < t_end) row(tb + u, nxt[u]);
+    for (int u = 0; u < TT; ++u) {
+        const int t = t0 + u;
+        float cur[VEC], acc[VEC];
+        raw[K - 1 + u].unpack(cur);
+        bool keep[K - 1];                           // taps that reach into another packed sequence contribute nothing
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int t = tb + u;
-            if (t < t_end) {
-                float acc[VEC];
-                bool keep[K - 1];                   // taps that reach into another packed sequence contribute nothing
-#pragma unroll
-                for (int j = 0; j < K - 1; ++j) {
-                    const int tj = t - (K - 1) + j;
-                    keep[j] = j >= lead && (!sid || tj < 0 || sid[tj] == sid[t]);
-                }
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) {
-                    float s = fmaf(w[K - 1][i], nxt[u][i], bias[i]);
-#pragma unroll
-                    for (int j = 0; j < K - 1; ++j)
-                        if (keep[j]) s = fmaf(w[j][i], win[j][i], s);
-                    acc[i] = act_silu(s, a.activation);
-                }
-                Vec16<T> o;
-                o.pack(acc);
-                o.store(out + (int64_t)t * a.out_stride[2]);
-#pragma unroll
-                for (int j = 0; j < K - 2; ++j)
-#pragma unroll
-                    for (int i = 0; i < VEC; ++i) win[j][i] = win[j + 1][i];
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) win[K - 2][i] = nxt[u][i];
-            }
+        for (int j = 0; j < K - 1; ++j) {
+            const int tj = t - (K - 1) + j;
+            keep[j] = j >= lead && (!sid || tj < 0 || t >= a.seqlen || sid[tj] == sid[t]);
         }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            float s = fmaf(w[K - 1][i], cur[i], bias[i]);
+#pragma unroll
+            for (int j = 0; j < K - 1; ++j)
+                if (keep[j]) s = fmaf(w[j][i], win[j][i], s);
+            acc[i] = a.activation ? silu_io<T>(s) : s;
+        }
+        if (t < a.seqlen) {
+            Vec16<T> o;
+            o.pack(acc);
+            o.store(out + (int64_t)t * a.out_stride[2]);
+        }
+#pragma unroll
+        for (int j = 0; j < K - 2; ++j)
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) win[j][i] = win[j + 1][i];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) win[K - 2][i] = cur[i];
     }
-    if (a.final_states && t_end == a.seqlen) {      // the last width-1 inputs (reaching back into the initial state if need be)
+    if (a.final_states && t0 + TT >= a.seqlen && t0 < a.seqlen) {      // the last width-1 inputs (reaching back into the initial state if need be)
         T *fs = static_cast<T *>(a.final_states) + (int64_t)b * a.final_stride[0];
         for (int j = 0; j < W - 1; ++j) {
-            float v[VEC];
-            row(a.seqlen - (W - 1) + j, v);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) fs[(int64_t)(c0 + i) * a.final_stride[1] + (int64_t)j * a.final_stride[2]] = from_float<T>(v[i]);
+            const int t = a.seqlen - (W - 1) + j;
+            for (int i = 0; i < VEC; ++i) {
+                T v = from_float<T>(0.f);
+                if (t >= 0) v = x[(int64_t)t * a.x_stride[2] + i];
+                else if (a.initial_states)
+                    v = static_cast<const T *>(a.initial_states)[(int64_t)b * a.init_stride[0] + (int64_t)(c0 + i) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]];
+                fs[(int64_t)(c0 + i) * a.final_stride[1] + (int64_t)j * a.final_stride[2]] = v;
+            }
         }
     }
 }
@@ -182,8 +234,8 @@ __global__ void __launch_bounds__(256) conv1d_update_kernel(const mb200_conv1d_u
 
 // ---- gated RMSNorm: one CTA per (row, group).  y = x * rstd * weight (+ bias) with the gate silu(z) applied to x
 // before the statistics (norm_before_gate = 0) or to y after them (= 1); all arithmetic in fp32.
-template <typename T, int PER>      // PER 16-byte packets per thread
-__global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const mb200_rmsnorm_args a, const int threads)
+template <typename T, int PER, bool GATE_AFTER>      // PER 16-byte packets per thread; gate applied after the norm or before it
+__global__ void __launch_bounds__(256, 3) rmsnorm_gated_kernel(const mb200_rmsnorm_args a, const int threads, const int wvec)
 {
     constexpr int VEC = 16 / sizeof(T);
     __shared__ float red[8];
@@ -193,25 +245,28 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const mb200_rmsnorm_
     const T *x = static_cast<const T *>(a.x) + rowi * a.x_stride + (int64_t)g * G;
     const T *z = a.z ? static_cast<const T *>(a.z) + rowi * a.z_stride + (int64_t)g * G : nullptr;
     T *out = static_cast<T *>(a.out) + rowi * a.out_stride + (int64_t)g * G;
-    float v[PER][VEC], zs[PER][VEC];
+    // every packet of the row is requested before any is used
+    Vec16<T> px[PER], pz[PER];
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+        const int e = (p * threads + threadIdx.x) * VEC;
+        if (e < G) {
+            px[p].load(x + e);
+            if (z) pz[p].load(z + e);
+        }
+    }
+    float v[PER][VEC];
     float ss = 0.f;
 #pragma unroll
     for (int p = 0; p < PER; ++p) {
         const int e = (p * threads + threadIdx.x) * VEC;
         if (e < G) {
-            Vec16<T> px;
-            px.load(x + e);
-            px.unpack(v[p]);
-            if (z) {
-                Vec16<T> pz;
-                pz.load(z + e);
-                pz.unpack(zs[p]);
+            px[p].unpack(v[p]);
+            if (z && !GATE_AFTER) {
+                float zz[VEC];
+                pz[p].unpack(zz);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) zs[p][i] = zs[p][i] / (1.f + __expf(-zs[p][i]));
-                if (!a.norm_before_gate) {
-#pragma unroll
-                    for (int i = 0; i < VEC; ++i) v[p][i] *= zs[p][i];
-                }
+                for (int i = 0; i < VEC; ++i) v[p][i] *= silu_io<T>(zz[i]);
             }
 #pragma unroll
             for (int i = 0; i < VEC; ++i) ss = fmaf(v[p][i], v[p][i], ss);
@@ -228,13 +283,20 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const mb200_rmsnorm_
     for (int p = 0; p < PER; ++p) {
         const int e = (p * threads + threadIdx.x) * VEC;
         if (e < G) {
-            float y[VEC];
+            float y[VEC], wv[VEC];
+            load_params<VEC>(a.weight, a.w_dtype, wvec != 0, g * G + e, wv);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                const int col = g * G + e + i;
-                y[i] = v[p][i] * rstd * load_any(a.weight, a.w_dtype, col);
-                if (a.bias) y[i] += load_any(a.bias, a.w_dtype, col);
-                if (z && a.norm_before_gate) y[i] *= zs[p][i];
+            for (int i = 0; i < VEC; ++i) y[i] = v[p][i] * rstd * wv[i];
+            if (a.bias) {
+                load_params<VEC>(a.bias, a.w_dtype, wvec != 0, g * G + e, wv);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) y[i] += wv[i];
+            }
+            if (z && GATE_AFTER) {
+                float zz[VEC];
+                pz[p].unpack(zz);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) y[i] *= silu_io<T>(zz[i]);
             }
             Vec16<T> po;
             po.pack(y);
@@ -287,13 +349,11 @@ int launch_conv1d(const mb200_conv1d_args &a, cudaStream_t stream)
 {
     constexpr int VEC = 16 / sizeof(T);
     const bool channels_last = a.x_stride[1] == 1 && a.out_stride[1] == 1 && a.dim % VEC == 0 && aligned16(a.x) && aligned16(a.out) &&
-                               a.x_stride[0] % VEC == 0 && a.x_stride[2] % VEC == 0 && a.out_stride[0] % VEC == 0 && a.out_stride[2] % VEC == 0;
+                               a.x_stride[0] % VEC == 0 && a.x_stride[2] % VEC == 0 && a.out_stride[0] % VEC == 0 && a.out_stride[2] % VEC == 0 &&
+                               (a.seqlen + kConvSteps - 1) / kConvSteps <= 65535;
     if (channels_last) {
         const int cols = (a.dim / VEC + 127) / 128;
-        // enough segments to fill the GPU several times over, long enough that the halo rows stay a few per cent
-        int seg = 64;
-        while (seg > 16 && (int64_t)cols * a.batch * ((a.seqlen + seg - 1) / seg) < 4 * 148) seg /= 2;
-        conv1d_cl_kernel<T><<<dim3(cols, (a.seqlen + seg - 1) / seg, a.batch), 128, 0, stream>>>(a, seg);
+        conv1d_cl_kernel<T><<<dim3(cols, (a.seqlen + kConvSteps - 1) / kConvSteps, a.batch), 128, 0, stream>>>(a);
     } else {
         const int64_t work = (int64_t)a.dim * ((a.seqlen + kRun - 1) / kRun);
         conv1d_any_kernel<T><<<dim3((unsigned)((work + 255) / 256), a.batch), 256, 0, stream>>>(a);
@@ -317,9 +377,15 @@ int launch_rmsnorm(const mb200_rmsnorm_args &a, cudaStream_t stream)
     int threads = 32;
     while (threads < 256 && threads * 2 <= packets) threads *= 2;      // a packet or two per thread while the group allows
     const int per = (packets + threads - 1) / threads;
-    if (per <= 1) rmsnorm_gated_kernel<T, 1><<<grid, threads, 0, stream>>>(a, threads);
-    else if (per <= 2) rmsnorm_gated_kernel<T, 2><<<grid, threads, 0, stream>>>(a, threads);
-    else rmsnorm_gated_kernel<T, 4><<<grid, threads, 0, stream>>>(a, threads);
+    const int wvec = aligned16(a.weight) && (!a.bias || aligned16(a.bias)) ? 1 : 0;      // columns are multiples of VEC: parameter packets are aligned too
+    auto go = [&](auto per_tag) {
+        constexpr int P = decltype(per_tag)::value;
+        if (a.norm_before_gate) rmsnorm_gated_kernel<T, P, true><<<grid, threads, 0, stream>>>(a, threads, wvec);
+        else rmsnorm_gated_kernel<T, P, false><<<grid, threads, 0, stream>>>(a, threads, wvec);
+    };
+    if (per <= 1) go(std::integral_constant<int, 1>{});
+    else if (per <= 2) go(std::integral_constant<int, 2>{});
+    else go(std::integral_constant<int, 4>{});
     return MB200_OK;
 }
 

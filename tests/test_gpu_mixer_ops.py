@@ -160,3 +160,41 @@ def test_split_conv1d_scan_combined(dtype, tol, rmsnorm, before, d_nonssm, ngrou
     assert out.shape == (b, L, d_model) and out.dtype == dtype
     assert_close(out, want, tol, "block out")
     assert_close(fin, wfin, tol, "block final_states")
+
+
+def _time_ms(fn, iters=20):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def test_streaming_rates_at_layer_size(capsys):
+    """Both steps are pure streaming work: at the size of a Mamba-2 2.7B layer on 8 x 4096 tokens (inputs larger than
+    L2) the achieved rate of algorithmic bytes (input read once + output written once) is reported and must be a
+    sizeable share of what a device-to-device copy reaches on this part."""
+    from mamba_b200 import causal_conv1d_fn, rmsnorm_fn
+    b, L, d_ssm, ngroups, dstate = 8, 4096, 5120, 1, 128
+    conv_dim = d_ssm + 2 * ngroups * dstate
+    g = torch.Generator(device=DEV).manual_seed(0)
+    xBC = torch.randn(b, L, conv_dim, generator=g, device=DEV).bfloat16()
+    w, bias = torch.randn(conv_dim, 4, generator=g, device=DEV).bfloat16(), torch.randn(conv_dim, generator=g, device=DEV).bfloat16()
+    y, z = torch.randn(b, L, d_ssm, generator=g, device=DEV).bfloat16(), torch.randn(b, L, d_ssm, generator=g, device=DEV).bfloat16()
+    nw = torch.ones(d_ssm, device=DEV, dtype=torch.bfloat16)
+    copy_src, copy_dst = torch.empty(1 << 28, device=DEV, dtype=torch.uint8), torch.empty(1 << 28, device=DEV, dtype=torch.uint8)
+    t_copy = _time_ms(lambda: copy_dst.copy_(copy_src))
+    t_conv = _time_ms(lambda: causal_conv1d_fn(xBC.transpose(1, 2), w, bias, activation="silu"))
+    t_norm = _time_ms(lambda: rmsnorm_fn(y, nw, None, z=z, eps=1e-5, group_size=d_ssm // ngroups, norm_before_gate=False))
+    copy_gbs = 2 * (1 << 28) / t_copy / 1e6
+    conv_gbs = 2 * xBC.numel() * 2 / t_conv / 1e6
+    norm_gbs = 3 * y.numel() * 2 / t_norm / 1e6
+    with capsys.disabled():
+        print(f"\n[mixer ops] copy {copy_gbs:.0f} GB/s; causal_conv1d (channels-last, {conv_dim} ch) {t_conv * 1e3:.1f} us = {conv_gbs:.0f} GB/s "
+              f"({conv_gbs / copy_gbs:.2f} of copy); gated rmsnorm ({d_ssm} cols) {t_norm * 1e3:.1f} us = {norm_gbs:.0f} GB/s ({norm_gbs / copy_gbs:.2f} of copy)")
+    assert conv_gbs > 0.3 * copy_gbs and norm_gbs > 0.3 * copy_gbs
