@@ -100,36 +100,64 @@ __global__ void __launch_bounds__(128, 3) conv1d_cl_kernel(const mb200_conv1d_ar
 #pragma unroll
             for (int k = 0; k < K; ++k) w[k][i] = k >= lead ? load_any(a.weight, a.w_dtype, (int64_t)(c0 + i) * W + (k - lead)) : 0.f;
     }
-    float win[K - 1][VEC];                          // the K-1 rows before the step being formed
+    // From here on channel pairs travel as packed fp32 pairs (one FMA-pipe issue slot for two channels).
+    constexpr int NP = VEC / 2;
+    uint64_t w2[K][NP], bias2[NP], win[K - 1][NP];   // win: the K-1 rows before the step being formed
+#pragma unroll
+    for (int q = 0; q < NP; ++q) {
+        bias2[q] = pack2(bias[2 * q], bias[2 * q + 1]);
+#pragma unroll
+        for (int k = 0; k < K; ++k) w2[k][q] = pack2(w[k][2 * q], w[k][2 * q + 1]);
+    }
+    auto unpack_row = [&](const Vec16<T> &r, uint64_t (&o)[NP]) {
+        float f[VEC];
+        r.unpack(f);
+#pragma unroll
+        for (int q = 0; q < NP; ++q) o[q] = pack2(f[2 * q], f[2 * q + 1]);
+    };
 #pragma unroll
     for (int j = 0; j < K - 1; ++j) {
         const int t = t0 - (K - 1) + j;
         if (t < 0 && j >= lead && a.initial_states) {       // before the sequence: the carried state
             const T *st = static_cast<const T *>(a.initial_states) + (int64_t)b * a.init_stride[0];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) win[j][i] = to_float(st[(int64_t)(c0 + i) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]);
+            for (int q = 0; q < NP; ++q)
+                win[j][q] = pack2(to_float(st[(int64_t)(c0 + 2 * q) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]),
+                                  to_float(st[(int64_t)(c0 + 2 * q + 1) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]));
         } else {
-            raw[j].unpack(win[j]);
+            unpack_row(raw[j], win[j]);
         }
     }
+    const uint64_t half2 = pack2(0.5f, 0.5f);
 #pragma unroll
     for (int u = 0; u < TT; ++u) {
         const int t = t0 + u;
-        float cur[VEC], acc[VEC];
-        raw[K - 1 + u].unpack(cur);
+        uint64_t cur[NP];
+        unpack_row(raw[K - 1 + u], cur);
         bool keep[K - 1];                           // taps that reach into another packed sequence contribute nothing
 #pragma unroll
         for (int j = 0; j < K - 1; ++j) {
             const int tj = t - (K - 1) + j;
             keep[j] = j >= lead && (!sid || tj < 0 || t >= a.seqlen || sid[tj] == sid[t]);
         }
+        float acc[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-            float s = fmaf(w[K - 1][i], cur[i], bias[i]);
+        for (int q = 0; q < NP; ++q) {
+            uint64_t s2 = fma2(w2[K - 1][q], cur[q], bias2[q]);
 #pragma unroll
             for (int j = 0; j < K - 1; ++j)
-                if (keep[j]) s = fmaf(w[j][i], win[j][i], s);
-            acc[i] = a.activation ? silu_io<T>(s) : s;
+                if (keep[j]) s2 = fma2(w2[j][q], win[j][q], s2);
+            if (a.activation && sizeof(T) == 2) {    // silu(s) = h + h tanh(h), h = s / 2 (16-bit results)
+                const uint64_t h2 = mul2(s2, half2);
+                float h0, h1;
+                unpack2(h2, h0, h1);
+                s2 = fma2(h2, pack2(tanh_approx(h0), tanh_approx(h1)), h2);
+            }
+            unpack2(s2, acc[2 * q], acc[2 * q + 1]);
+            if (a.activation && sizeof(T) == 4) {
+                acc[2 * q] = silu_io<T>(acc[2 * q]);
+                acc[2 * q + 1] = silu_io<T>(acc[2 * q + 1]);
+            }
         }
         if (t < a.seqlen) {
             Vec16<T> o;
@@ -139,9 +167,9 @@ __global__ void __launch_bounds__(128, 3) conv1d_cl_kernel(const mb200_conv1d_ar
 #pragma unroll
         for (int j = 0; j < K - 2; ++j)
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) win[j][i] = win[j + 1][i];
+            for (int q = 0; q < NP; ++q) win[j][q] = win[j + 1][q];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) win[K - 2][i] = cur[i];
+        for (int q = 0; q < NP; ++q) win[K - 2][q] = cur[q];
     }
     if (a.final_states && t0 + TT >= a.seqlen && t0 < a.seqlen) {      // the last width-1 inputs (reaching back into the initial state if need be)
         T *fs = static_cast<T *>(a.final_states) + (int64_t)b * a.final_stride[0];
