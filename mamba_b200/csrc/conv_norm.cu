@@ -14,12 +14,50 @@ constexpr int kMaxWidth = 4;
 
 __device__ __forceinline__ float act_silu(float v, int activation) { return activation ? v / (1.f + __expf(-v)) : v; }
 
+// A packet of PB bytes (16 or 8) of T, widened to floats and back.
+template <typename T, int PB> struct Pkt {
+    static constexpr int N = PB / sizeof(T);
+    uint32_t w[PB / 4];
+    __device__ __forceinline__ void zero()
+    {
+#pragma unroll
+        for (int i = 0; i < PB / 4; ++i) w[i] = 0u;
+    }
+    __device__ __forceinline__ void load(const T *p)
+    {
+        if constexpr (PB == 16) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(p);
+            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+        } else {
+            const uint2 v = *reinterpret_cast<const uint2 *>(p);
+            w[0] = v.x; w[1] = v.y;
+        }
+    }
+    __device__ __forceinline__ void store(T *p) const
+    {
+        if constexpr (PB == 16) *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+        else *reinterpret_cast<uint2 *>(p) = make_uint2(w[0], w[1]);
+    }
+    __device__ __forceinline__ void unpack(float (&f)[N]) const
+    {
+        const T *e = reinterpret_cast<const T *>(w);
+#pragma unroll
+        for (int i = 0; i < N; ++i) f[i] = to_float(e[i]);
+    }
+    __device__ __forceinline__ void pack(const float (&f)[N])
+    {
+        T *e = reinterpret_cast<T *>(w);
+#pragma unroll
+        for (int i = 0; i < N; ++i) e[i] = from_float<T>(f[i]);
+    }
+};
+
 // VEC consecutive parameters (weight or bias) starting at a column that is a multiple of VEC, as floats: one or two
 // 16-byte loads when the parameter tensor allows, element loads otherwise.
 template <int VEC>
 __device__ __forceinline__ void load_params(const void *p, int dtype, bool vec_ok, int col, float (&f)[VEC])
 {
-    if (vec_ok && dtype == MB200_F32) {
+    if (vec_ok && dtype == MB200_F32 && VEC % 4 == 0) {
 #pragma unroll
         for (int q = 0; q < VEC / 4; ++q) {
             const float4 v = reinterpret_cast<const float4 *>(static_cast<const float *>(p) + col)[q];
@@ -39,6 +77,14 @@ __device__ __forceinline__ void load_params(const void *p, int dtype, bool vec_o
         v.unpack(t);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) f[i] = t[i % 8];
+    } else if (vec_ok && VEC == 4 && dtype != MB200_F32) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(p) + col);
+        const uint32_t ww[2] = {v.x, v.y};
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const uint16_t h = (uint16_t)(ww[(i % 4) >> 1] >> (16 * (i & 1)));
+            f[i] = dtype == MB200_BF16 ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) f[i] = load_any(p, dtype, col + i);
@@ -57,129 +103,139 @@ template <typename T> __device__ __forceinline__ float silu_io(float z)
 // (batch, dim, seqlen)).  A thread owns VEC adjacent channels and walks a segment of the sequence with the last
 // width-1 rows of its channels in registers, so every row is read once (plus width-1 rows of halo per segment).
 constexpr int kConvSteps = 16;      // output steps per thread of the channels-contiguous kernel
-template <typename T>
+// W (width), packed sequences and the activation are compile-time so that the inner loop holds nothing but loads,
+// conversions, packed FMAs and stores; `interior` tiles (no sequence edge, no carried state) skip every bounds test.
+template <typename T, int W, bool SID, bool ACT>
 __global__ void __launch_bounds__(128, 3) conv1d_cl_kernel(const mb200_conv1d_args a)
 {
-    constexpr int VEC = 16 / sizeof(T);
-    constexpr int K = kMaxWidth, TT = kConvSteps;
+    constexpr int PB = 16, VEC = PB / sizeof(T), NP = VEC / 2;
+    constexpr int TT = kConvSteps, H = W - 1;       // H rows of history before the first output step
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * VEC;
     if (c0 >= a.dim) return;
     const int b = blockIdx.z;
     const int t0 = blockIdx.y * TT;
-    const int W = a.width, lead = K - W;        // taps are kept right-aligned: tap k of K reads step t - (K-1) + k, the first `lead` weigh 0
     const T *x = static_cast<const T *>(a.x) + (int64_t)b * a.x_stride[0] + c0;
     T *out = static_cast<T *>(a.out) + (int64_t)b * a.out_stride[0] + c0;
-    const int32_t *sid = a.seq_idx ? a.seq_idx + (int64_t)b * a.seqlen : nullptr;
-    // rows t0 - (K-1) .. t0 + TT - 1 of my channels: every load is issued before any row is used
-    Vec16<T> raw[TT + K - 1];
+    const int64_t xs = a.x_stride[2], os = a.out_stride[2];
+    const bool interior = t0 >= H && t0 + TT <= a.seqlen;
+    // rows t0 - H .. t0 + TT - 1 of my channels: every load is issued before any row is used
+    Pkt<T, PB> raw[TT + H];
+    if (interior) {
+        const T *p = x + (int64_t)(t0 - H) * xs;
 #pragma unroll
-    for (int r = 0; r < TT + K - 1; ++r) {
-        const int t = t0 - (K - 1) + r;
-        raw[r].raw = make_uint4(0u, 0u, 0u, 0u);
-        if (t >= 0 && t < a.seqlen && r >= lead) raw[r].load(x + (int64_t)t * a.x_stride[2]);
-    }
-    float w[K][VEC], bias[VEC];
-    const bool wvec = (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0;
-    if (a.bias) load_params<VEC>(a.bias, a.w_dtype, wvec, c0, bias);
-    if (!a.bias) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) bias[i] = 0.f;
-    }
-    if (W == K && (reinterpret_cast<uintptr_t>(a.weight) & 15) == 0) {
-        // the K taps of my VEC channels are VEC * K consecutive parameters: whole packets
-        float flat[K][VEC];                          // flat[q][j] = parameter q * VEC + j = tap (q * VEC + j) % K of channel (q * VEC + j) / K
-#pragma unroll
-        for (int q = 0; q < K; ++q) load_params<VEC>(a.weight, a.w_dtype, true, c0 * K + q * VEC, flat[q]);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i)
-#pragma unroll
-            for (int k = 0; k < K; ++k) w[k][i] = flat[(i * K + k) / VEC][(i * K + k) % VEC];
+        for (int r = 0; r < TT + H; ++r, p += xs) raw[r].load(p);
     } else {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i)
-#pragma unroll
-            for (int k = 0; k < K; ++k) w[k][i] = k >= lead ? load_any(a.weight, a.w_dtype, (int64_t)(c0 + i) * W + (k - lead)) : 0.f;
+        for (int r = 0; r < TT + H; ++r) {
+            const int t = t0 - H + r;
+            raw[r].zero();
+            if (t >= 0 && t < a.seqlen) raw[r].load(x + (int64_t)t * xs);
+        }
     }
-    // From here on channel pairs travel as packed fp32 pairs (one FMA-pipe issue slot for two channels).
-    constexpr int NP = VEC / 2;
-    uint64_t w2[K][NP], bias2[NP], win[K - 1][NP];   // win: the K-1 rows before the step being formed
+    // the W taps of my VEC channels are VEC * W consecutive parameters
+    uint64_t w2[W][NP], bias2[NP];
+    {
+        const bool wvec = (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.weight) & 15) == 0 && (VEC * W) % VEC == 0;
+        float flat[W][VEC], bias[VEC];
 #pragma unroll
-    for (int q = 0; q < NP; ++q) {
-        bias2[q] = pack2(bias[2 * q], bias[2 * q + 1]);
+        for (int q = 0; q < W; ++q) load_params<VEC>(a.weight, a.w_dtype, wvec, c0 * W + q * VEC, flat[q]);
+        if (a.bias) load_params<VEC>(a.bias, a.w_dtype, wvec, c0, bias);
 #pragma unroll
-        for (int k = 0; k < K; ++k) w2[k][q] = pack2(w[k][2 * q], w[k][2 * q + 1]);
+        for (int q = 0; q < NP; ++q) {
+            bias2[q] = a.bias ? pack2(bias[2 * q], bias[2 * q + 1]) : pack2(0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < W; ++k) {
+                const int i0 = (2 * q) * W + k, i1 = (2 * q + 1) * W + k;       // parameter index of (channel, tap)
+                w2[k][q] = pack2(flat[i0 / VEC][i0 % VEC], flat[i1 / VEC][i1 % VEC]);
+            }
+        }
     }
-    auto unpack_row = [&](const Vec16<T> &r, uint64_t (&o)[NP]) {
-        float f[VEC];
-        r.unpack(f);
+    auto unpack_row = [&](const Pkt<T, PB> &r, uint64_t (&o)[NP]) {
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
 #pragma unroll
-        for (int q = 0; q < NP; ++q) o[q] = pack2(f[2 * q], f[2 * q + 1]);
+            for (int q = 0; q < NP; ++q) o[q] = pack2(__uint_as_float(r.w[q] << 16), __uint_as_float(r.w[q] & 0xffff0000u));
+        } else {
+            float f[VEC];
+            r.unpack(f);
+#pragma unroll
+            for (int q = 0; q < NP; ++q) o[q] = pack2(f[2 * q], f[2 * q + 1]);
+        }
     };
+    uint64_t win[H][NP];                            // the H rows before the step being formed
 #pragma unroll
-    for (int j = 0; j < K - 1; ++j) {
-        const int t = t0 - (K - 1) + j;
-        if (t < 0 && j >= lead && a.initial_states) {       // before the sequence: the carried state
+    for (int j = 0; j < H; ++j) {
+        const int t = t0 - H + j;
+        if (!interior && t < 0 && a.initial_states) {       // before the sequence: the carried state
             const T *st = static_cast<const T *>(a.initial_states) + (int64_t)b * a.init_stride[0];
 #pragma unroll
             for (int q = 0; q < NP; ++q)
-                win[j][q] = pack2(to_float(st[(int64_t)(c0 + 2 * q) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]),
-                                  to_float(st[(int64_t)(c0 + 2 * q + 1) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]]));
+                win[j][q] = pack2(to_float(st[(int64_t)(c0 + 2 * q) * a.init_stride[1] + (int64_t)(H + t) * a.init_stride[2]]),
+                                  to_float(st[(int64_t)(c0 + 2 * q + 1) * a.init_stride[1] + (int64_t)(H + t) * a.init_stride[2]]));
         } else {
             unpack_row(raw[j], win[j]);
         }
     }
+    const int32_t *sid = SID ? a.seq_idx + (int64_t)b * a.seqlen : nullptr;
     const uint64_t half2 = pack2(0.5f, 0.5f);
+    T *po = out + (int64_t)t0 * os;
 #pragma unroll
-    for (int u = 0; u < TT; ++u) {
+    for (int u = 0; u < TT; ++u, po += os) {
         const int t = t0 + u;
         uint64_t cur[NP];
-        unpack_row(raw[K - 1 + u], cur);
-        bool keep[K - 1];                           // taps that reach into another packed sequence contribute nothing
+        unpack_row(raw[H + u], cur);
+        bool keep[H];                               // taps that reach into another packed sequence contribute nothing
 #pragma unroll
-        for (int j = 0; j < K - 1; ++j) {
-            const int tj = t - (K - 1) + j;
-            keep[j] = j >= lead && (!sid || tj < 0 || t >= a.seqlen || sid[tj] == sid[t]);
+        for (int j = 0; j < H; ++j) {
+            const int tj = t - H + j;
+            keep[j] = !SID || tj < 0 || t >= a.seqlen || sid[tj] == sid[t];
         }
-        float acc[VEC];
+        Pkt<T, PB> o;
 #pragma unroll
         for (int q = 0; q < NP; ++q) {
-            uint64_t s2 = fma2(w2[K - 1][q], cur[q], bias2[q]);
+            uint64_t s2 = fma2(w2[H][q], cur[q], bias2[q]);
 #pragma unroll
-            for (int j = 0; j < K - 1; ++j)
-                if (keep[j]) s2 = fma2(w2[j][q], win[j][q], s2);
-            if (a.activation && sizeof(T) == 2) {    // silu(s) = h + h tanh(h), h = s / 2 (16-bit results)
+            for (int j = 0; j < H; ++j)
+                if (!SID || keep[j]) s2 = fma2(w2[j][q], win[j][q], s2);
+            float s0, s1;
+            if (ACT && sizeof(T) == 2) {            // silu(s) = h + h tanh(h), h = s / 2 (16-bit results)
                 const uint64_t h2 = mul2(s2, half2);
                 float h0, h1;
                 unpack2(h2, h0, h1);
                 s2 = fma2(h2, pack2(tanh_approx(h0), tanh_approx(h1)), h2);
             }
-            unpack2(s2, acc[2 * q], acc[2 * q + 1]);
-            if (a.activation && sizeof(T) == 4) {
-                acc[2 * q] = silu_io<T>(acc[2 * q]);
-                acc[2 * q + 1] = silu_io<T>(acc[2 * q + 1]);
+            unpack2(s2, s0, s1);
+            if (ACT && sizeof(T) == 4) {
+                s0 = silu_io<T>(s0);
+                s1 = silu_io<T>(s1);
+            }
+            if constexpr (sizeof(T) == 2) {
+                T *e = reinterpret_cast<T *>(&o.w[q]);
+                e[0] = from_float<T>(s0);
+                e[1] = from_float<T>(s1);
+            } else {
+                o.w[2 * q] = __float_as_uint(s0);
+                o.w[2 * q + 1] = __float_as_uint(s1);
             }
         }
-        if (t < a.seqlen) {
-            Vec16<T> o;
-            o.pack(acc);
-            o.store(out + (int64_t)t * a.out_stride[2]);
-        }
+        if (interior || t < a.seqlen) o.store(po);
 #pragma unroll
-        for (int j = 0; j < K - 2; ++j)
+        for (int j = 0; j + 1 < H; ++j)
 #pragma unroll
             for (int q = 0; q < NP; ++q) win[j][q] = win[j + 1][q];
+        if (H > 0) {
 #pragma unroll
-        for (int q = 0; q < NP; ++q) win[K - 2][q] = cur[q];
+            for (int q = 0; q < NP; ++q) win[H - 1][q] = cur[q];
+        }
     }
     if (a.final_states && t0 + TT >= a.seqlen && t0 < a.seqlen) {      // the last width-1 inputs (reaching back into the initial state if need be)
         T *fs = static_cast<T *>(a.final_states) + (int64_t)b * a.final_stride[0];
-        for (int j = 0; j < W - 1; ++j) {
-            const int t = a.seqlen - (W - 1) + j;
+        for (int j = 0; j < H; ++j) {
+            const int t = a.seqlen - H + j;
             for (int i = 0; i < VEC; ++i) {
                 T v = from_float<T>(0.f);
-                if (t >= 0) v = x[(int64_t)t * a.x_stride[2] + i];
+                if (t >= 0) v = x[(int64_t)t * xs + i];
                 else if (a.initial_states)
-                    v = static_cast<const T *>(a.initial_states)[(int64_t)b * a.init_stride[0] + (int64_t)(c0 + i) * a.init_stride[1] + (int64_t)(W - 1 + t) * a.init_stride[2]];
+                    v = static_cast<const T *>(a.initial_states)[(int64_t)b * a.init_stride[0] + (int64_t)(c0 + i) * a.init_stride[1] + (int64_t)(H + t) * a.init_stride[2]];
                 fs[(int64_t)(c0 + i) * a.final_stride[1] + (int64_t)j * a.final_stride[2]] = v;
             }
         }
@@ -380,8 +436,20 @@ int launch_conv1d(const mb200_conv1d_args &a, cudaStream_t stream)
                                a.x_stride[0] % VEC == 0 && a.x_stride[2] % VEC == 0 && a.out_stride[0] % VEC == 0 && a.out_stride[2] % VEC == 0 &&
                                (a.seqlen + kConvSteps - 1) / kConvSteps <= 65535;
     if (channels_last) {
-        const int cols = (a.dim / VEC + 127) / 128;
-        conv1d_cl_kernel<T><<<dim3(cols, (a.seqlen + kConvSteps - 1) / kConvSteps, a.batch), 128, 0, stream>>>(a);
+        const dim3 grid((a.dim / VEC + 127) / 128, (a.seqlen + kConvSteps - 1) / kConvSteps, a.batch);
+        auto go = [&](auto w_tag) {
+            constexpr int W = decltype(w_tag)::value;
+            if (a.seq_idx) {
+                if (a.activation) conv1d_cl_kernel<T, W, true, true><<<grid, 128, 0, stream>>>(a);
+                else conv1d_cl_kernel<T, W, true, false><<<grid, 128, 0, stream>>>(a);
+            } else {
+                if (a.activation) conv1d_cl_kernel<T, W, false, true><<<grid, 128, 0, stream>>>(a);
+                else conv1d_cl_kernel<T, W, false, false><<<grid, 128, 0, stream>>>(a);
+            }
+        };
+        if (a.width == 4) go(std::integral_constant<int, 4>{});
+        else if (a.width == 3) go(std::integral_constant<int, 3>{});
+        else go(std::integral_constant<int, 2>{});
     } else {
         const int64_t work = (int64_t)a.dim * ((a.seqlen + kRun - 1) / kRun);
         conv1d_any_kernel<T><<<dim3((unsigned)((work + 255) / 256), a.batch), 256, 0, stream>>>(a);
