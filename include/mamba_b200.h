@@ -84,6 +84,51 @@ int mb200_selective_scan_fwd(const mb200_scan_args *args, void *stream);
  * one-pass scan to fp32 rounding. */
 int mb200_scan_scratch_bytes(const mb200_scan_args *args, size_t *bytes);
 
+/* ---------------------------------------------------------------------------------------------
+ * Mamba-1 selective scan, backward.
+ * Replaces selective_scan_cuda.bwd (csrc/selective_scan/selective_scan.cpp:338-492, kernel
+ * selective_scan_bwd_kernel.cuh), called at mamba_ssm/ops/selective_scan_interface.py:83-86.
+ *
+ * Inputs as in mb200_scan_args plus dout (batch, dim, seqlen) io_dtype = dL/d(out), where out is the gated
+ * output when z is given.  The scan is recomputed from the inputs: neither the forward's prefix tensor `x` nor its
+ * pre-gate output is read (the reference needs both, selective_scan_bwd_kernel.cuh:140-142,180-188).
+ *
+ * Outputs.  du, ddelta (and dz with z): (batch, dim, seqlen) io_dtype, last stride 1.  dA: (dim, dstate) fp32
+ * contiguous.  dB, dC: fp32 contiguous in the shape of B, C -- (batch, ngroups, dstate, seqlen) when
+ * input-dependent (the reference accumulates them in fp32 too, selective_scan.cpp:461-462, and casts afterwards),
+ * (dim, dstate) otherwise.  dD, ddelta_bias: (dim) fp32, optional (NULL when D / delta_bias is NULL).
+ * The library zeroes dA, dB, dC, dD, ddelta_bias on the stream before it accumulates into them.
+ * The gradient with respect to last_state is not taken, as in the reference (selective_scan_interface.py:121-122).
+ *
+ * scratch: required, 16-byte aligned, mb200_scan_bwd_scratch_bytes() bytes: the states at every eighth step
+ * (written by a first forward launch, read by the backward launch that walks the sequence from the end) and, above
+ * 16 states, fp32 partial sums of du, ddelta, dz between the passes over 16 states each.
+ */
+typedef struct mb200_scan_bwd_args {
+    const void *u, *delta;
+    const float *A;
+    const void *B, *C;
+    const float *D;
+    const void *z;
+    const float *delta_bias;
+    const void *dout;
+    void *du, *ddelta, *dz;
+    float *dA, *dB, *dC, *dD, *ddelta_bias;
+    int32_t batch, dim, seqlen, dstate, ngroups;
+    int32_t io_dtype;                 /* mb200_dtype of u, delta, z, dout, du, ddelta, dz and of variable B, C */
+    int32_t B_variable, C_variable, delta_softplus;
+    int32_t device;
+    int64_t u_stride[2], delta_stride[2], z_stride[2], dout_stride[2];    /* {batch, dim} */
+    int64_t du_stride[2], ddelta_stride[2], dz_stride[2];
+    int64_t A_stride[2];              /* {dim, dstate} */
+    int64_t B_stride[3], C_stride[3]; /* as in mb200_scan_args */
+    void *scratch;
+    size_t scratch_bytes;
+} mb200_scan_bwd_args;
+
+int mb200_scan_bwd_scratch_bytes(const mb200_scan_bwd_args *args, size_t *bytes);
+int mb200_selective_scan_bwd(const mb200_scan_bwd_args *args, void *stream);
+
 /* Diagnostic, no counterpart in the reference.  The TMA-fed scan kernel bounds every wait on a copy or on
  * another warp; when a wait runs out it stops and records a non-zero code in a per-device word instead of
  * hanging.  This call copies that word to *status (0 = no wait has ever run out on `device`).  It

@@ -35,6 +35,21 @@ class ScanArgs(ctypes.Structure):
     ]
 
 
+class ScanBwdArgs(ctypes.Structure):
+    _fields_ = [
+        ("u", c_vp), ("delta", c_vp), ("A", c_vp), ("B", c_vp), ("C", c_vp), ("D", c_vp), ("z", c_vp),
+        ("delta_bias", c_vp), ("dout", c_vp), ("du", c_vp), ("ddelta", c_vp), ("dz", c_vp),
+        ("dA", c_vp), ("dB", c_vp), ("dC", c_vp), ("dD", c_vp), ("ddelta_bias", c_vp),
+        ("batch", c_i32), ("dim", c_i32), ("seqlen", c_i32), ("dstate", c_i32), ("ngroups", c_i32),
+        ("io_dtype", c_i32), ("B_variable", c_i32), ("C_variable", c_i32), ("delta_softplus", c_i32),
+        ("device", c_i32),
+        ("u_stride", c_i64 * 2), ("delta_stride", c_i64 * 2), ("z_stride", c_i64 * 2), ("dout_stride", c_i64 * 2),
+        ("du_stride", c_i64 * 2), ("ddelta_stride", c_i64 * 2), ("dz_stride", c_i64 * 2),
+        ("A_stride", c_i64 * 2), ("B_stride", c_i64 * 3), ("C_stride", c_i64 * 3),
+        ("scratch", c_vp), ("scratch_bytes", ctypes.c_size_t),
+    ]
+
+
 class SsuArgs(ctypes.Structure):
     _fields_ = [
         ("state", c_vp), ("x", c_vp), ("dt", c_vp), ("A", c_vp), ("B", c_vp), ("C", c_vp), ("D", c_vp),
@@ -99,6 +114,8 @@ _PROTOTYPES = {
     "mb200_selective_scan_fwd": (ctypes.c_int, [ctypes.POINTER(ScanArgs), c_vp]),
     "mb200_scan_scratch_bytes": (ctypes.c_int, [ctypes.POINTER(ScanArgs), ctypes.POINTER(ctypes.c_size_t)]),
     "mb200_scan_status": (ctypes.c_int, [c_i32, ctypes.POINTER(c_i32)]),
+    "mb200_scan_bwd_scratch_bytes": (ctypes.c_int, [ctypes.POINTER(ScanBwdArgs), ctypes.POINTER(ctypes.c_size_t)]),
+    "mb200_selective_scan_bwd": (ctypes.c_int, [ctypes.POINTER(ScanBwdArgs), c_vp]),
     "mb200_selective_state_update": (ctypes.c_int, [ctypes.POINTER(SsuArgs), c_vp]),
     "mb200_ssd_scratch_bytes": (ctypes.c_int, [ctypes.POINTER(SsdArgs), ctypes.POINTER(ctypes.c_size_t)]),
     "mb200_ssd_chunk_scan_fwd": (ctypes.c_int, [ctypes.POINTER(SsdArgs), c_vp]),

@@ -10,7 +10,7 @@ reference's own Python run unmodified on top of libmamba_b200 for inference:
     import sys, mamba_b200.compat
     sys.modules["selective_scan_cuda"] = mamba_b200.compat.selective_scan_cuda
 
-``bwd`` is not provided (forward / inference only).
+``bwd`` serves the reference's ``SelectiveScanFn.backward`` (:70-100) from the library's backward kernel.
 """
 import ctypes
 
@@ -74,8 +74,23 @@ class _SelectiveScanCuda:
         return [out, x] if z_ is None else [out, x, out_z]
 
     @staticmethod
-    def bwd(*args, **kwargs):
-        raise NotImplementedError("mamba_b200 serves the forward (inference) path only")
+    def bwd(u, delta, A, B, C, D_, z_, delta_bias_, dout, x_, out_, dz_, delta_softplus, recompute_out_z):
+        """``selective_scan_cuda.bwd`` (csrc/selective_scan/selective_scan.cpp:338-492): returns
+        ``[du, ddelta, dA, dB, dC, dD, ddelta_bias]`` followed by ``dz`` when z is given and ``out_z`` when asked for.
+        ``x_`` and ``out_`` are accepted and ignored: the library's backward recomputes the scan from the inputs."""
+        from . import ops
+        assert (B.dim() != 3) and (C.dim() != 3), "variable B/C must be (batch, groups, dstate, seqlen)"
+        du, ddelta, dA, dB, dC, dD, dz, dbias = ops.selective_scan_bwd(u, delta, A, B, C, D_, z_, delta_bias_, dout,
+                                                                       delta_softplus)
+        result = [du, ddelta, dA, dB, dC, dD, dbias]
+        if z_ is not None:
+            if dz_ is not None:        # a preallocated dz is filled in place, as the extension does
+                dz_.copy_(dz)
+                dz = dz_
+            result.append(dz)
+            if recompute_out_z:
+                result.append(ops._selective_scan(u, delta, A, B, C, D_, z_, delta_bias_, delta_softplus))
+        return result
 
 
 selective_scan_cuda = _SelectiveScanCuda()

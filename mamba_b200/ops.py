@@ -6,8 +6,9 @@ Signatures, argument meaning, return values and error behaviour mirror the refer
 * ``mamba_chunk_scan_combined``  mamba_ssm/ops/triton/ssd_combined.py:628-648 (forward :343-394)
 * ``selective_state_update``     mamba_ssm/ops/triton/selective_state_update.py:135-221
 
-Forward only (inference): the outputs carry no autograd graph.  PyTorch supplies device memory
-and the current stream; all arithmetic happens in the library's CUDA kernels.
+The SSD and decode operators are forward only (their outputs carry no autograd graph); the Mamba-1 scan also has
+its backward (``selective_scan_bwd``).  PyTorch supplies device memory and the current stream; all arithmetic
+happens in the library's CUDA kernels.
 """
 import ctypes
 import math
@@ -29,20 +30,26 @@ def _fp32(t):
 # --------------------------------------------------------------------------------------- Mamba-1
 def selective_scan_fn(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus=False,
                       return_last_state=False):
-    """Mamba-1 selective scan forward.
+    """Mamba-1 selective scan.
 
     u, delta, z: (batch, dim, seqlen).  A: (dim, dstate) fp32.  B, C: (batch, dstate, seqlen),
     (batch, ngroups, dstate, seqlen) or constant (dim, dstate).  D, delta_bias: (dim) fp32.
     Returns ``out`` (gated by silu(z) when z is given) or ``(out, last_state)`` with
     ``last_state`` (batch, dim, dstate) fp32.
+
+    When gradients are enabled and an input requires them, the result carries an autograd node whose backward is
+    the library's backward kernel (the role of SelectiveScanFn.backward, selective_scan_interface.py:70-100); as in
+    the reference, no gradient flows through ``last_state``.
     """
+    tensors = (u, delta, A, B, C, D, z, delta_bias)
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        return _SelectiveScanFn.apply(u, delta, A, B, C, D, z, delta_bias, delta_softplus, return_last_state)
     return _selective_scan(u, delta, A, B, C, D, z, delta_bias, delta_softplus, return_last_state)
 
 
-def _selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus=False, return_last_state=False,
-                    out=None):
-    """selective_scan_fn with an optional caller-provided ``out`` (batch, dim, seqlen; last stride 1)."""
-    L.require_cuda(u, delta, A, B, C, D, z, delta_bias, out)
+def _scan_inputs(u, delta, A, B, C, D, z, delta_bias):
+    """The contiguity fix-ups and shape checks of SelectiveScanFn.forward (selective_scan_interface.py:40-57) and of the
+    extension (selective_scan.cpp:233-305).  Returns the tensors the library reads plus (B_var, C_var, ngroups)."""
     if A.is_complex():
         raise NotImplementedError("mamba_b200: complex A is not supported")
     u, delta, z = _last_dim_contiguous(u), _last_dim_contiguous(delta), _last_dim_contiguous(z)
@@ -77,7 +84,16 @@ def _selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_so
         assert D.shape == (dim,)
     if delta_bias is not None:
         assert delta_bias.shape == (dim,)
+    return (u, delta, A, B, C, D, z, delta_bias), (B_var, C_var, ngroups)
 
+
+def _selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus=False, return_last_state=False,
+                    out=None):
+    """selective_scan_fn with an optional caller-provided ``out`` (batch, dim, seqlen; last stride 1)."""
+    L.require_cuda(u, delta, A, B, C, D, z, delta_bias, out)
+    (u, delta, A, B, C, D, z, delta_bias), (B_var, C_var, ngroups) = _scan_inputs(u, delta, A, B, C, D, z, delta_bias)
+    batch, dim, seqlen = u.shape
+    dstate = A.shape[1]
     if out is None:
         out = torch.empty_like(delta)
     assert out.shape == u.shape and out.dtype == u.dtype and out.stride(-1) == 1, "out must match u, last stride 1"
@@ -106,6 +122,84 @@ def _selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_so
     a.scratch, a.scratch_bytes = L.ptr(scratch), need.value
     L.check(L.lib().mb200_selective_scan_fwd(ctypes.byref(a), L.stream_ptr(u.device)))
     return out if not return_last_state else (out, last_state)
+
+
+def selective_scan_bwd(u, delta, A, B, C, D, z, delta_bias, dout, delta_softplus=False):
+    """Gradients of selective_scan_fn for ``dout`` = dL/d(out): the call ``selective_scan_cuda.bwd`` serves in the
+    reference (selective_scan_interface.py:83-86, selective_scan.cpp:338-492).  The scan is recomputed from the inputs,
+    so nothing of the forward is needed.  Returns ``(du, ddelta, dA, dB, dC, dD, dz, ddelta_bias)``: du, ddelta, dz in
+    the dtype of u, dA, dD, ddelta_bias fp32, dB and dC in the dtype and shape of B and C (accumulated in fp32);
+    None where the input is None."""
+    L.require_cuda(u, delta, A, B, C, D, z, delta_bias, dout)
+    squeeze_B, squeeze_C = B.dim() == 3, C.dim() == 3
+    B_dtype, C_dtype = B.dtype, C.dtype
+    (u, delta, A, B, C, D, z, delta_bias), (B_var, C_var, ngroups) = _scan_inputs(u, delta, A, B, C, D, z, delta_bias)
+    batch, dim, seqlen = u.shape
+    dstate = A.shape[1]
+    dout = _last_dim_contiguous(dout)
+    assert dout.shape == u.shape and dout.dtype == u.dtype, "dout must match u"
+    dev = u.device
+    du, ddelta = torch.empty_like(u), torch.empty_like(delta)
+    dz = torch.empty_like(z) if z is not None else None
+    f32 = dict(device=dev, dtype=torch.float32)
+    dA = torch.empty(dim, dstate, **f32)
+    dB = torch.empty(B.shape, **f32)
+    dC = torch.empty(C.shape, **f32)
+    dD = torch.empty(dim, **f32) if D is not None else None
+    dbias = torch.empty(dim, **f32) if delta_bias is not None else None
+
+    a = L.ScanBwdArgs()
+    a.u, a.delta, a.A, a.B, a.C = L.ptr(u), L.ptr(delta), L.ptr(A), L.ptr(B), L.ptr(C)
+    a.D, a.z, a.delta_bias, a.dout = L.ptr(D), L.ptr(z), L.ptr(delta_bias), L.ptr(dout)
+    a.du, a.ddelta, a.dz = L.ptr(du), L.ptr(ddelta), L.ptr(dz)
+    a.dA, a.dB, a.dC, a.dD, a.ddelta_bias = L.ptr(dA), L.ptr(dB), L.ptr(dC), L.ptr(dD), L.ptr(dbias)
+    a.batch, a.dim, a.seqlen, a.dstate, a.ngroups = batch, dim, seqlen, dstate, ngroups
+    a.io_dtype = L.dtype_code(u.dtype)
+    a.B_variable, a.C_variable, a.delta_softplus = int(B_var), int(C_var), int(bool(delta_softplus))
+    a.device = dev.index
+    for field, t in ((a.u_stride, u), (a.delta_stride, delta), (a.dout_stride, dout), (a.du_stride, du),
+                     (a.ddelta_stride, ddelta)):
+        L.set_strides(field, t, 2)
+    if z is not None:
+        L.set_strides(a.z_stride, z, 2)
+        L.set_strides(a.dz_stride, dz, 2)
+    L.set_strides(a.A_stride, A, 2)
+    L.set_strides(a.B_stride, B, 3 if B_var else 2)
+    L.set_strides(a.C_stride, C, 3 if C_var else 2)
+    need = ctypes.c_size_t(0)
+    L.check(L.lib().mb200_scan_bwd_scratch_bytes(ctypes.byref(a), ctypes.byref(need)))
+    scratch = torch.empty(need.value, dtype=torch.uint8, device=dev)
+    a.scratch, a.scratch_bytes = L.ptr(scratch), need.value
+    L.check(L.lib().mb200_selective_scan_bwd(ctypes.byref(a), L.stream_ptr(dev)))
+    dB, dC = dB.to(B_dtype), dC.to(C_dtype)       # selective_scan.cpp:487
+    if squeeze_B:
+        dB = dB.squeeze(1)
+    if squeeze_C:
+        dC = dC.squeeze(1)
+    return du, ddelta, dA, dB, dC, dD, dz, dbias
+
+
+class _SelectiveScanFn(torch.autograd.Function):
+    """Autograd node of selective_scan_fn.  Unlike SelectiveScanFn (selective_scan_interface.py:34-100) it saves only the
+    inputs: the backward kernel recomputes the scan, so neither the prefix tensor nor the pre-gate output is kept."""
+
+    @staticmethod
+    def forward(ctx, u, delta, A, B, C, D, z, delta_bias, delta_softplus, return_last_state):
+        res = _selective_scan(u, delta, A, B, C, D, z, delta_bias, delta_softplus, return_last_state)
+        ctx.delta_softplus = delta_softplus
+        ctx.save_for_backward(u, delta, A, B, C, D, z, delta_bias)
+        if return_last_state:
+            ctx.mark_non_differentiable(res[1])
+        return res
+
+    @staticmethod
+    def backward(ctx, dout, *unused):
+        u, delta, A, B, C, D, z, delta_bias = ctx.saved_tensors
+        du, ddelta, dA, dB, dC, dD, dz, dbias = selective_scan_bwd(u, delta, A, B, C, D, z, delta_bias, dout,
+                                                                   ctx.delta_softplus)
+        as_of = lambda g, t: None if g is None else g.to(t.dtype).reshape(t.shape)
+        return (du, ddelta, as_of(dA, A), dB, dC, as_of(dD, D) if D is not None else None, dz,
+                as_of(dbias, delta_bias) if delta_bias is not None else None, None, None)
 
 
 # --------------------------------------------------------------------------------------- decode

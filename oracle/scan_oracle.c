@@ -6,6 +6,8 @@
  *
  * Each function restates one of the reference's pure-PyTorch definitions:
  *   oracle_selective_scan     <- mamba_ssm/ops/selective_scan_interface.py:127-193
+ *   oracle_selective_scan_bwd <- the gradient autograd derives from the same lines (checked against the CUDA
+ *                                backward at tests/ops/test_selective_scan.py:119-147)
  *   oracle_state_update       <- mamba_ssm/ops/triton/selective_state_update.py:224-285
  *   oracle_causal_conv1d      <- the depthwise nn.Conv1d with left padding that the mixers fall back to,
  *                                mamba_ssm/modules/mamba2.py:232-234 (mamba_simple.py:166-171), with the packed-
@@ -97,6 +99,134 @@ void oracle_selective_scan(const float *u, const float *delta, const float *A,
                     last_state[((size_t)b * dim + d) * N + n] = (float)h[n];
         }
     }
+}
+
+/*
+ * Gradient of the Mamba-1 selective scan with respect to every differentiable input, given dout = dL/d(out).
+ * The reference defines it only through autograd on selective_scan_ref (the check that
+ * tests/ops/test_selective_scan.py:119-147 makes against the CUDA backward); this is the adjoint of the
+ * recurrence above, written out:
+ *   dy_t = dout_t silu(z_t)            dz_t = dout_t y_t silu'(z_t)            (dy_t = dout_t without z)
+ *   g_t  = C_t dy_t + a_{t+1} g_{t+1}                                          (a_t = exp(dt_t A), g_L = 0)
+ *   du_t = D dy_t + dt_t sum_n g_t B_t          dD = sum u_t dy_t
+ *   d(dt_t) = sum_n g_t (A a_t h_{t-1} + B_t u_t)        dA = sum_t g_t dt_t a_t h_{t-1}
+ *   dB_t = sum_d g_t dt_t u_t   dC_t = sum_d dy_t h_t    (sums over the channels of the group; over batch and
+ *                                                          time for constant B, C)
+ *   d(delta_t) = d(dt_t) softplus'(delta_t + bias)        d(delta_bias) = sum_{b,t} d(delta_t)
+ * Shapes as in oracle_selective_scan; dB, dC have the shape of B, C.  dD, ddelta_bias, dz may be NULL.
+ */
+void oracle_selective_scan_bwd(const float *u, const float *delta, const float *A,
+                               const float *B, const float *C, const float *D,
+                               const float *z, const float *delta_bias, const float *dout,
+                               int delta_softplus, int batch, int dim, int L, int N,
+                               int ngroups, int B_variable, int C_variable,
+                               float *du, float *ddelta, float *dA, float *dB, float *dC,
+                               float *dD, float *ddelta_bias, float *dz)
+{
+    const int G = ngroups > 0 ? ngroups : 1;
+    const int per_group = dim / G;
+    double *accA = (double *)calloc((size_t)dim * N, sizeof(double));
+    double *accBc = (double *)calloc((size_t)dim * N, sizeof(double));      /* constant B, C */
+    double *accCc = (double *)calloc((size_t)dim * N, sizeof(double));
+    double *accD = (double *)calloc((size_t)dim, sizeof(double));
+    double *accb = (double *)calloc((size_t)dim, sizeof(double));
+    /* one (batch row, group) per iteration: its channels are walked one after the other, so the sums over the
+     * channels of a group stay inside one thread; the per-channel parameter gradients, which sum over batch rows,
+     * are accumulated with atomic updates */
+#pragma omp parallel for collapse(2) schedule(dynamic)
+    for (int b = 0; b < batch; ++b) {
+        for (int g = 0; g < G; ++g) {
+            double *hist = (double *)malloc(sizeof(double) * (size_t)(L + 1) * N);     /* h_0 .. h_L */
+            double *dts = (double *)malloc(sizeof(double) * (size_t)L);
+            double *sBv = B_variable ? (double *)calloc((size_t)N * L, sizeof(double)) : NULL;
+            double *sCv = C_variable ? (double *)calloc((size_t)N * L, sizeof(double)) : NULL;
+            double gv[256];
+            const float *Bg = B_variable ? B + ((size_t)b * G + g) * (size_t)N * L : NULL;
+            const float *Cg = C_variable ? C + ((size_t)b * G + g) * (size_t)N * L : NULL;
+            for (int d = g * per_group; d < (g + 1) * per_group; ++d) {
+                const size_t row = ((size_t)b * dim + d) * (size_t)L;
+                const float *Ad = A + (size_t)d * N;
+                for (int n = 0; n < N; ++n) hist[n] = 0.0;
+                for (int t = 0; t < L; ++t) {
+                    double dt = delta[row + t];
+                    if (delta_bias) dt += delta_bias[d];
+                    if (delta_softplus) dt = softplus20(dt);
+                    dts[t] = dt;
+                    for (int n = 0; n < N; ++n) {
+                        const double bn = B_variable ? Bg[(size_t)n * L + t] : B[(size_t)d * N + n];
+                        hist[(size_t)(t + 1) * N + n] = exp(dt * (double)Ad[n]) * hist[(size_t)t * N + n] + dt * bn * (double)u[row + t];
+                    }
+                }
+                for (int n = 0; n < N; ++n) gv[n] = 0.0;       /* a_{t+1} g_{t+1}, carried backwards */
+                double sumD = 0.0, sumb = 0.0;
+                for (int t = L - 1; t >= 0; --t) {
+                    const double dt = dts[t], uu = u[row + t];
+                    double dy = dout[row + t];
+                    if (z) {
+                        const double zz = z[row + t], sg = 1.0 / (1.0 + exp(-zz));
+                        double y = D ? uu * (double)D[d] : 0.0;
+                        for (int n = 0; n < N; ++n) {
+                            const double cn = C_variable ? Cg[(size_t)n * L + t] : C[(size_t)d * N + n];
+                            y += hist[(size_t)(t + 1) * N + n] * cn;
+                        }
+                        if (dz) dz[row + t] = (float)(dy * y * sg * (1.0 + zz * (1.0 - sg)));
+                        dy *= zz * sg;
+                    }
+                    double s_gb = 0.0, ddt = 0.0;
+                    for (int n = 0; n < N; ++n) {
+                        const double bn = B_variable ? Bg[(size_t)n * L + t] : B[(size_t)d * N + n];
+                        const double cn = C_variable ? Cg[(size_t)n * L + t] : C[(size_t)d * N + n];
+                        const double a = exp(dt * (double)Ad[n]);
+                        const double hprev = hist[(size_t)t * N + n], hcur = hist[(size_t)(t + 1) * N + n];
+                        const double gt = cn * dy + gv[n];
+                        s_gb += gt * bn;
+                        ddt += gt * ((double)Ad[n] * a * hprev + bn * uu);
+#pragma omp atomic
+                        accA[(size_t)d * N + n] += gt * dt * a * hprev;
+                        if (B_variable) sBv[(size_t)n * L + t] += gt * dt * uu;
+                        else {
+#pragma omp atomic
+                            accBc[(size_t)d * N + n] += gt * dt * uu;
+                        }
+                        if (C_variable) sCv[(size_t)n * L + t] += dy * hcur;
+                        else {
+#pragma omp atomic
+                            accCc[(size_t)d * N + n] += dy * hcur;
+                        }
+                        gv[n] = a * gt;
+                    }
+                    du[row + t] = (float)((D ? (double)D[d] * dy : 0.0) + dt * s_gb);
+                    sumD += uu * dy;
+                    double dd = ddt;
+                    if (delta_softplus) {
+                        const double x = (double)delta[row + t] + (delta_bias ? (double)delta_bias[d] : 0.0);
+                        if (x <= 20.0) dd *= 1.0 / (1.0 + exp(-x));
+                    }
+                    ddelta[row + t] = (float)dd;
+                    sumb += dd;
+                }
+#pragma omp atomic
+                accD[d] += sumD;
+#pragma omp atomic
+                accb[d] += sumb;
+            }
+            if (B_variable)
+                for (size_t i = 0; i < (size_t)N * L; ++i) dB[((size_t)b * G + g) * (size_t)N * L + i] = (float)sBv[i];
+            if (C_variable)
+                for (size_t i = 0; i < (size_t)N * L; ++i) dC[((size_t)b * G + g) * (size_t)N * L + i] = (float)sCv[i];
+            free(hist); free(dts); free(sBv); free(sCv);
+        }
+    }
+    for (size_t i = 0; i < (size_t)dim * N; ++i) {
+        dA[i] = (float)accA[i];
+        if (!B_variable) dB[i] = (float)accBc[i];
+        if (!C_variable) dC[i] = (float)accCc[i];
+    }
+    for (int d = 0; d < dim; ++d) {
+        if (dD) dD[d] = (float)accD[d];
+        if (ddelta_bias) ddelta_bias[d] = (float)accb[d];
+    }
+    free(accA); free(accBc); free(accCc); free(accD); free(accb);
 }
 
 /*

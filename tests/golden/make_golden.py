@@ -83,6 +83,31 @@ def mamba1(name, seed, batch, dim, L, N, groups, dtype=torch.float32, has_z=True
          is_bf16=np.int32(dtype == torch.bfloat16))
 
 
+def mamba1_bwd(name, seed, batch, dim, L, N, groups, dtype=torch.float32, has_z=True, has_D=True, has_bias=True,
+               const_b=False, const_c=False, softplus=True):
+    """Gradients of selective_scan_ref by autograd for a seeded dout: the comparison the reference makes for its CUDA
+    backward (tests/ops/test_selective_scan.py:56-147, whose input distributions these are)."""
+    g = gen(seed)
+    r = lambda *s: torch.randn(*s, generator=g)
+    A = -0.5 * torch.rand(dim, N, generator=g)
+    delta = 0.5 * torch.rand(batch, dim, L, generator=g)
+    bias = 0.5 * torch.rand(dim, generator=g) if has_bias else None
+    u = r(batch, dim, L)
+    B = r(dim, N) if const_b else r(batch, groups, N, L).to(dtype)
+    C = r(dim, N) if const_c else r(batch, groups, N, L).to(dtype)
+    D = r(dim) if has_D else None
+    z = r(batch, dim, L).to(dtype) if has_z else None
+    u, delta = u.to(dtype), delta.to(dtype)
+    dout = r(batch, dim, L).to(dtype)
+    leaves = [None if t is None else t.detach().clone().requires_grad_() for t in (u, delta, A, B, C, D, z, bias)]
+    out = selective_scan_ref(*leaves[:5], leaves[5], leaves[6], leaves[7], delta_softplus=softplus)
+    out.backward(dout.to(out.dtype))
+    gr = [None if t is None else t.grad for t in leaves]
+    save(name, u=u, delta=delta, A=A, B=B, C=C, D=D, z=z, delta_bias=bias, dout=dout, du=gr[0], ddelta=gr[1], dA=gr[2],
+         dB=gr[3], dC=gr[4], dD=gr[5], dz=gr[6], ddelta_bias=gr[7], is_bf16=np.int32(dtype == torch.bfloat16),
+         delta_softplus=np.int32(softplus))
+
+
 # ----------------------------------------------------------------------------- decode update
 def decode(name, seed, batch, nheads, dim, N, groups, dtype=torch.float32, tie=False, heads=True,
            has_z=True, steps=1):
@@ -240,6 +265,13 @@ def main():
     ssd("ssd_fp32_init", 33, 2, 128, 2, 16, 1, 16, 32, with_init=True)
     ssd("ssd_fp32_tail", 34, 1, 200, 2, 8, 2, 16, 64)
     ssd("ssd_bf16", 35, 1, 512, 2, 64, 1, 128, 256, dtype=torch.bfloat16)
+    mamba1_bwd("m1b_fp32_g1", 61, 2, 4, 128, 8, 1)
+    mamba1_bwd("m1b_fp32_g2_odd", 62, 2, 4, 372, 8, 2, has_z=False, has_bias=False, softplus=False)
+    mamba1_bwd("m1b_fp32_constbc", 63, 2, 6, 100, 4, 1, const_b=True, const_c=True, has_D=False)
+    mamba1_bwd("m1b_fp32_constb", 64, 1, 40, 77, 16, 1, const_b=True)
+    mamba1_bwd("m1b_fp32_wide", 65, 2, 64, 200, 16, 2)
+    mamba1_bwd("m1b_fp32_n40", 66, 1, 8, 60, 40, 1)
+    mamba1_bwd("m1b_bf16", 67, 2, 64, 256, 16, 1, dtype=torch.bfloat16)
 
 
 if __name__ == "__main__":
