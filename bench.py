@@ -47,6 +47,7 @@ NCU_TRAFFIC = {
 WORKLOAD_DESC = {
     "c0": "mamba1_selective_scan_fwd fp32 b2 d256 L512 N16",
     "c1": "mamba1_selective_scan_fwd bf16 b8 d5120 L2048 N16 (2.8B layer)",
+    "c1b": "mamba1_selective_scan_bwd bf16 b8 d5120 L2048 N16 (gradients of c1 for a seeded dout; --only c1b, not part of the default line)",
     "c2": "mamba2_ssd_chunk_scan_fwd bf16 b8 L4096 h80 P64 g1 N128 Q256 (+z, +final_states)",
     "c3": "mamba2_ssd_chunk_scan_fwd bf16 b1 L262144 h128 P64 g8 N128 Q256 (no z, +final_states)",
     "c4": "mamba2_selective_state_update b256 h80 P64 g1 N128, fp32 state, bf16 activations, consecutive steps",
@@ -54,6 +55,7 @@ WORKLOAD_DESC = {
 PARTITION = {
     "c0": "replicas only (correctness configuration)",
     "c1": "batch rows divided over the GPUs, no collective",
+    "c1b": "batch rows divided over the GPUs; parameter gradients (dA, dD, ddelta_bias) would be summed by the caller",
     "c2": "heads divided over the GPUs (B and C replicated), no collective",
     "c3": "contiguous chunk ranges of the sequence per GPU; range states exchanged by NCCL (all-gather + local fold)",
     "c4": "batch rows divided over the GPUs, each owning its slice of the state; no collective",
@@ -122,8 +124,8 @@ class Workload:
         self.step_no = 0
         self.flops = None
         bf = torch.bfloat16
-        if name in ("c1", "c0"):
-            if name == "c1":
+        if name in ("c1", "c0", "c1b"):
+            if name != "c0":
                 nb = batch or 8
                 lo, hi = split_even(nb, world, rank)
                 host = make_c1_rows(range(lo, hi))
@@ -134,12 +136,19 @@ class Workload:
             b, d, L = host["u"].shape
             esz = host["u"].element_size()
             self.shape = dict(batch=b, d_inner=d, seqlen=L, d_state=16)
-            self.dtype = "bf16" if name == "c1" else "f32"
+            self.dtype = "f32" if name == "c0" else "bf16"
             self.alg_bytes = 4 * b * d * L * esz + 2 * b * 16 * L * esz + d * 16 * 4 + 2 * d * 4 + b * d * 16 * 4
             self.launches_per_step = 1 if b > 0 else 0
             self.kernels = "scan_stream_kernel"
             self.host = host
             self.d = {k: v.to(dev) for k, v in host.items()}
+            if name == "c1b":
+                # reads u, delta, z, dout, B, C; writes du, ddelta, dz, fp32 dB and dC, and the parameter gradients
+                g = torch.Generator().manual_seed(1001 + 7919 * rank)
+                self.d["dout"] = torch.randn(b, d, L, generator=g).to(bf).to(dev)
+                self.alg_bytes = 7 * b * d * L * esz + 2 * b * 16 * L * (esz + 4) + 2 * d * 16 * 4 + 4 * d * 4
+                self.launches_per_step = 2 if b > 0 else 0
+                self.kernels = "scan_bwd_states_kernel, scan_bwd_kernel (+ 5 memsets of the accumulators)"
         elif name == "c2":
             nb, L, Hall, P, N = batch or 8, 4096, 80, 64, 128
             lo, hi = split_even(Hall, world, rank)
@@ -203,6 +212,8 @@ class Workload:
     # -- one pass with this rank's inputs already in HBM ---------------------------------------
     def step(self, src=None):
         d, mb = (self.d if src is None else src), self.mb
+        if self.name == "c1b":
+            return mb.selective_scan_bwd(d["u"], d["delta"], d["A"], d["B"], d["C"], d["D"], d["z"], d["delta_bias"], d["dout"], True)[0]
         if self.name in ("c1", "c0"):
             return mb.selective_scan_fn(d["u"], d["delta"], self.d["A"], d["B"], d["C"], self.d["D"], d["z"],
                                         self.d["delta_bias"], delta_softplus=True, return_last_state=True)[0]
@@ -268,6 +279,13 @@ class Workload:
 def cpu_inputs(name):
     """Host tensors of the bounded sample of `name` the CPU baseline runs, and what that sample is."""
     bf = torch.bfloat16
+    if name == "c1b":
+        h = make_c1_rows([0])
+        keep = 64    # autograd through the reference keeps every step's (channels x states) tensors alive
+        h = {k: (v[:, :keep].contiguous() if k in ("u", "delta", "z") else v[:keep].contiguous() if k in ("A", "D", "delta_bias") else v)
+             for k, v in h.items()}
+        h["dout"] = torch.randn(h["u"].shape, generator=torch.Generator().manual_seed(7)).to(bf)
+        return h, h["u"].shape[2] * keep / 5120, f"1 of 8 batch rows x {keep} of 5120 channels, full seqlen, forward + autograd backward"
     if name in ("c1", "c0"):
         h = make_c1_rows([0]) if name == "c1" else make_c0()
         nb = h["u"].shape[0]
@@ -296,6 +314,15 @@ def cpu_callable(name, h):
     ref = make_ref.load()
     kind = "reference" if ref else "port"
     f = lambda t: None if t is None else t.float()
+    if name == "c1b":
+        fn = ref["selective_scan"] if ref else tp.selective_scan
+
+        def fwd_bwd():
+            leaves = [h[k].detach().clone().requires_grad_() for k in ("u", "delta", "A", "B", "C", "D", "z", "delta_bias")]
+            out = fn(*leaves, delta_softplus=True)
+            out.backward(h["dout"].to(out.dtype))
+            return leaves[0].grad
+        return fwd_bwd, kind
     if name in ("c1", "c0"):
         fn = ref["selective_scan"] if ref else tp.selective_scan
         return (lambda: fn(h["u"], h["delta"], h["A"], h["B"], h["C"], h["D"], h["z"], h["delta_bias"], delta_softplus=True,
@@ -567,7 +594,7 @@ def reference_arm(args, rank):
     note = (f"each step is the bounded sample below, not the whole batch; {steps} of the {args.steps} requested steps and "
             f"{warm} of the {args.warmup} requested warm-ups fit the wall-clock budget of {budget:.0f} s")
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "impl": "reference", "metric": METRIC if name != "c1b" else "scan_bwd_tokens_per_s", "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warm,
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD_DESC[name], "sample_per_step": sample, "note": note},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind, "sample": sample},
@@ -582,9 +609,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["c0", "c1", "c2", "c3", "c4"],
+    ap.add_argument("--only", default=None, choices=["c0", "c1", "c1b", "c2", "c3", "c4"],
                     help="measure this one workload as the headline and skip the others")
-    ap.add_argument("--workload", dest="only", choices=["c0", "c1", "c2", "c3", "c4"], help=argparse.SUPPRESS)
+    ap.add_argument("--workload", dest="only", choices=["c0", "c1", "c1b", "c2", "c3", "c4"], help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--blocks", type=int, default=None, help="fixed number of timed blocks instead of >= 0.3 s worth (profiling captures)")
@@ -612,7 +639,7 @@ def main():
     cpu_budget = 0 if args.no_cpu_baseline else 8.0
     head, w = measure(head_name, dev, rank, world, local, args.steps, warmup, args.batch, cpu_budget)
     line = {
-        "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "metric": METRIC if head_name != "c1b" else "scan_bwd_tokens_per_s", "value": head["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong" if head_name != "c0" else "weak",
         "vs_baseline": None, "dtype": head["dtype"], "data": "synthetic",
         "config": {"workload": head["workload"], "this_gpu": head["this_gpu"], "partition": head["partition"],

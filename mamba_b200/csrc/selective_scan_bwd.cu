@@ -117,7 +117,7 @@ __device__ __forceinline__ const T *bc_row(const mb200_scan_bwd_args &a, const B
 // ---------------------------------------------------------------------------------------------- stored states
 // Walks forward and stores the state before every block but the first (which is zero).
 template <typename T, bool BV>
-__global__ void __launch_bounds__(64, 8) scan_bwd_states_kernel(const mb200_scan_bwd_args a, const BwdPlan pl)
+__global__ void __launch_bounds__(64, 9) scan_bwd_states_kernel(const mb200_scan_bwd_args a, const BwdPlan pl)
 {
     __shared__ float s_dl[kBlk][32], s_dlu[kBlk][32];
     __shared__ __align__(16) float s_B[kBlk][kNS];
@@ -206,15 +206,17 @@ __global__ void __launch_bounds__(64, 8) scan_bwd_states_kernel(const mb200_scan
 }
 
 // ---------------------------------------------------------------------------------------------- backward walk
-// What a warp keeps of its four steps of a block between the scalar phase and the final sums
-struct Kept {
-    float dl[4], u[4], slope[4], dy[4], dzf[4];
-};
-
+// Registers decide how many CTAs an SM holds, and with equal-length CTAs anything short of the whole grid resident
+// costs a second round: nine CTAs per SM hold all 1280 channel tiles of an (8, 5120) call at once.  To stay under
+// that limit only four of a block's eight h_t are kept at a time: the block is walked forward to its middle, its
+// second half forward (kept) and backward, then its first half again from the stored state, forward (kept) and
+// backward -- half a forward walk more instead of 32 more registers.
 template <typename T, bool BV, bool CV>
-__global__ void __launch_bounds__(64, 6) scan_bwd_kernel(const mb200_scan_bwd_args a, const BwdPlan pl)
+__global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_args a, const BwdPlan pl)
 {
     __shared__ float s_dl[kBlk][32], s_dlu[kBlk][32], s_dy[kBlk][32];
+    __shared__ float s_u[kBlk][32], s_slope[kBlk][32], s_dzf[kBlk][32];   // of a step, for the warp that finishes it
+    __shared__ float s_h0[2][8][32];                               // per warp: the state before the block
     __shared__ __align__(16) float s_BC[kBlk][2 * kNS];            // [step][B of 16 states, C of 16 states]
     __shared__ float s_part[2][3][kBlk][32];                       // per warp: sum g B, sum g (a h) A log2e, sum C h
     __shared__ __align__(16) float s_red[2][16 * kRedStride];      // per warp: 16 values of one step, by lane
@@ -275,7 +277,6 @@ __global__ void __launch_bounds__(64, 6) scan_bwd_kernel(const mb200_scan_bwd_ar
     for (int k = pl.nblk - 1; k >= 0; --k) {
         const int t0 = k * kBlk;
         // ---- scalars of my four steps, B and C of the block
-        Kept kp;
 #pragma unroll
         for (int i4 = 0; i4 < 4; ++i4) {
             const int i = 4 * w + i4;
@@ -290,10 +291,12 @@ __global__ void __launch_bounds__(64, 6) scan_bwd_kernel(const mb200_scan_bwd_ar
                 dzf = go * sg * fmaf(zz, 1.f - sg, 1.f);
             }
             if (!in) { dl = 0.f; uu = 0.f; dy = 0.f; dzf = 0.f; slope = 0.f; }
-            kp.dl[i4] = dl; kp.u[i4] = uu; kp.slope[i4] = slope; kp.dy[i4] = dy; kp.dzf[i4] = dzf;
             s_dl[i][lane] = dl;
             s_dlu[i][lane] = dl * uu;
             s_dy[i][lane] = dy;
+            s_u[i][lane] = uu;
+            s_slope[i][lane] = slope;
+            s_dzf[i][lane] = dzf;
         }
         if ((BV || CV) && w == 0) {
 #pragma unroll
@@ -301,17 +304,15 @@ __global__ void __launch_bounds__(64, 6) scan_bwd_kernel(const mb200_scan_bwd_ar
         }
         uint64_t h[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = pack2(hck[2 * j], hck[2 * j + 1]);
+        for (int j = 0; j < 4; ++j) {
+            h[j] = pack2(hck[2 * j], hck[2 * j + 1]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s_h0[w][j][lane] = hck[j];
         if (k > 0) fetch(k - 1);
         __syncthreads();
 
-        // ---- eight steps forward from the stored state, every h_t kept
-        uint64_t hs[kBlk][4];
-#pragma unroll
-        for (int i = 0; i < kBlk; ++i) {
-            const float dl = s_dl[i][lane], dlu = s_dlu[i][lane];
-            const uint64_t dl2 = pack2(dl, dl), dlu2 = pack2(dlu, dlu);
-            uint64_t Bp[4], Cp[4];
+        auto load_B = [&](int i, uint64_t (&Bp)[4]) {
             if (BV) {
                 const ulonglong2 b01 = *reinterpret_cast<const ulonglong2 *>(&s_BC[i][8 * w]);
                 const ulonglong2 b23 = *reinterpret_cast<const ulonglong2 *>(&s_BC[i][8 * w + 4]);
@@ -320,46 +321,8 @@ __global__ void __launch_bounds__(64, 6) scan_bwd_kernel(const mb200_scan_bwd_ar
 #pragma unroll
                 for (int j = 0; j < 4; ++j) Bp[j] = Bc[j];
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float x0, x1;
-                unpack2(mul2(dl2, A2[j]), x0, x1);
-                h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(dlu2, Bp[j]));
-                hs[i][j] = h[j];
-            }
-            if (has_z) {      // y_t, which only dz needs
-                if (CV) {
-                    const ulonglong2 c01 = *reinterpret_cast<const ulonglong2 *>(&s_BC[i][kNS + 8 * w]);
-                    const ulonglong2 c23 = *reinterpret_cast<const ulonglong2 *>(&s_BC[i][kNS + 8 * w + 4]);
-                    Cp[0] = c01.x; Cp[1] = c01.y; Cp[2] = c23.x; Cp[3] = c23.y;
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) Cp[j] = Cc[j];
-                }
-                uint64_t y2 = mul2(h[0], Cp[0]);
-#pragma unroll
-                for (int j = 1; j < 4; ++j) y2 = fma2(h[j], Cp[j], y2);
-                float y0, y1;
-                unpack2(y2, y0, y1);
-                s_part[w][2][i][lane] = y0 + y1;
-            }
-        }
-
-        // ---- the same eight steps backward
-        float res[kBlk];     // (variable B, C) lane pair v = lane / 2: sum over the channels of value v, per step
-#pragma unroll
-        for (int i = kBlk - 1; i >= 0; --i) {
-            const float dl = s_dl[i][lane], dlu = s_dlu[i][lane], dy = s_dy[i][lane];
-            const uint64_t dl2 = pack2(dl, dl), dlu2 = pack2(dlu, dlu), dy2 = pack2(dy, dy);
-            uint64_t Bp[4], Cp[4];
-            if (BV) {
-                const ulonglong2 b01 = *reinterpret_cast<const ulonglong2 *>(&s_BC[i][8 * w]);
-                const ulonglong2 b23 = *reinterpret_cast<const ulonglong2 *>(&s_BC[i][8 * w + 4]);
-                Bp[0] = b01.x; Bp[1] = b01.y; Bp[2] = b23.x; Bp[3] = b23.y;
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) Bp[j] = Bc[j];
-            }
+        };
+        auto load_C = [&](int i, uint64_t (&Cp)[4]) {
             if (CV) {
                 const ulonglong2 c01 = *reinterpret_cast<const ulonglong2 *>(&s_BC[i][kNS + 8 * w]);
                 const ulonglong2 c23 = *reinterpret_cast<const ulonglong2 *>(&s_BC[i][kNS + 8 * w + 4]);
@@ -368,53 +331,104 @@ __global__ void __launch_bounds__(64, 6) scan_bwd_kernel(const mb200_scan_bwd_ar
 #pragma unroll
                 for (int j = 0; j < 4; ++j) Cp[j] = Cc[j];
             }
-            uint64_t s1 = pack2(0.f, 0.f), s2 = pack2(0.f, 0.f);
-            float *red = s_red[w];
+        };
+        auto step_forward = [&](int i) {
+            const float dl = s_dl[i][lane], dlu = s_dlu[i][lane];
+            const uint64_t dl2 = pack2(dl, dl), dlu2 = pack2(dlu, dlu);
+            uint64_t Bp[4];
+            load_B(i, Bp);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint64_t g = fma2(Cp[j], dy2, gc[j]);                 // g_t
-                const uint64_t ah = sub2(hs[i][j], mul2(dlu2, Bp[j]));      // a_t h_{t-1}
-                const uint64_t gah = mul2(g, ah);
-                dA2[j] = fma2(gah, dl2, dA2[j]);
-                s1 = fma2(g, Bp[j], s1);
-                s2 = fma2(gah, A2[j], s2);
-                const uint64_t db = mul2(g, dlu2), dc = mul2(hs[i][j], dy2);
-                if (BV) {
-                    float lo, hi;
-                    unpack2(db, lo, hi);
-                    red[(2 * j) * kRedStride + lane] = lo;
-                    red[(2 * j + 1) * kRedStride + lane] = hi;
-                } else {
-                    dBc[j] = add2(dBc[j], db);
-                }
-                if (CV) {
-                    float lo, hi;
-                    unpack2(dc, lo, hi);
-                    red[(8 + 2 * j) * kRedStride + lane] = lo;
-                    red[(8 + 2 * j + 1) * kRedStride + lane] = hi;
-                } else {
-                    dCc[j] = add2(dCc[j], dc);
-                }
                 float x0, x1;
                 unpack2(mul2(dl2, A2[j]), x0, x1);
-                gc[j] = mul2(pack2(ex2(x0), ex2(x1)), g);                   // a_t g_t, what step t-1 receives
+                h[j] = fma2(pack2(ex2(x0), ex2(x1)), h[j], mul2(dlu2, Bp[j]));
             }
-            {
-                float lo, hi;
-                unpack2(s1, lo, hi);
-                s_part[w][0][i][lane] = lo + hi;
-                unpack2(s2, lo, hi);
-                s_part[w][1][i][lane] = lo + hi;
+        };
+
+        // ---- forward to the middle of the block; then per half: forward with every h_t kept, and backward
+#pragma unroll
+        for (int i = 0; i < 4; ++i) step_forward(i);
+        float res[kBlk];     // (variable B, C) lane pair v = lane / 2: sum over the channels of value v, per step
+#pragma unroll
+        for (int half = 1; half >= 0; --half) {
+            if (half == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = pack2(s_h0[w][2 * j][lane], s_h0[w][2 * j + 1][lane]);
             }
-            if (BV || CV) {
-                __syncwarp();
-                const float4 *src = reinterpret_cast<const float4 *>(red + (lane >> 1) * kRedStride + (lane & 1) * 16);
-                const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
-                float s = ((p0.x + p0.y) + (p0.z + p0.w)) + ((p1.x + p1.y) + (p1.z + p1.w)) + ((p2.x + p2.y) + (p2.z + p2.w)) +
-                          ((p3.x + p3.y) + (p3.z + p3.w));
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                res[i] = s;
-                __syncwarp();
+            uint64_t hs[4][4];
+#pragma unroll
+            for (int i4 = 0; i4 < 4; ++i4) {
+                const int i = 4 * half + i4;
+                step_forward(i);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) hs[i4][j] = h[j];
+                if (has_z) {      // y_t, which only dz needs
+                    uint64_t Cp[4];
+                    load_C(i, Cp);
+                    uint64_t y2 = mul2(h[0], Cp[0]);
+#pragma unroll
+                    for (int j = 1; j < 4; ++j) y2 = fma2(h[j], Cp[j], y2);
+                    float y0, y1;
+                    unpack2(y2, y0, y1);
+                    s_part[w][2][i][lane] = y0 + y1;
+                }
+            }
+#pragma unroll
+            for (int i4 = 3; i4 >= 0; --i4) {
+                const int i = 4 * half + i4;
+                const float dl = s_dl[i][lane], dlu = s_dlu[i][lane], dy = s_dy[i][lane];
+                const uint64_t dl2 = pack2(dl, dl), dlu2 = pack2(dlu, dlu), dy2 = pack2(dy, dy);
+                uint64_t Bp[4], Cp[4];
+                load_B(i, Bp);
+                load_C(i, Cp);
+                uint64_t s1 = pack2(0.f, 0.f), s2 = pack2(0.f, 0.f);
+                float *red = s_red[w];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint64_t g = fma2(Cp[j], dy2, gc[j]);                 // g_t
+                    const uint64_t ah = sub2(hs[i4][j], mul2(dlu2, Bp[j]));     // a_t h_{t-1}
+                    const uint64_t gah = mul2(g, ah);
+                    dA2[j] = fma2(gah, dl2, dA2[j]);
+                    s1 = fma2(g, Bp[j], s1);
+                    s2 = fma2(gah, A2[j], s2);
+                    const uint64_t db = mul2(g, dlu2), dc = mul2(hs[i4][j], dy2);
+                    if (BV) {
+                        float lo, hi;
+                        unpack2(db, lo, hi);
+                        red[(2 * j) * kRedStride + lane] = lo;
+                        red[(2 * j + 1) * kRedStride + lane] = hi;
+                    } else {
+                        dBc[j] = add2(dBc[j], db);
+                    }
+                    if (CV) {
+                        float lo, hi;
+                        unpack2(dc, lo, hi);
+                        red[(8 + 2 * j) * kRedStride + lane] = lo;
+                        red[(8 + 2 * j + 1) * kRedStride + lane] = hi;
+                    } else {
+                        dCc[j] = add2(dCc[j], dc);
+                    }
+                    float x0, x1;
+                    unpack2(mul2(dl2, A2[j]), x0, x1);
+                    gc[j] = mul2(pack2(ex2(x0), ex2(x1)), g);                   // a_t g_t, what step t-1 receives
+                }
+                {
+                    float lo, hi;
+                    unpack2(s1, lo, hi);
+                    s_part[w][0][i][lane] = lo + hi;
+                    unpack2(s2, lo, hi);
+                    s_part[w][1][i][lane] = lo + hi;
+                }
+                if (BV || CV) {
+                    __syncwarp();
+                    const float4 *src = reinterpret_cast<const float4 *>(red + (lane >> 1) * kRedStride + (lane & 1) * 16);
+                    const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
+                    float s = ((p0.x + p0.y) + (p0.z + p0.w)) + ((p1.x + p1.y) + (p1.z + p1.w)) + ((p2.x + p2.y) + (p2.z + p2.w)) +
+                              ((p3.x + p3.y) + (p3.z + p3.w));
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    res[i] = s;
+                    __syncwarp();
+                }
             }
         }
         if (BV || CV) {
@@ -445,11 +459,12 @@ __global__ void __launch_bounds__(64, 6) scan_bwd_kernel(const mb200_scan_bwd_ar
             const int i = 4 * w + i4;
             const float S1 = s_part[0][0][i][lane] + s_part[1][0][i][lane];
             const float S2 = s_part[0][1][i][lane] + s_part[1][1][i][lane];
-            o_du[i4] = fmaf(kp.dl[i4], S1, Dd * kp.dy[i4]);
-            o_dd[i4] = fmaf(kLn2, S2, kp.u[i4] * S1) * kp.slope[i4];
+            const float uu = s_u[i][lane], dy = s_dy[i][lane];
+            o_du[i4] = fmaf(s_dl[i][lane], S1, Dd * dy);
+            o_dd[i4] = fmaf(kLn2, S2, uu * S1) * s_slope[i][lane];
             o_dz[i4] = 0.f;
-            if (has_z) o_dz[i4] = fmaf(Dd, kp.u[i4], s_part[0][2][i][lane] + s_part[1][2][i][lane]) * kp.dzf[i4];
-            dD_acc = fmaf(kp.u[i4], kp.dy[i4], dD_acc);
+            if (has_z) o_dz[i4] = fmaf(Dd, uu, s_part[0][2][i][lane] + s_part[1][2][i][lane]) * s_dzf[i][lane];
+            dD_acc = fmaf(uu, dy, dD_acc);
             dbias_acc += o_dd[i4];
         }
         if (q.active) {
@@ -496,8 +511,10 @@ __global__ void __launch_bounds__(64, 6) scan_bwd_kernel(const mb200_scan_bwd_ar
                 if (has_z) put(a.dz, a.dz_stride, o_dz);
             }
         }
-        // the next block's scalar phase rewrites s_dl.. and s_BC, which both warps stopped reading at the barrier
-        // above; s_part is rewritten only after the next block's first barrier, which the reads above precede
+        // The next block's scalar phase rewrites the rows of s_dl .. s_dzf that this warp itself has just read (each warp
+        // prepares and finishes the same four steps), but the other warp's forward walk of that block must not start
+        // before they are complete and this block's reads are done: the barrier after the scalar phase orders both.
+        // s_part is rewritten only after that barrier, which the reads above precede.
     }
 
     if (q.active) {

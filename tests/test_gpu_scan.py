@@ -277,8 +277,17 @@ def test_extension_module_stand_in(many):
     assert_close(x[:, :, -1, 1::2], want_last, TOL_FP32, "last state slice")
     out2, x2 = selective_scan_cuda.fwd(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], None, c["delta_bias"], True)
     assert_close(out2, want, TOL_FP32, "no gate")
-    with pytest.raises(NotImplementedError):
-        selective_scan_cuda.bwd()
+    # the backward of the same module, called the way SelectiveScanFn.backward does (:83-86): x and out are handed
+    # over (and not needed), dz comes back last
+    g = torch.Generator().manual_seed(181)
+    dout = torch.randn(inp["u"].shape, generator=g)
+    res = selective_scan_cuda.bwd(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], c["z"], c["delta_bias"], dout.to(DEV), x, out,
+                                  None, True, False)
+    want_g = oracle.selective_scan_bwd(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"], inp["z"], inp["delta_bias"],
+                                       dout, True)
+    for k, got, ref in zip(("du", "ddelta", "dA", "dB", "dC", "dD", "ddelta_bias", "dz"), res,
+                           (want_g[0], want_g[1], want_g[2], want_g[3], want_g[4], want_g[5], want_g[7], want_g[6])):
+        assert_close(got, ref, TOL_FP32, "stand-in bwd " + k)
 
 
 def test_extension_module_stand_in_converts_parameter_dtypes():
