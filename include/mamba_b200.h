@@ -100,9 +100,10 @@ int mb200_scan_scratch_bytes(const mb200_scan_args *args, size_t *bytes);
  * The library zeroes dA, dB, dC, dD, ddelta_bias on the stream before it accumulates into them.
  * The gradient with respect to last_state is not taken, as in the reference (selective_scan_interface.py:121-122).
  *
- * scratch: required, 16-byte aligned, mb200_scan_bwd_scratch_bytes() bytes: the states at every eighth step
- * (written by a first forward launch, read by the backward launch that walks the sequence from the end) and, above
- * 16 states, fp32 partial sums of du, ddelta, dz between the passes over 16 states each.
+ * scratch: required, 16-byte aligned: the states at every eighth step (written by a first forward launch, read by the
+ * backward launch that walks the sequence from the end) and, above 16 states, fp32 partial sums of du, ddelta, dz
+ * between the passes over 16 states each.  mb200_scan_bwd_scratch_bytes() returns the size for the whole batch up to
+ * 1 GiB; a larger batch is walked in slices of as many rows as the lent scratch holds (one row is the minimum).
  */
 typedef struct mb200_scan_bwd_args {
     const void *u, *delta;

@@ -3,8 +3,9 @@
 The reference's ``SelectiveScanFn.forward`` (mamba_ssm/ops/selective_scan_interface.py:36-68) calls
 ``selective_scan_cuda.fwd(u, delta, A, B, C, D, z, delta_bias, delta_softplus)`` and expects
 ``[out, x]`` or ``[out, x, out_z]`` back (csrc/selective_scan/selective_scan.cpp:226-336), where ``x``
-is ``(batch, dim, n_chunks, 2 * dstate)`` with the running state at the odd positions of the last chunk
-(the forward only ever reads ``x[:, :, -1, 1::2]``).  Installing this object under that name lets the
+is ``(batch, dim, n_chunks, 2 * dstate)`` holding, per 2048-step chunk and state, the product of the decays from the
+first step to the chunk's end (even positions) and the state there (odd positions); the reference's forward only ever
+reads ``x[:, :, -1, 1::2]``, its backward kernel reads all of it.  Installing this object under that name lets the
 reference's own Python run unmodified on top of libmamba_b200 for inference:
 
     import sys, mamba_b200.compat
@@ -70,7 +71,22 @@ class _SelectiveScanCuda:
         else:
             L.set_strides(a.out_stride, out, 2)
         L.check(L.lib().mb200_selective_scan_fwd(ctypes.byref(a), L.stream_ptr(u.device)))
+        # x[b, d, c] = (product of exp(dt A) from the first step to the end of chunk c, state there) per state, interleaved:
+        # the running prefix of selective_scan_fwd_kernel.cuh:240-258, which the extension's own backward reads.  The
+        # library's kernels do not need it, so it is assembled here, off the hot path: the decay products from a running
+        # sum of dt, the states before the last chunk end from forward calls over the prefixes (none up to 2048 steps).
         x[:, :, -1, 1::2] = last
+        dt = delta.float() if bias32 is None else delta.float() + bias32[:, None]
+        if delta_softplus:
+            dt = torch.nn.functional.softplus(dt)
+        ends = [min((c + 1) * _CHUNK, seqlen) for c in range(n_chunks)]
+        sums = dt.cumsum(-1)[..., [e - 1 for e in ends]] if seqlen > 0 else dt.new_zeros(batch, dim, n_chunks)
+        x[..., 0::2] = torch.exp(sums[..., None] * A[None, :, None, :])
+        from . import ops
+        for c, e in enumerate(ends[:-1]):
+            cut = lambda t, var: t[..., :e] if var else t
+            x[:, :, c, 1::2] = ops._selective_scan(u[..., :e], delta[..., :e], A, cut(B, B_var), cut(C, C_var), D32, None, bias32,
+                                                   delta_softplus, return_last_state=True)[1]
         return [out, x] if z_ is None else [out, x, out_z]
 
     @staticmethod

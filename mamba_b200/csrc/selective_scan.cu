@@ -553,6 +553,7 @@ __device__ int g_scan_status;
 enum { kStScanFull = 31, kStScanZ, kStScanReady, kStScanYdone, kStScanAlign };
 
 constexpr int kStreamCh = 32;      // channels per CTA (lanes of a warp)
+constexpr int64_t kStreamMinChannels = 1024;   // fewer (batch x dim) channels than this go to the time-parallel kernel
 constexpr int kHB = 8;             // steps per hand-off
 
 struct ScanMaps { CUtensorMap u, dt, z, out, B, C; };
@@ -567,7 +568,7 @@ struct ScanSplit {
     float *hend, *pdec;     // (batch, nseg, dim, dstate), SUMMARY launches only
 };
 
-template <typename T, int NS>
+template <typename T, int NS, int SW, int NB>
 struct __align__(256) StreamSmem {
     uint8_t u[2][kStreamCh * 32];
     uint8_t dt[2][kStreamCh * 32];
@@ -577,26 +578,36 @@ struct __align__(256) StreamSmem {
     uint8_t C[2][(NS * 32 + 255) / 256 * 256];
     // per-channel rows of 8 steps (32 bytes) in the same chunk-swizzled layout as the tiles: a lane moves four
     // steps with one conflict-free 128-bit access
-    float xd[2][2][kStreamCh * kHB];         // [buffer][dt | dt*u][channel][step]
-    float du[2][kStreamCh * kHB];            // [buffer][channel][step]: D*u, kept by the scalar warp for its epilogue
-    float bc[2][2][kHB * NS + 16];           // [buffer][B | C][step][state]; the pad puts B and C on different banks
-    float yp[2][2][kStreamCh * kHB];         // [buffer][state warp][channel][step]
-    uint64_t full[2], zfull[2], ready[2], ydone[2];
+    float xd[NB][2][kStreamCh * kHB];        // [buffer][dt | dt*u][channel][step]
+    float du[NB][kStreamCh * kHB];           // [buffer][channel][step]: D*u, kept by the scalar warp for its epilogue
+    float bc[NB][2][kHB * NS + 16];          // [buffer][B | C][step][state]; the pad puts B and C on different banks
+    float yp[NB][SW][kStreamCh * kHB];       // [buffer][state warp][channel][step]
+    uint64_t full[2], zfull[2], ready[NB], ydone[NB], edone[NB];
 };
 
 // byte offset of 16-byte chunk `chunk` of row `row` in a [rows x 32 B] SWIZZLE_32B tile (256-byte aligned)
 __device__ __forceinline__ int sw32_offset(int row, int chunk) { return row * 32 + ((chunk ^ ((row >> 2) & 1)) << 4); }
 
-template <typename T, int NS, bool SUMMARY>
-__global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_args a, const __grid_constant__ ScanMaps maps, const ScanSplit sp)
+// SW state warps share the states of the 32 channels; SPLIT gives the scalar work to two warps (warp 0 streams the
+// tiles in and prepares the hand-offs, warp 1 finishes the outputs and streams them out) instead of one.  (2, false) is
+// the layout described above: three warps, nine CTAs per SM, the choice whenever the grid fills the GPU.  (4, true) is
+// the layout for grids that leave SMs nearly empty (a batch divided over several GPUs): six warps per CTA cut the
+// serial chain of a hand-off -- which is all that matters when a CTA has an SM almost to itself -- to a quarter.
+template <typename T, int NS, bool SUMMARY, int SW, bool SPLIT>
+__global__ void __launch_bounds__(32 * (SW + (SPLIT ? 2 : 1)), SW == 2 && !SPLIT ? 9 : 4)
+scan_stream_kernel(const mb200_scan_args a, const __grid_constant__ ScanMaps maps, const ScanSplit sp)
 {
     using namespace tc;
     constexpr int TB = 32 / sizeof(T);                 // steps per tile (32 bytes of a row)
     constexpr int HPT = TB / kHB;                      // hand-offs per tile: 2 (16-bit) or 1 (fp32)
     constexpr int CPH = kHB * sizeof(T) / 16;          // 16-byte chunks per hand-off: 1 or 2
-    constexpr int HS = NS / 2;                         // states per lane of a state warp
+    constexpr int HS = NS / SW;                        // states per lane of a state warp
+    constexpr int kScalarWarps = SPLIT ? 2 : 1;
+    // hand-off buffers: with one scalar warp two are all it can use (it prepares hand-off hb+1, then finishes hb); with
+    // the work on two warps, four let the three stages of the chain run at the pace of the slowest, not of their sum
+    constexpr int NB = SPLIT ? 4 : 2;
     extern __shared__ __align__(256) uint8_t smem_raw[];
-    StreamSmem<T, NS> &sm = *reinterpret_cast<StreamSmem<T, NS> *>(smem_raw);
+    StreamSmem<T, NS, SW, NB> &sm = *reinterpret_cast<StreamSmem<T, NS, SW, NB> *>(smem_raw);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int N = a.dstate;
     const int b = blockIdx.y / sp.nseg, seg = blockIdx.y % sp.nseg;
@@ -619,15 +630,19 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sm.full[i], 1);
             mbar_init(&sm.zfull[i], 1);
+        }
+        for (int i = 0; i < NB; ++i) {
             mbar_init(&sm.ready[i], 1);
-            mbar_init(&sm.ydone[i], 2);
+            mbar_init(&sm.ydone[i], SW);
+            mbar_init(&sm.edone[i], 1);
         }
         mbar_fence_init();
     }
     __syncthreads();
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ scalar warp
+    if (warp < kScalarWarps) {
+        // ------------------------------------------------------------------ scalar warp(s)
+        const bool in_side = warp == 0, out_side = warp == kScalarWarps - 1;
         constexpr uint32_t kTileBytes = 2 * kStreamCh * 32 + (SUMMARY ? 1 : 2) * NS * 32;      // a summary needs no C
         auto issue_tile = [&](int k) {          // lane 0 only
             const int s = k & 1;
@@ -649,7 +664,8 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
             if (has_z) prefetch_tmap(&maps.z);
         }
         for (int k = 0; k < 2 && k < ntiles; ++k) {
-            if (lane == 0) { issue_tile(k); if (has_z) issue_z(k); }
+            if (lane == 0 && in_side) issue_tile(k);
+            if (lane == 0 && out_side && has_z) issue_z(k);
             ++issued; ++zissued;
         }
         const float bias = a.delta_bias ? a.delta_bias[d] : 0.f;
@@ -659,7 +675,10 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
         bool ok = true;
 
         auto prologue = [&](int hb) {
-            const int k = hb / HPT, s = k & 1, part = hb % HPT, buf = hb & 1;
+            const int k = hb / HPT, s = k & 1, part = hb % HPT, buf = hb % NB;
+            if (SPLIT && hb >= NB) {    // the other scalar warp has finished with this buffer's D*u and partial outputs
+                if (!mbar_wait(&sm.edone[buf], ((hb - NB) / NB) & 1, status, kStScanYdone)) { ok = false; return; }
+            }
             if (part == 0) {
                 if (!mbar_wait(&sm.full[s], (k >> 1) & 1, status, kStScanFull)) { ok = false; return; }
                 ++waited;
@@ -716,9 +735,12 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
         };
 
         auto epilogue = [&](int hb) {
-            const int k = hb / HPT, s = k & 1, part = hb % HPT, buf = hb & 1;
-            if (!mbar_wait(&sm.ydone[buf], (hb >> 1) & 1, status, kStScanYdone)) { ok = false; return; }
-            if (SUMMARY) return;                // nothing to put out: the wait only hands the buffers back
+            const int k = hb / HPT, s = k & 1, part = hb % HPT, buf = hb % NB;
+            if (!mbar_wait(&sm.ydone[buf], (hb / NB) & 1, status, kStScanYdone)) { ok = false; return; }
+            if (SUMMARY) {                      // nothing to put out: the wait only hands the buffers back
+                if (SPLIT && lane == 0) mbar_arrive(&sm.edone[buf]);
+                return;
+            }
             if (part == 0) {
                 if (has_z) {
                     if (!mbar_wait(&sm.zfull[s], (k >> 1) & 1, status, kStScanZ)) { ok = false; return; }
@@ -733,13 +755,23 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const int off = sw32_offset(lane, c);
-                const float4 p0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.yp[buf][0]) + off);
+                float4 p0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.yp[buf][0]) + off);
                 const float4 p1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.yp[buf][1]) + off);
+                if constexpr (SW == 4) {
+                    const float4 p2 = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.yp[buf][2]) + off);
+                    const float4 p3 = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.yp[buf][3]) + off);
+                    p0 = make_float4(p0.x + p2.x, p0.y + p2.y, p0.z + p2.z, p0.w + p2.w);
+                    p0 = make_float4(p0.x + p3.x, p0.y + p3.y, p0.z + p3.z, p0.w + p3.w);
+                }
                 const float4 sk = *reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(sm.du[buf]) + off);
                 y[4 * c] = (p0.x + p1.x) + sk.x;
                 y[4 * c + 1] = (p0.y + p1.y) + sk.y;
                 y[4 * c + 2] = (p0.z + p1.z) + sk.z;
                 y[4 * c + 3] = (p0.w + p1.w) + sk.w;
+            }
+            if (SPLIT) {        // D*u and the partial outputs of this buffer are in registers: the other warp may refill it
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.edone[buf]);
             }
             if (has_z) {
                 uint32_t wz[CPH * 4];
@@ -779,22 +811,29 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
             }
         };
 
-        prologue(0);
-        for (int hb = 0; hb < nhb && ok; ++hb) {
-            if (hb + 1 < nhb) prologue(hb + 1);
-            if (ok) epilogue(hb);
+        if (!SPLIT) {
+            prologue(0);
+            for (int hb = 0; hb < nhb && ok; ++hb) {
+                if (hb + 1 < nhb) prologue(hb + 1);
+                if (ok) epilogue(hb);
+            }
+        } else if (in_side) {
+            for (int hb = 0; hb < nhb && ok; ++hb) prologue(hb);
+        } else {
+            for (int hb = 0; hb < nhb && ok; ++hb) epilogue(hb);
         }
         if (lane == 0) {
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (out_side) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             if (!ok) {      // stopped early: let the tiles already requested land before the CTA's shared memory goes away
-                for (int k = waited; k < issued; ++k) mbar_wait(&sm.full[k & 1], (k >> 1) & 1, status, kStScanFull);
-                if (has_z)
+                if (in_side)
+                    for (int k = waited; k < issued; ++k) mbar_wait(&sm.full[k & 1], (k >> 1) & 1, status, kStScanFull);
+                if (out_side && has_z)
                     for (int k = zwaited; k < zissued; ++k) mbar_wait(&sm.zfull[k & 1], (k >> 1) & 1, status, kStScanZ);
             }
         }
     } else {
         // ------------------------------------------------------------------ state warps
-        const int w = warp - 1;
+        const int w = warp - kScalarWarps;
         uint64_t A2[HS / 2], h[HS / 2];
 #pragma unroll
         for (int j = 0; j < HS / 2; ++j) {
@@ -816,8 +855,8 @@ __global__ void __launch_bounds__(96, 9) scan_stream_kernel(const mb200_scan_arg
         }
         float sum_dl = 0.f;          // SUMMARY: the decay product of the segment is 2^(A log2e * sum of dt)
         for (int hb = 0; hb < nhb; ++hb) {
-            const int buf = hb & 1;
-            if (!mbar_wait(&sm.ready[buf], (hb >> 1) & 1, status, kStScanReady)) break;
+            const int buf = hb % NB;
+            if (!mbar_wait(&sm.ready[buf], (hb / NB) & 1, status, kStScanReady)) break;
             const float *Bt = sm.bc[buf][0] + w * HS, *Ct = sm.bc[buf][1] + w * HS;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
@@ -914,7 +953,7 @@ bool stream_eligible(const mb200_scan_args &a)
     constexpr int VEC = 16 / sizeof(T);
     if (a.dstate > 16 || !a.B_variable || !a.C_variable || a.out_pregate) return false;
     if ((a.dim / a.ngroups) % kStreamCh != 0) return false;
-    if ((int64_t)a.batch * a.dim < 2LL * 32 * 148 && split_segments<T>(a) <= 1) return false;
+    if ((int64_t)a.batch * a.dim < kStreamMinChannels && split_segments<T>(a) <= 1) return false;
     auto ok2 = [&](const void *p, const int64_t *s) { return aligned16(p) && s[0] > 0 && s[1] > 0 && s[0] % VEC == 0 && s[1] % VEC == 0; };
     auto ok3 = [&](const void *p, const int64_t *s) {
         return aligned16(p) && s[0] > 0 && s[1] > 0 && s[2] > 0 && s[0] % VEC == 0 && s[1] % VEC == 0 && s[2] % VEC == 0;
@@ -973,11 +1012,21 @@ int launch_stream(const mb200_scan_args &a, cudaStream_t stream)
         seg_len = (int)(((a.seqlen + nseg - 1) / nseg + TB - 1) / TB * TB);     // whole tiles per segment
         nseg = (a.seqlen + seg_len - 1) / seg_len;                              // rounding up may leave the last ones empty
     }
+    // A grid that leaves the SMs nearly empty runs the six-warp layout (four CTAs of it fit an SM); see the kernel.
+    auto go = [&](dim3 grid, const ScanSplit &split, bool summary) {
+        const bool wide = (int64_t)grid.x * grid.y <= 4 * 148;
+        auto pick = [&](auto ns_c, auto sum_c) {
+            constexpr int NS = decltype(ns_c)::value;
+            constexpr bool SUM = decltype(sum_c)::value;
+            if (wide) scan_stream_kernel<T, NS, SUM, 4, true><<<grid, 192, sizeof(StreamSmem<T, NS, 4, 4>), stream>>>(a, maps, split);
+            else scan_stream_kernel<T, NS, SUM, 2, false><<<grid, 96, sizeof(StreamSmem<T, NS, 2, 2>), stream>>>(a, maps, split);
+        };
+        if (ns == 8) summary ? pick(std::integral_constant<int, 8>{}, std::true_type{}) : pick(std::integral_constant<int, 8>{}, std::false_type{});
+        else summary ? pick(std::integral_constant<int, 16>{}, std::true_type{}) : pick(std::integral_constant<int, 16>{}, std::false_type{});
+    };
     if (nseg <= 1) {
         const ScanSplit one = {1, seg_len, nullptr, nullptr, nullptr};
-        dim3 grid(a.dim / kStreamCh, a.batch);
-        if (ns == 8) scan_stream_kernel<T, 8, false><<<grid, 96, sizeof(StreamSmem<T, 8>), stream>>>(a, maps, one);
-        else scan_stream_kernel<T, 16, false><<<grid, 96, sizeof(StreamSmem<T, 16>), stream>>>(a, maps, one);
+        go(dim3(a.dim / kStreamCh, a.batch), one, false);
         return MB200_OK;
     }
     // Few channel groups: the sequence is cut into nseg segments that run side by side.  A first launch summarises
@@ -987,11 +1036,9 @@ int launch_stream(const mb200_scan_args &a, cudaStream_t stream)
     float *h0 = static_cast<float *>(a.scratch), *hend = h0 + region, *pdec = hend + region;
     const ScanSplit sum = {nseg, seg_len, nullptr, hend, pdec}, full = {nseg, seg_len, h0, nullptr, nullptr};
     dim3 grid(a.dim / kStreamCh, a.batch * nseg);       // in the summary launch the CTAs of the last segment return at once
-    if (ns == 8) scan_stream_kernel<T, 8, true><<<grid, 96, sizeof(StreamSmem<T, 8>), stream>>>(a, maps, sum);
-    else scan_stream_kernel<T, 16, true><<<grid, 96, sizeof(StreamSmem<T, 16>), stream>>>(a, maps, sum);
+    go(grid, sum, true);
     scan_fold_segments_kernel<<<(unsigned)((a.batch * per_seg + 255) / 256), 256, 0, stream>>>(h0, hend, pdec, nseg, per_seg, a.batch);
-    if (ns == 8) scan_stream_kernel<T, 8, false><<<grid, 96, sizeof(StreamSmem<T, 8>), stream>>>(a, maps, full);
-    else scan_stream_kernel<T, 16, false><<<grid, 96, sizeof(StreamSmem<T, 16>), stream>>>(a, maps, full);
+    go(grid, full, false);
     return MB200_OK;
 }
 

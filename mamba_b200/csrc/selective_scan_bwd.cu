@@ -18,6 +18,7 @@
 // leave as one vector atomic per four steps, 1/32 of the reference's atomic traffic.  The sums over the states
 // (du, d(dt), y for dz) cross the two warps through shared memory.  dstate > 16 repeats both launches per 16 states
 // and carries fp32 partial sums of du, ddelta, dz between the passes.
+#include <algorithm>
 #include <type_traits>
 
 #include "common.cuh"
@@ -540,12 +541,20 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
 
 bool aligned_to(const void *p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
 
-size_t ckpt_floats(const mb200_scan_bwd_args &a)
+// Scratch per batch row: the stored states and, above 16 states, the partial sums carried between the passes.  Batch
+// rows are independent, so a large batch is walked in slices that re-use one scratch of at most kScratchCap bytes (one
+// row if a single row needs more).
+constexpr size_t kScratchCap = size_t(1) << 30;
+size_t ckpt_floats_per_row(const mb200_scan_bwd_args &a) { return (((size_t)a.seqlen + kBlk - 1) / kBlk) * kNS * a.dim; }
+size_t acc_floats_per_row(const mb200_scan_bwd_args &a) { return a.dstate > kNS ? 3 * (size_t)a.dim * a.seqlen : 0; }
+size_t row_bytes(const mb200_scan_bwd_args &a) { return sizeof(float) * (ckpt_floats_per_row(a) + acc_floats_per_row(a)); }
+int rows_under_cap(const mb200_scan_bwd_args &a)
 {
-    const size_t nblk = ((size_t)a.seqlen + kBlk - 1) / kBlk;
-    return (size_t)a.batch * nblk * kNS * a.dim;
+    const size_t per_row = row_bytes(a);
+    if (per_row == 0) return a.batch;
+    const size_t rows = kScratchCap / per_row;
+    return (int)(rows < 1 ? 1 : rows > (size_t)a.batch ? (size_t)a.batch : rows);
 }
-size_t acc_floats(const mb200_scan_bwd_args &a) { return a.dstate > kNS ? 3 * (size_t)a.batch * a.dim * a.seqlen : 0; }
 
 template <typename T, bool BV, bool CV>
 void launch_pass(const mb200_scan_bwd_args &a, const BwdPlan &pl, dim3 grid, cudaStream_t stream)
@@ -555,7 +564,41 @@ void launch_pass(const mb200_scan_bwd_args &a, const BwdPlan &pl, dim3 grid, cud
 }
 
 template <typename T>
+int launch_slice(const mb200_scan_bwd_args &a, cudaStream_t stream);
+
+// Walks the batch in slices of as many rows as the lent scratch holds.
+template <typename T>
 int launch_bwd(const mb200_scan_bwd_args &a, cudaStream_t stream)
+{
+    const size_t per_row = row_bytes(a);
+    const int rows = per_row ? (int)std::min<size_t>((size_t)a.batch, a.scratch_bytes / per_row) : a.batch;
+    for (int b0 = 0; b0 < a.batch; b0 += rows) {
+        mb200_scan_bwd_args s = a;
+        s.batch = std::min(rows, a.batch - b0);
+        auto adv = [&](const void *p, int64_t stride) { return p ? static_cast<const void *>(static_cast<const char *>(p) + (int64_t)b0 * stride * (int64_t)sizeof(T)) : p; };
+        s.u = adv(a.u, a.u_stride[0]);
+        s.delta = adv(a.delta, a.delta_stride[0]);
+        s.z = adv(a.z, a.z_stride[0]);
+        s.dout = adv(a.dout, a.dout_stride[0]);
+        s.du = const_cast<void *>(adv(a.du, a.du_stride[0]));
+        s.ddelta = const_cast<void *>(adv(a.ddelta, a.ddelta_stride[0]));
+        s.dz = const_cast<void *>(adv(a.dz, a.dz_stride[0]));
+        const int64_t vrow = (int64_t)a.ngroups * a.dstate * a.seqlen;      // dB, dC: fp32, contiguous
+        if (a.B_variable) {
+            s.B = adv(a.B, a.B_stride[0]);
+            s.dB = a.dB + (int64_t)b0 * vrow;
+        }
+        if (a.C_variable) {
+            s.C = adv(a.C, a.C_stride[0]);
+            s.dC = a.dC + (int64_t)b0 * vrow;
+        }
+        if (int rc = launch_slice<T>(s, stream)) return rc;
+    }
+    return MB200_OK;
+}
+
+template <typename T>
+int launch_slice(const mb200_scan_bwd_args &a, cudaStream_t stream)
 {
     constexpr int VEC = 16 / sizeof(T);
     auto rows_ok = [&](const void *p, const int64_t *s) { return aligned_to(p, 16) && s[0] % VEC == 0 && s[1] % VEC == 0; };
@@ -571,7 +614,7 @@ int launch_bwd(const mb200_scan_bwd_args &a, cudaStream_t stream)
     pl.tiles_per_group = (per_group + 31) / 32;
     pl.npass = (a.dstate + kNS - 1) / kNS;
     pl.ckpt = static_cast<float *>(a.scratch);
-    pl.acc = pl.ckpt + ckpt_floats(a);
+    pl.acc = pl.ckpt + (size_t)a.batch * ckpt_floats_per_row(a);
     dim3 grid(a.ngroups * pl.tiles_per_group, a.batch);
     for (int p = 0; p < pl.npass; ++p) {
         pl.pass = p;
@@ -606,7 +649,7 @@ extern "C" int mb200_scan_bwd_scratch_bytes(const mb200_scan_bwd_args *args, siz
     if (!args || !bytes) return fail(MB200_ERR_BAD_ARG, "scan_bwd_scratch_bytes: NULL argument");
     *bytes = 0;
     if (int rc = check_bwd(*args)) return rc;
-    *bytes = sizeof(float) * (ckpt_floats(*args) + acc_floats(*args)) + 16;
+    *bytes = (size_t)rows_under_cap(*args) * row_bytes(*args) + 16;
     return MB200_OK;
 }
 
@@ -636,9 +679,9 @@ extern "C" int mb200_selective_scan_bwd(const mb200_scan_bwd_args *args, void *s
     MB200_CHECK_ARG(a.u && a.delta && a.B && a.C && a.dout && a.du && a.ddelta && a.dB && a.dC,
                     "selective_scan_bwd: a required tensor is NULL");
     MB200_CHECK_ARG(!a.z || a.dz, "selective_scan_bwd: dz is required with z");
-    const size_t need = sizeof(float) * (ckpt_floats(a) + acc_floats(a));
+    const size_t need = row_bytes(a);      // at least one batch row at a time
     MB200_CHECK_ARG(a.scratch && a.scratch_bytes >= need && aligned_to(a.scratch, 16),
-                    "selective_scan_bwd: scratch of %zu bytes, 16-byte aligned, is required (got %zu)", need, a.scratch_bytes);
+                    "selective_scan_bwd: scratch of at least %zu bytes, 16-byte aligned, is required (got %zu)", need, a.scratch_bytes);
     int rc;
     if (a.io_dtype == MB200_F32) rc = launch_bwd<float>(a, stream);
     else if (a.io_dtype == MB200_BF16) rc = launch_bwd<__nv_bfloat16>(a, stream);

@@ -124,12 +124,13 @@ def _selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_so
     return out if not return_last_state else (out, last_state)
 
 
-def selective_scan_bwd(u, delta, A, B, C, D, z, delta_bias, dout, delta_softplus=False):
+def selective_scan_bwd(u, delta, A, B, C, D, z, delta_bias, dout, delta_softplus=False, scratch_bytes=None):
     """Gradients of selective_scan_fn for ``dout`` = dL/d(out): the call ``selective_scan_cuda.bwd`` serves in the
     reference (selective_scan_interface.py:83-86, selective_scan.cpp:338-492).  The scan is recomputed from the inputs,
     so nothing of the forward is needed.  Returns ``(du, ddelta, dA, dB, dC, dD, dz, ddelta_bias)``: du, ddelta, dz in
     the dtype of u, dA, dD, ddelta_bias fp32, dB and dC in the dtype and shape of B and C (accumulated in fp32);
-    None where the input is None."""
+    None where the input is None.  ``scratch_bytes`` caps the temporary buffer (default: what the library asks for, at
+    most 1 GiB): with less than the whole batch needs, the batch is walked in slices (one row's worth is the minimum)."""
     L.require_cuda(u, delta, A, B, C, D, z, delta_bias, dout)
     squeeze_B, squeeze_C = B.dim() == 3, C.dim() == 3
     B_dtype, C_dtype = B.dtype, C.dtype
@@ -168,8 +169,9 @@ def selective_scan_bwd(u, delta, A, B, C, D, z, delta_bias, dout, delta_softplus
     L.set_strides(a.C_stride, C, 3 if C_var else 2)
     need = ctypes.c_size_t(0)
     L.check(L.lib().mb200_scan_bwd_scratch_bytes(ctypes.byref(a), ctypes.byref(need)))
-    scratch = torch.empty(need.value, dtype=torch.uint8, device=dev)
-    a.scratch, a.scratch_bytes = L.ptr(scratch), need.value
+    nbytes = need.value if scratch_bytes is None else min(need.value, int(scratch_bytes))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+    a.scratch, a.scratch_bytes = L.ptr(scratch), nbytes
     L.check(L.lib().mb200_selective_scan_bwd(ctypes.byref(a), L.stream_ptr(dev)))
     dB, dC = dB.to(B_dtype), dC.to(C_dtype)       # selective_scan.cpp:487
     if squeeze_B:

@@ -290,6 +290,24 @@ def test_extension_module_stand_in(many):
         assert_close(got, ref, TOL_FP32, "stand-in bwd " + k)
 
 
+def test_extension_module_stand_in_prefix_tensor():
+    """x of the stand-in holds what the extension's forward leaves for its backward (selective_scan_fwd_kernel.cuh:240-258):
+    per 2048-step chunk the decay product from the first step and the state at the chunk's end."""
+    from mamba_b200.compat import selective_scan_cuda
+    inp = make_inputs(83, 1, 8, 5000, 8, 1, torch.float32, has_z=False)
+    c = {k: (None if v is None else v.to(DEV)) for k, v in inp.items()}
+    out, x = selective_scan_cuda.fwd(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], None, c["delta_bias"], True)
+    assert x.shape == (1, 8, 3, 16)
+    dt = torch.nn.functional.softplus(inp["delta"].double() + inp["delta_bias"].double()[:, None])
+    for ch, end in enumerate((2048, 4096, 5000)):
+        want_state = oracle.selective_scan(inp["u"][..., :end], inp["delta"][..., :end], inp["A"], inp["B"][..., :end],
+                                           inp["C"][..., :end], inp["D"], None, inp["delta_bias"], delta_softplus=True,
+                                           return_last_state=True)[1]
+        want_prod = torch.exp(dt[..., :end].sum(-1)[..., None] * inp["A"].double()[None]).float()
+        assert_close(x[:, :, ch, 1::2], want_state, TOL_FP32, f"state at the end of chunk {ch}")
+        assert_close(x[:, :, ch, 0::2], want_prod, TOL_FP32, f"decay product to the end of chunk {ch}")
+
+
 def test_extension_module_stand_in_converts_parameter_dtypes():
     """D and delta_bias in bf16 and a non-contiguous A: the stand-in converts them, and every converted copy must
     still be alive (and described by its own strides) when the kernel runs."""
