@@ -19,6 +19,8 @@ int sm_count(int device);
 // Raises the dynamic shared-memory limit of `kernel` on `device` (which must be current) to at least `bytes`; the
 // runtime is asked once per (kernel, device) and size increase, later calls only consult a small table.
 cudaError_t ensure_dynamic_smem(const void *kernel, int bytes, int device);
+// The backward scan's status word (0 = no bounded wait of its kernels has ever run out on the current device).
+cudaError_t scan_bwd_status(int *status);
 
 #define MB200_CHECK_ARG(cond, ...)                                     \
     do {                                                               \

@@ -1119,8 +1119,11 @@ extern "C" int mb200_scan_status(int device, int *status)
     using namespace mb200;
     if (!status) return fail(MB200_ERR_BAD_ARG, "scan_status: status is NULL");
     if (int rc = enter_device(device)) return rc;
-    const cudaError_t e = cudaMemcpyFromSymbol(status, g_scan_status, sizeof(int));
+    cudaError_t e = cudaMemcpyFromSymbol(status, g_scan_status, sizeof(int));
+    int bwd = 0;
+    if (e == cudaSuccess) e = scan_bwd_status(&bwd);
     if (e != cudaSuccess) return fail(MB200_ERR_LAUNCH, "scan_status: %s", cudaGetErrorString(e));
+    if (*status == 0) *status = bwd;
     return MB200_OK;
 }
 

@@ -22,6 +22,8 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "tc_sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace mb200 {
 namespace {
@@ -31,12 +33,20 @@ constexpr int kBlk = 8;           // steps per block = spacing of the stored sta
 constexpr int kRedStride = 36;    // row stride (words) of the transposition buffer: 16-byte aligned rows, no bank conflicts
 constexpr float kLn2 = 0.6931471805599453f;
 
+// Bounded waits on tile copies record a code here when they run out (0 = never); read through mb200_scan_status.
+__device__ int g_scan_bwd_status;
+constexpr int kStBwdTile = 41;
+
+// u, delta, dout, z as (seqlen, dim, batch) tensors, fetched as tiles of 8 steps x 32 channels
+struct BwdMaps { CUtensorMap u, delta, dout, z, du, ddelta, dz; };
+
 struct BwdPlan {
     int n0;                 // first state of this pass
     int pass, npass;
     int nblk;               // blocks of kBlk steps
     int tiles_per_group;    // CTAs per group (32 channels each, the last one possibly ragged)
     int io_vec, bc_vec;     // rows of the (batch, dim, seqlen) tensors / of B and C may be read in packets
+    int tma_out;            // du, ddelta, dz leave as tiles (16-bit outputs, whole tiles of 32 channels per group)
     float *ckpt;            // [batch][nblk][kNS][dim]: state before each block
     float *acc;             // [3][batch][dim][seqlen] fp32: du, ddelta, dz summed over the earlier passes (npass > 1)
 };
@@ -117,9 +127,13 @@ __device__ __forceinline__ const T *bc_row(const mb200_scan_bwd_args &a, const B
 
 // ---------------------------------------------------------------------------------------------- stored states
 // Walks forward and stores the state before every block but the first (which is zero).
-template <typename T, bool BV>
-__global__ void __launch_bounds__(64, 9) scan_bwd_states_kernel(const mb200_scan_bwd_args a, const BwdPlan pl)
+template <typename T, bool BV, bool TMA>
+__global__ void __launch_bounds__(64, 9) scan_bwd_states_kernel(const mb200_scan_bwd_args a, const BwdPlan pl, const __grid_constant__ BwdMaps maps)
 {
+    constexpr int kTileBytes = 32 * kBlk * (int)sizeof(T);
+    __shared__ __align__(128) uint8_t s_tile[TMA ? 2 : 1][TMA ? kTileBytes : 16];   // u, delta: [channel][step]
+    __shared__ uint64_t s_full;
+    __shared__ int s_dead;
     __shared__ float s_dl[kBlk][32], s_dlu[kBlk][32];
     __shared__ __align__(16) float s_B[kBlk][kNS];
     const Where q = where(pl, a.dim, a.ngroups);
@@ -150,11 +164,41 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_states_kernel(const mb200_scan
     }
     Raw<T, 4> ru, rd;
     Raw<T, 8> rb;
-    ru.load(urow, 4 * w, L, pl.io_vec);
-    rd.load(drow, 4 * w, L, pl.io_vec);
+    auto request_tiles = [&](int k) {     // one thread; the tiles of block k-1 have been read by everybody
+        tc::mbar_expect_tx(&s_full, 2 * kTileBytes);
+        tc::tma_load_3d(s_tile[0], &maps.u, &s_full, k * kBlk, q.dbeg, q.b);
+        tc::tma_load_3d(s_tile[1], &maps.delta, &s_full, k * kBlk, q.dbeg, q.b);
+    };
+    if (TMA) {
+        if (threadIdx.x == 0) {
+            tc::mbar_init(&s_full, 1);
+            tc::mbar_fence_init();
+            s_dead = 0;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) request_tiles(0);
+    } else {
+        ru.load(urow, 4 * w, L, pl.io_vec);
+        rd.load(drow, 4 * w, L, pl.io_vec);
+    }
     if (bc_on) rb.load(brow, 0, L, pl.bc_vec);
     for (int k = 0; k + 1 < pl.nblk; ++k) {
         const int t0 = k * kBlk;
+        if (TMA) {       // my four steps of my row of each tile
+            if (!s_dead && !tc::mbar_wait(&s_full, k & 1, &g_scan_bwd_status, kStBwdTile)) s_dead = 1;
+            auto take = [&](int which, Raw<T, 4> &r) {
+                const uint8_t *src = s_tile[which] + (lane * kBlk + 4 * w) * (int)sizeof(T);
+                if constexpr (sizeof(T) == 4) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                    r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w;
+                } else {
+                    const uint2 v = *reinterpret_cast<const uint2 *>(src);
+                    r.w[0] = v.x; r.w[1] = v.y;
+                }
+            };
+            take(0, ru);
+            take(1, rd);
+        }
 #pragma unroll
         for (int i4 = 0; i4 < 4; ++i4) {
             const int i = 4 * w + i4;
@@ -168,10 +212,13 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_states_kernel(const mb200_scan
 #pragma unroll
             for (int i = 0; i < kBlk; ++i) s_B[i][lane] = bc_on ? rb.get(i) : 0.f;
         }
-        ru.load(urow, t0 + kBlk + 4 * w, L, pl.io_vec);
-        rd.load(drow, t0 + kBlk + 4 * w, L, pl.io_vec);
+        if (!TMA) {
+            ru.load(urow, t0 + kBlk + 4 * w, L, pl.io_vec);
+            rd.load(drow, t0 + kBlk + 4 * w, L, pl.io_vec);
+        }
         if (bc_on) rb.load(brow, t0 + kBlk, L, pl.bc_vec);
         __syncthreads();
+        if (TMA && k + 2 < pl.nblk && threadIdx.x == 0 && !s_dead) request_tiles(k + 1);    // everybody has read the tiles of block k
 #pragma unroll
         for (int i = 0; i < kBlk; ++i) {
             const float dl = s_dl[i][lane], dlu = s_dlu[i][lane];
@@ -212,9 +259,17 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_states_kernel(const mb200_scan
 // that limit only four of a block's eight h_t are kept at a time: the block is walked forward to its middle, its
 // second half forward (kept) and backward, then its first half again from the stored state, forward (kept) and
 // backward -- half a forward walk more instead of 32 more registers.
-template <typename T, bool BV, bool CV>
-__global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_args a, const BwdPlan pl)
+// TMA: the four row tensors arrive as tiles through the copy engine (one request per block from one thread, no
+// row-strided loads, no prefetch registers); otherwise every lane reads its own row.
+template <typename T, bool BV, bool CV, bool TMA>
+__global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_args a, const BwdPlan pl, const __grid_constant__ BwdMaps maps)
 {
+    constexpr int kTileBytes = 32 * kBlk * (int)sizeof(T);
+    constexpr bool TMA_OUT = TMA && sizeof(T) == 2;     // fp32 tiles would cost a CTA per SM
+    __shared__ __align__(128) uint8_t s_tile[TMA ? 4 : 1][TMA ? kTileBytes : 16];   // u, delta, dout, z: [channel][step]
+    __shared__ __align__(128) uint8_t s_out[TMA_OUT ? 3 : 1][TMA_OUT ? kTileBytes : 16];   // du, ddelta, dz
+    __shared__ uint64_t s_full;
+    __shared__ int s_dead;
     __shared__ float s_dl[kBlk][32], s_dlu[kBlk][32], s_dy[kBlk][32];
     __shared__ float s_u[kBlk][32], s_slope[kBlk][32], s_dzf[kBlk][32];   // of a step, for the warp that finishes it
     __shared__ float s_h0[2][8][32];                               // per warp: the state before the block
@@ -257,12 +312,27 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
     Raw<T, 4> ru, rd, rg, rz;
     Raw<T, 8> rbc;
     float hck[8];
-    auto fetch = [&](int k) {        // everything block k needs from memory
+    auto request_tiles = [&](int k) {     // one thread; the tiles of block k+1 have been read by everybody
+        tc::mbar_expect_tx(&s_full, (has_z ? 4 : 3) * kTileBytes);
+        tc::tma_load_3d(s_tile[0], &maps.u, &s_full, k * kBlk, q.dbeg, q.b);
+        tc::tma_load_3d(s_tile[1], &maps.delta, &s_full, k * kBlk, q.dbeg, q.b);
+        tc::tma_load_3d(s_tile[2], &maps.dout, &s_full, k * kBlk, q.dbeg, q.b);
+        if (has_z) tc::tma_load_3d(s_tile[3], &maps.z, &s_full, k * kBlk, q.dbeg, q.b);
+    };
+    auto send_out = [&](int k) {          // one thread; the output tiles of block k are complete
+        tc::tma_store_3d(&maps.du, s_out[0], k * kBlk, q.dbeg, q.b);
+        tc::tma_store_3d(&maps.ddelta, s_out[1], k * kBlk, q.dbeg, q.b);
+        if (has_z) tc::tma_store_3d(&maps.dz, s_out[2], k * kBlk, q.dbeg, q.b);
+        tc::tma_store_commit();
+    };
+    auto fetch = [&](int k) {        // what block k needs from memory through this lane
         const int t = k * kBlk + 4 * w;
-        ru.load(urow, t, L, pl.io_vec);
-        rd.load(drow, t, L, pl.io_vec);
-        rg.load(grow, t, L, pl.io_vec);
-        if (has_z) rz.load(zrow, t, L, pl.io_vec);
+        if (!TMA) {
+            ru.load(urow, t, L, pl.io_vec);
+            rd.load(drow, t, L, pl.io_vec);
+            rg.load(grow, t, L, pl.io_vec);
+            if (has_z) rz.load(zrow, t, L, pl.io_vec);
+        }
         if (bc_on) rbc.load(bcrow, k * kBlk, L, pl.bc_vec);
         if (k > 0 && q.active) {
             const float *src = pl.ckpt + (((int64_t)q.b * pl.nblk + k) * kNS + 8 * w) * a.dim + q.d;
@@ -273,10 +343,36 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
             for (int j = 0; j < 8; ++j) hck[j] = 0.f;
         }
     };
+    if (TMA) {
+        if (threadIdx.x == 0) {
+            tc::mbar_init(&s_full, 1);
+            tc::mbar_fence_init();
+            s_dead = 0;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) request_tiles(pl.nblk - 1);
+    }
     fetch(pl.nblk - 1);
 
     for (int k = pl.nblk - 1; k >= 0; --k) {
         const int t0 = k * kBlk;
+        if (TMA) {       // my four steps of my row of each tile
+            if (!s_dead && !tc::mbar_wait(&s_full, (pl.nblk - 1 - k) & 1, &g_scan_bwd_status, kStBwdTile)) s_dead = 1;
+            auto take = [&](int which, Raw<T, 4> &r) {
+                const uint8_t *src = s_tile[which] + (lane * kBlk + 4 * w) * (int)sizeof(T);
+                if constexpr (sizeof(T) == 4) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                    r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w;
+                } else {
+                    const uint2 v = *reinterpret_cast<const uint2 *>(src);
+                    r.w[0] = v.x; r.w[1] = v.y;
+                }
+            };
+            take(0, ru);
+            take(1, rd);
+            take(2, rg);
+            if (has_z) take(3, rz);
+        }
         // ---- scalars of my four steps, B and C of the block
 #pragma unroll
         for (int i4 = 0; i4 < 4; ++i4) {
@@ -312,6 +408,9 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
         for (int j = 0; j < 8; ++j) s_h0[w][j][lane] = hck[j];
         if (k > 0) fetch(k - 1);
         __syncthreads();
+        if (TMA && k > 0 && threadIdx.x == 0 && !s_dead) request_tiles(k - 1);     // everybody has read the tiles of block k
+        const bool out_tiles = TMA_OUT && pl.tma_out && last;
+        if (out_tiles && k + 1 < pl.nblk && threadIdx.x == 0) send_out(k + 1);      // block k+1's outputs are complete in s_out
 
         auto load_B = [&](int i, uint64_t (&Bp)[4]) {
             if (BV) {
@@ -451,6 +550,7 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
                 }
             }
         }
+        if (out_tiles && threadIdx.x == 0) tc::tma_store_wait_read();     // the tiles of block k+1 have left shared memory
         __syncthreads();
 
         // ---- sums over the 16 states, my four steps
@@ -488,7 +588,21 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
                     }
                 }
             }
-            if (last) {
+            if (out_tiles) {
+                if constexpr (TMA_OUT) {
+                    auto park = [&](int which, const float (&v)[4]) {
+                        uint2 o;
+                        T *e = reinterpret_cast<T *>(&o);
+#pragma unroll
+                        for (int i4 = 0; i4 < 4; ++i4) e[i4] = from_float<T>(v[i4]);
+                        *reinterpret_cast<uint2 *>(s_out[which] + (lane * kBlk + 4 * w) * (int)sizeof(T)) = o;
+                    };
+                    park(0, o_du);
+                    park(1, o_dd);
+                    if (has_z) park(2, o_dz);
+                    tc::fence_proxy_async();
+                }
+            } else if (last) {
                 auto put = [&](void *base, const int64_t *st, const float (&v)[4]) {
                     T *row = static_cast<T *>(base) + (int64_t)q.b * st[0] + (int64_t)q.d * st[1] + t;
                     if (pl.io_vec && t + 4 <= L) {
@@ -518,6 +632,13 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
         // s_part is rewritten only after that barrier, which the reads above precede.
     }
 
+    if (TMA_OUT && pl.tma_out && last) {      // the outputs of block 0
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            send_out(0);
+            tc::tma_store_wait_read();
+        }
+    }
     if (q.active) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -557,10 +678,36 @@ int rows_under_cap(const mb200_scan_bwd_args &a)
 }
 
 template <typename T, bool BV, bool CV>
-void launch_pass(const mb200_scan_bwd_args &a, const BwdPlan &pl, dim3 grid, cudaStream_t stream)
+void launch_pass(const mb200_scan_bwd_args &a, const BwdPlan &pl, dim3 grid, cudaStream_t stream, const BwdMaps *maps)
 {
-    if (pl.nblk > 1) scan_bwd_states_kernel<T, BV><<<grid, 64, 0, stream>>>(a, pl);
-    scan_bwd_kernel<T, BV, CV><<<grid, 64, 0, stream>>>(a, pl);
+    if (maps) {
+        if (pl.nblk > 1) scan_bwd_states_kernel<T, BV, true><<<grid, 64, 0, stream>>>(a, pl, *maps);
+        scan_bwd_kernel<T, BV, CV, true><<<grid, 64, 0, stream>>>(a, pl, *maps);
+    } else {
+        static const BwdMaps none = {};
+        if (pl.nblk > 1) scan_bwd_states_kernel<T, BV, false><<<grid, 64, 0, stream>>>(a, pl, none);
+        scan_bwd_kernel<T, BV, CV, false><<<grid, 64, 0, stream>>>(a, pl, none);
+    }
+}
+
+// Tensor maps of the four row tensors of this slice; false when a tensor cannot be described (the lanes then read
+// their rows themselves).
+template <typename T>
+bool encode_rows(const mb200_scan_bwd_args &a, BwdMaps &m)
+{
+    if (!encode_fn()) return false;
+    const int dtype = sizeof(T) == 4 ? MB200_F32 : (std::is_same<T, __half>::value ? MB200_F16 : MB200_BF16);
+    auto one = [&](CUtensorMap *map, const void *p, const int64_t *st) {
+        const uint64_t dims[3] = {(uint64_t)a.seqlen, (uint64_t)a.dim, (uint64_t)a.batch};
+        const uint64_t sb[2] = {(uint64_t)st[1] * sizeof(T), (uint64_t)st[0] * sizeof(T)};
+        const uint32_t box[3] = {(uint32_t)kBlk, 32u, 1u};
+        return st[0] > 0 && st[1] > 0 && encode_tiled(map, dtype, p, 3, dims, sb, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    };
+    bool ok = one(&m.u, a.u, a.u_stride) && one(&m.delta, a.delta, a.delta_stride) && one(&m.dout, a.dout, a.dout_stride) &&
+              one(&m.du, a.du, a.du_stride) && one(&m.ddelta, a.ddelta, a.ddelta_stride);
+    if (a.z) ok = ok && one(&m.z, a.z, a.z_stride) && one(&m.dz, a.dz, a.dz_stride);
+    else { m.z = m.u; m.dz = m.du; }
+    return ok;
 }
 
 template <typename T>
@@ -612,17 +759,20 @@ int launch_slice(const mb200_scan_bwd_args &a, cudaStream_t stream)
     pl.nblk = (a.seqlen + kBlk - 1) / kBlk;
     const int per_group = a.dim / a.ngroups;
     pl.tiles_per_group = (per_group + 31) / 32;
+    pl.tma_out = per_group % 32 == 0;      // a ragged tile's idle lanes would store into the next group's rows
     pl.npass = (a.dstate + kNS - 1) / kNS;
     pl.ckpt = static_cast<float *>(a.scratch);
     pl.acc = pl.ckpt + (size_t)a.batch * ckpt_floats_per_row(a);
     dim3 grid(a.ngroups * pl.tiles_per_group, a.batch);
+    BwdMaps maps;
+    const BwdMaps *use = (pl.io_vec && encode_rows<T>(a, maps)) ? &maps : nullptr;
     for (int p = 0; p < pl.npass; ++p) {
         pl.pass = p;
         pl.n0 = p * kNS;
-        if (a.B_variable && a.C_variable) launch_pass<T, true, true>(a, pl, grid, stream);
-        else if (a.B_variable) launch_pass<T, true, false>(a, pl, grid, stream);
-        else if (a.C_variable) launch_pass<T, false, true>(a, pl, grid, stream);
-        else launch_pass<T, false, false>(a, pl, grid, stream);
+        if (a.B_variable && a.C_variable) launch_pass<T, true, true>(a, pl, grid, stream, use);
+        else if (a.B_variable) launch_pass<T, true, false>(a, pl, grid, stream, use);
+        else if (a.C_variable) launch_pass<T, false, true>(a, pl, grid, stream, use);
+        else launch_pass<T, false, false>(a, pl, grid, stream, use);
     }
     return MB200_OK;
 }
@@ -641,6 +791,9 @@ int check_bwd(const mb200_scan_bwd_args &a)
 }
 
 }  // namespace
+
+cudaError_t scan_bwd_status(int *status) { return cudaMemcpyFromSymbol(status, g_scan_bwd_status, sizeof(int)); }
+
 }  // namespace mb200
 
 extern "C" int mb200_scan_bwd_scratch_bytes(const mb200_scan_bwd_args *args, size_t *bytes)

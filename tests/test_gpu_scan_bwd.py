@@ -87,6 +87,23 @@ def test_no_softplus_no_bias_strided():
     _check(got, want, TOL_FP32, "strided")
 
 
+@pytest.mark.parametrize("dim,groups", [(64, 2), (48, 1)])
+def test_tiles_through_the_copy_engine_ragged(dim, groups):
+    """16-bit rows with aligned strides take the tile path in and (whole channel tiles only) out: a sequence that ends
+    inside a block of eight steps, rows that are views of wider buffers, and a channel count that leaves a tile ragged."""
+    L = 100
+    x = make_inputs(71, 2, dim, L, 16, groups, torch.bfloat16)
+    g = torch.Generator().manual_seed(171)
+    dout = torch.randn(2, dim, L, generator=g).bfloat16()
+    want = oracle.selective_scan_bwd(*[x[k] for k in KEYS], dout, True)
+    wide = lambda t: torch.cat([t, torch.ones_like(t)], dim=2).to(DEV)[:, :, :L]        # row stride 200, last stride 1
+    got = _bwd()(wide(x["u"]), wide(x["delta"]), _dev(x["A"]), _dev(x["B"]), _dev(x["C"]), _dev(x["D"]), wide(x["z"]),
+                 _dev(x["delta_bias"]), wide(dout), True)
+    _check(got, want, TOL_BF16, f"tiles d{dim}")
+    from mamba_b200 import ops
+    assert ops.scan_status() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_autograd_matches_reference_style_check(dtype):
     """selective_scan_fn(...).backward(g) fills .grad of every input, as tests/ops/test_selective_scan.py:119-147 checks."""
