@@ -953,6 +953,9 @@ bool stream_eligible(const mb200_scan_args &a)
     constexpr int VEC = 16 / sizeof(T);
     if (a.dstate > 16 || !a.B_variable || !a.C_variable || a.out_pregate) return false;
     if ((a.dim / a.ngroups) % kStreamCh != 0) return false;
+    // the output tile store clips the innermost dimension in 16-byte units, not in elements: a row (of a wider buffer)
+    // that ends inside such a unit would have the bytes after its end overwritten
+    if (((size_t)a.seqlen * sizeof(T)) % 16 != 0) return false;
     if ((int64_t)a.batch * a.dim < kStreamMinChannels && split_segments<T>(a) <= 1) return false;
     auto ok2 = [&](const void *p, const int64_t *s) { return aligned16(p) && s[0] > 0 && s[1] > 0 && s[0] % VEC == 0 && s[1] % VEC == 0; };
     auto ok3 = [&](const void *p, const int64_t *s) {

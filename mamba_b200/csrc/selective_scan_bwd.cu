@@ -759,7 +759,10 @@ int launch_slice(const mb200_scan_bwd_args &a, cudaStream_t stream)
     pl.nblk = (a.seqlen + kBlk - 1) / kBlk;
     const int per_group = a.dim / a.ngroups;
     pl.tiles_per_group = (per_group + 31) / 32;
-    pl.tma_out = per_group % 32 == 0;      // a ragged tile's idle lanes would store into the next group's rows
+    // Output tiles need whole channel tiles (a ragged tile's idle lanes would store into the next group's rows) and rows
+    // that end on a 16-byte boundary: a tile store clips the innermost dimension in 16-byte units, not in elements, so
+    // a row of a wider buffer that ends inside such a unit would have the bytes after its end overwritten.
+    pl.tma_out = per_group % 32 == 0 && ((size_t)a.seqlen * sizeof(T)) % 16 == 0;
     pl.npass = (a.dstate + kNS - 1) / kNS;
     pl.ckpt = static_cast<float *>(a.scratch);
     pl.acc = pl.ckpt + (size_t)a.batch * ckpt_floats_per_row(a);

@@ -124,13 +124,15 @@ def _selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_so
     return out if not return_last_state else (out, last_state)
 
 
-def selective_scan_bwd(u, delta, A, B, C, D, z, delta_bias, dout, delta_softplus=False, scratch_bytes=None):
+def selective_scan_bwd(u, delta, A, B, C, D, z, delta_bias, dout, delta_softplus=False, scratch_bytes=None, outputs=None):
     """Gradients of selective_scan_fn for ``dout`` = dL/d(out): the call ``selective_scan_cuda.bwd`` serves in the
     reference (selective_scan_interface.py:83-86, selective_scan.cpp:338-492).  The scan is recomputed from the inputs,
     so nothing of the forward is needed.  Returns ``(du, ddelta, dA, dB, dC, dD, dz, ddelta_bias)``: du, ddelta, dz in
     the dtype of u, dA, dD, ddelta_bias fp32, dB and dC in the dtype and shape of B and C (accumulated in fp32);
     None where the input is None.  ``scratch_bytes`` caps the temporary buffer (default: what the library asks for, at
-    most 1 GiB): with less than the whole batch needs, the batch is walked in slices (one row's worth is the minimum)."""
+    most 1 GiB): with less than the whole batch needs, the batch is walked in slices (one row's worth is the minimum).
+    ``outputs`` = (du, ddelta, dz) lets the caller provide these three (shape and dtype of u, last stride 1; dz None
+    without z), as the extension accepts a preallocated dz (selective_scan.cpp:434-441)."""
     L.require_cuda(u, delta, A, B, C, D, z, delta_bias, dout)
     squeeze_B, squeeze_C = B.dim() == 3, C.dim() == 3
     B_dtype, C_dtype = B.dtype, C.dtype
@@ -140,8 +142,15 @@ def selective_scan_bwd(u, delta, A, B, C, D, z, delta_bias, dout, delta_softplus
     dout = _last_dim_contiguous(dout)
     assert dout.shape == u.shape and dout.dtype == u.dtype, "dout must match u"
     dev = u.device
-    du, ddelta = torch.empty_like(u), torch.empty_like(delta)
-    dz = torch.empty_like(z) if z is not None else None
+    if outputs is None:
+        du, ddelta = torch.empty_like(u), torch.empty_like(delta)
+        dz = torch.empty_like(z) if z is not None else None
+    else:
+        du, ddelta, dz = outputs
+        for t in (du, ddelta) + ((dz,) if z is not None else ()):
+            assert t is not None and t.shape == u.shape and t.dtype == u.dtype and t.stride(-1) == 1, \
+                "outputs must have the shape and dtype of u and a unit last stride"
+        L.require_cuda(du, ddelta, dz)
     f32 = dict(device=dev, dtype=torch.float32)
     dA = torch.empty(dim, dstate, **f32)
     dB = torch.empty(B.shape, **f32)

@@ -204,6 +204,22 @@ def test_bench_config0_full():
     run_both(make_inputs(1000, 2, 256, 512, 16, 1, torch.float32, bench_style=True), TOL_FP32, "config 0")
 
 
+def test_output_row_inside_a_wider_buffer_is_not_overrun():
+    """A caller-provided `out` whose rows are the first 100 steps of 200-step buffers (16-bit, aligned strides): the bytes
+    after a row's end stay untouched (a tile store would clip at a 16-byte unit, not at the element)."""
+    from mamba_b200 import ops
+    L = 100
+    inp = make_inputs(91, 2, 2400, L, 16, 1, torch.bfloat16)
+    wide = lambda t: torch.cat([t, torch.ones_like(t)], dim=2).to(DEV)[:, :, :L]
+    out = torch.full((2, 2400, 2 * L), 7.0, dtype=torch.bfloat16, device=DEV)[:, :, :L]
+    got = ops._selective_scan(wide(inp["u"]), wide(inp["delta"]), inp["A"].to(DEV), inp["B"].to(DEV), inp["C"].to(DEV),
+                              inp["D"].to(DEV), wide(inp["z"]), inp["delta_bias"].to(DEV), True, out=out)
+    want = oracle.selective_scan(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"], inp["z"], inp["delta_bias"],
+                                 delta_softplus=True)
+    assert_close(got, want, TOL_BF16, "row view")
+    assert float((out._base[:, :, L:].float() - 7.0).abs().max()) == 0.0
+
+
 def test_strided_views_like_the_mixer():
     """u and z as the two halves of one xz buffer and delta as a permuted view, as Mamba.forward passes
     them (mamba_ssm/modules/mamba_simple.py:141-200); out inherits delta's strides."""

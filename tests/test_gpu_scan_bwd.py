@@ -89,17 +89,21 @@ def test_no_softplus_no_bias_strided():
 
 @pytest.mark.parametrize("dim,groups", [(64, 2), (48, 1)])
 def test_tiles_through_the_copy_engine_ragged(dim, groups):
-    """16-bit rows with aligned strides take the tile path in and (whole channel tiles only) out: a sequence that ends
-    inside a block of eight steps, rows that are views of wider buffers, and a channel count that leaves a tile ragged."""
+    """16-bit rows with aligned strides arrive as tiles through the copy engine: a sequence that ends inside a block of eight
+    steps, rows that are views of wider buffers (nothing may be written past a row's end: tile stores clip in 16-byte
+    units, so these outputs must leave by plain stores), and a channel count that leaves a tile ragged."""
     L = 100
     x = make_inputs(71, 2, dim, L, 16, groups, torch.bfloat16)
     g = torch.Generator().manual_seed(171)
     dout = torch.randn(2, dim, L, generator=g).bfloat16()
     want = oracle.selective_scan_bwd(*[x[k] for k in KEYS], dout, True)
     wide = lambda t: torch.cat([t, torch.ones_like(t)], dim=2).to(DEV)[:, :, :L]        # row stride 200, last stride 1
+    outs = tuple(torch.full((2, dim, 2 * L), 7.0, dtype=torch.bfloat16, device=DEV)[:, :, :L] for _ in range(3))
     got = _bwd()(wide(x["u"]), wide(x["delta"]), _dev(x["A"]), _dev(x["B"]), _dev(x["C"]), _dev(x["D"]), wide(x["z"]),
-                 _dev(x["delta_bias"]), wide(dout), True)
+                 _dev(x["delta_bias"]), wide(dout), True, outputs=outs)
     _check(got, want, TOL_BF16, f"tiles d{dim}")
+    for t in outs:      # nothing was written past the end of a row
+        assert float((t._base[:, :, L:].float() - 7.0).abs().max()) == 0.0
     from mamba_b200 import ops
     assert ops.scan_status() == 0
 
