@@ -43,7 +43,7 @@ NCU_TRAFFIC = {
     "c2": (1_735_000_000, "profiles/ssd_chunk_scan_forward__config2.md + profiles/ssd_state_stream_kernel__config2.md"),
     "c3": (20_734_000_000, "profiles/ssd_forward__config3_eighth.md (captured on an eighth of the sequence, scaled by 8: every kernel's traffic grows with the number of chunks)"),
     "c4": (1_291_591_424, "profiles/ssu_packet_kernel__config4.md"),
-    "c1b": (3_071_000_000, "profiles/scan_bwd_kernels__config1_shape.md"),
+    "c1b": (3_002_000_000, "profiles/scan_bwd_kernels__config1_shape.md"),
 }
 
 WORKLOAD_DESC = {
