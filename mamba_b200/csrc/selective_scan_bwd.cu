@@ -357,6 +357,9 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
     for (int k = pl.nblk - 1; k >= 0; --k) {
         const int t0 = k * kBlk;
         if (TMA) {       // my four steps of my row of each tile
+            // a wait that ran out has recorded its code; s_dead (set by whichever thread saw it, read unsynchronised:
+            // every thread of the CTA waits on the same barrier and gives up on its own) only keeps the CTA from
+            // spending another time limit per block on its way out
             if (!s_dead && !tc::mbar_wait(&s_full, (pl.nblk - 1 - k) & 1, &g_scan_bwd_status, kStBwdTile)) s_dead = 1;
             auto take = [&](int which, Raw<T, 4> &r) {
                 const uint8_t *src = s_tile[which] + (lane * kBlk + 4 * w) * (int)sizeof(T);
@@ -520,6 +523,8 @@ __global__ void __launch_bounds__(64, 9) scan_bwd_kernel(const mb200_scan_bwd_ar
                     s_part[w][1][i][lane] = lo + hi;
                 }
                 if (BV || CV) {
+                    // lane pair v reads back row v (16 lanes each); with only one of B, C input-dependent the other half of
+                    // the rows was never written, and what the pairs 8-15 (or 0-7) add up there is dropped below
                     __syncwarp();
                     const float4 *src = reinterpret_cast<const float4 *>(red + (lane >> 1) * kRedStride + (lane & 1) * 16);
                     const float4 p0 = src[0], p1 = src[1], p2 = src[2], p3 = src[3];
