@@ -590,11 +590,12 @@ __device__ __forceinline__ int sw32_offset(int row, int chunk) { return row * 32
 
 // SW state warps share the states of the 32 channels; SPLIT gives the scalar work to two warps (warp 0 streams the
 // tiles in and prepares the hand-offs, warp 1 finishes the outputs and streams them out) instead of one.  (2, false) is
-// the layout described above: three warps, nine CTAs per SM, the choice whenever the grid fills the GPU.  (4, true) is
-// the layout for grids that leave SMs nearly empty (a batch divided over several GPUs): six warps per CTA cut the
-// serial chain of a hand-off -- which is all that matters when a CTA has an SM almost to itself -- to a quarter.
+// the layout described above: three warps, nine CTAs per SM, the choice whenever the grid fills the GPU.  The other two
+// are for grids that leave the SMs partly empty (a batch divided over several GPUs), where a CTA's own serial chain per
+// hand-off matters more than the number of CTAs an SM can hold: (2, true), four warps and six CTAs per SM, for up to
+// 888 CTAs; (4, true), six warps (four states per lane) and four CTAs per SM, for up to 592.
 template <typename T, int NS, bool SUMMARY, int SW, bool SPLIT>
-__global__ void __launch_bounds__(32 * (SW + (SPLIT ? 2 : 1)), SW == 2 && !SPLIT ? 9 : 4)
+__global__ void __launch_bounds__(32 * (SW + (SPLIT ? 2 : 1)), !SPLIT ? 9 : SW == 2 ? 6 : 4)
 scan_stream_kernel(const mb200_scan_args a, const __grid_constant__ ScanMaps maps, const ScanSplit sp)
 {
     using namespace tc;
@@ -1015,13 +1016,14 @@ int launch_stream(const mb200_scan_args &a, cudaStream_t stream)
         seg_len = (int)(((a.seqlen + nseg - 1) / nseg + TB - 1) / TB * TB);     // whole tiles per segment
         nseg = (a.seqlen + seg_len - 1) / seg_len;                              // rounding up may leave the last ones empty
     }
-    // A grid that leaves the SMs nearly empty runs the six-warp layout (four CTAs of it fit an SM); see the kernel.
+    // A grid that leaves the SMs partly empty runs the six- or four-warp layout (four / six CTAs of them fit an SM).
     auto go = [&](dim3 grid, const ScanSplit &split, bool summary) {
-        const bool wide = (int64_t)grid.x * grid.y <= 4 * 148;
+        const int64_t ctas = (int64_t)grid.x * grid.y;
         auto pick = [&](auto ns_c, auto sum_c) {
             constexpr int NS = decltype(ns_c)::value;
             constexpr bool SUM = decltype(sum_c)::value;
-            if (wide) scan_stream_kernel<T, NS, SUM, 4, true><<<grid, 192, sizeof(StreamSmem<T, NS, 4, 4>), stream>>>(a, maps, split);
+            if (ctas <= 4 * 148) scan_stream_kernel<T, NS, SUM, 4, true><<<grid, 192, sizeof(StreamSmem<T, NS, 4, 4>), stream>>>(a, maps, split);
+            else if (ctas <= 6 * 148) scan_stream_kernel<T, NS, SUM, 2, true><<<grid, 128, sizeof(StreamSmem<T, NS, 2, 4>), stream>>>(a, maps, split);
             else scan_stream_kernel<T, NS, SUM, 2, false><<<grid, 96, sizeof(StreamSmem<T, NS, 2, 2>), stream>>>(a, maps, split);
         };
         if (ns == 8) summary ? pick(std::integral_constant<int, 8>{}, std::true_type{}) : pick(std::integral_constant<int, 8>{}, std::false_type{});
