@@ -536,6 +536,12 @@ def measure(name, dev, rank, world, local, steps, warmup, batch, cpu_budget):
                      "per": "this GPU's share of the problem, slowest rank's time"},
         "clocks": clocks,
     }
+    if name == "c1" and world == 1 and not w.reduced:
+        # the pipe this kernel leans on hardest is not HBM: the same count of special-function operations issued by
+        # themselves takes 0.3764 ms on this part (tests/test_gpu_mufu_ceiling.py measures it)
+        out["roofline"]["special_function_ceiling"] = {
+            "ms_per_step": 0.3764, "operations": 8 * 5120 * 2048 * (16 + 3), "source": "tests/test_gpu_mufu_ceiling.py (measured on B200, 1965 MHz)",
+            "frac_of_ceiling": 0.3764e-3 / per_step, "ceiling_as_frac_of_hbm_peak": w.alg_bytes / 0.3764e-3 / 1e9 / peak_gbs}
     if w.flops:
         tf = w.flops / per_step / 1e12
         out["roofline"]["tensor"] = {"flops_per_launch": w.flops, "achieved_tflops": tf, "peak_tflops": peak_tf,
