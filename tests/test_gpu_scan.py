@@ -114,11 +114,12 @@ def _row_padded(t, mult=8):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_FP32), (torch.bfloat16, TOL_BF16), (torch.float16, TOL_BF16)])
-@pytest.mark.parametrize("L,N,groups,gated", [(704, 16, 1, True), (333, 8, 2, True), (8, 16, 1, False), (1, 16, 1, True),
-                                              (1030, 12, 1, True), (23, 3, 2, False)])
+@pytest.mark.parametrize("L,N,groups,gated", [(704, 16, 1, True), (328, 8, 2, True), (8, 16, 1, False), (1, 16, 1, True),
+                                              (1032, 12, 1, True), (333, 8, 2, True), (23, 3, 2, False)])
 def test_tma_fed_kernel(dtype, tol, L, N, groups, gated):
-    """Whole groups of 32 channels with 16-byte aligned rows take the warp-specialised TMA-fed kernel: ragged
-    lengths (tiles that run past the end of the rows), dstate below 8 and 16, two groups, with and without gate."""
+    """Whole groups of 32 channels with 16-byte aligned rows that end on a 16-byte boundary take the warp-specialised
+    TMA-fed kernel: lengths that leave the last tile ragged (328, 1032, 8), dstate below 8 and 16, two groups, with and
+    without gate; rows that end inside a 16-byte unit (333, 23, 1) must take another kernel and still be right."""
     from mamba_b200 import ops
     inp = make_inputs(90 + L, 2, 4800, L, N, groups, dtype, has_z=gated, has_D=gated, bench_style=True)
     want, want_last = oracle.selective_scan(inp["u"].float(), inp["delta"].float(), inp["A"], inp["B"].float(),
@@ -134,6 +135,21 @@ def test_tma_fed_kernel(dtype, tol, L, N, groups, gated):
     assert ops.scan_status() == 0
     assert_close(got, want, tol, "tma-fed out")
     assert_close(got_last, want_last, tol, "tma-fed last_state")
+
+
+@pytest.mark.parametrize("batch", [2, 5, 7])
+def test_tma_fed_kernel_layouts_by_grid_size(batch):
+    """300, 750 and 1050 CTAs: the six-warp, the four-warp and the three-warp layout of the TMA-fed kernel."""
+    from mamba_b200 import ops
+    inp = make_inputs(95, batch, 4800, 264, 16, 1, torch.bfloat16, bench_style=True)
+    want, want_last = oracle.selective_scan(inp["u"].float(), inp["delta"].float(), inp["A"], inp["B"].float(), inp["C"].float(),
+                                            inp["D"], inp["z"].float(), inp["delta_bias"], delta_softplus=True, return_last_state=True)
+    c = {k: v.to(DEV) for k, v in inp.items()}
+    got, got_last = _fn()(c["u"], c["delta"], c["A"], c["B"], c["C"], c["D"], c["z"], c["delta_bias"], delta_softplus=True,
+                          return_last_state=True)
+    assert ops.scan_status() == 0
+    assert_close(got, want, TOL_BF16, f"layout for {batch * 150} CTAs out")
+    assert_close(got_last, want_last, TOL_BF16, f"layout for {batch * 150} CTAs last_state")
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_FP32), (torch.bfloat16, TOL_BF16)])
